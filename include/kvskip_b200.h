@@ -1,0 +1,184 @@
+/*
+ * kvskip_b200 -- C ABI of the sm_100a decode-attention library (libkvskip_b200.so).
+ *
+ * One entry point per launcher of the reference's kernel layer (kernels/kvskip.h:113-120 in
+ * format37/kvskip), with the same parameter blocks: plain pointers, sizes and ELEMENT strides,
+ * no framework types.  Differences from the reference's C++ launchers:
+ *   - C linkage, the parameter block is passed by pointer, the stream as an opaque pointer
+ *     (a cudaStream_t);
+ *   - every call returns 0 on success or a negative KVSKIP_E_* code and never throws;
+ *     kvskip_last_error() gives the message of the calling thread's last failure;
+ *   - per-device set-up (shared-memory opt-in, scratch) is keyed by the current device, so one
+ *     process can drive several GPUs.
+ * Nothing is synchronised: kernels are enqueued on the given stream and the call returns.
+ * All pointers are device pointers on the current device unless stated otherwise.
+ */
+#ifndef KVSKIP_B200_H_
+#define KVSKIP_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KVSKIP_TILE 64 /* tokens per KV block: unit of the masks, of the statistics and of a load */
+
+#define KVSKIP_OK 0
+#define KVSKIP_E_ARG (-1)     /* unsupported shape / flag combination / misaligned pointer */
+#define KVSKIP_E_CUDA (-2)    /* a CUDA runtime or driver call failed */
+#define KVSKIP_E_LIMIT (-3)   /* size beyond a stated maximum */
+
+/* Parameter block of the attention family.  Field meaning follows the reference's
+ * kvskip::Params (kernels/kvskip.h:13-60); bf16 / fp16 tensors are typed as uint16_t. */
+typedef struct kvskip_params {
+  /* q [B,Hq,D]; k, v [B,Hkv,T,D], any batch / head / token strides, D contiguous, rows 16-byte
+   * aligned */
+  const uint16_t* q;
+  const uint16_t* k;
+  const uint16_t* v;
+  int64_t q_sb, q_sh;
+  int64_t k_sb, k_sh, k_st;
+  int64_t v_sb, v_sh, v_st;
+  int32_t B, Hq, Hkv, T;
+  float scale_log2; /* softmax scale * log2(e) */
+
+  /* masked mode: ascending list of blocks to read per (b, kv head); entries >= block_cnt ignored */
+  const int32_t* block_idx; /* [B,Hkv,max_blocks] */
+  const int32_t* block_cnt; /* [B,Hkv] */
+  int32_t max_blocks;
+
+  /* split-K: caller-provided scratch, needed when num_splits > 1 */
+  int32_t num_splits;
+  float* part_acc; /* [B,Hq,num_splits,D] un-normalised partial outputs, relative to the split max */
+  float* part_ml;  /* [B,Hq,num_splits,2] split max (log2 units) and split sum */
+
+  /* outputs */
+  uint16_t* out;  /* bf16 [B,Hq,D] */
+  float* out_f32; /* optional [B,Hq,D] */
+  float* lse;     /* [B,Hq] natural-log log-sum-exp over the blocks read */
+
+  /* block statistics: per query head and 64-token block */
+  float* blk_max; /* [B,Hq,nb] max score, natural-log units, scale applied */
+  float* blk_sum; /* [B,Hq,nb] sum exp(score - blk_max) */
+  int32_t nb;
+
+  /* two-pass V-skip */
+  uint16_t* p_out;        /* fp16 [B,Hq,t_pad] exp(s - blk_max), written by a statistics pass, or NULL */
+  const uint16_t* p_in;   /* fp16 [B,Hq,t_pad], read by the pv pass */
+  const float* blk_scale; /* [B,Hkv,nb,G] exp(blk_max - lse_kept), 0 for dropped blocks */
+  int64_t t_pad;          /* nb * KVSKIP_TILE */
+
+  /* single-pass V-skip */
+  float log2_tau;
+  int32_t local;
+  int32_t* vcount;       /* [B,Hkv] V blocks loaded, accumulated atomically; optional */
+  const float* lse_prev; /* [B,Hq] natural-log normaliser estimate; NULL: bound by the sink block */
+} kvskip_params;
+
+/* Refresh planner, before the pass.  Follows kvskip::PlanParams (kernels/kvskip.h:63-89). */
+typedef struct kvskip_plan_params {
+  const uint16_t* q; /* bf16 [B,Hq,D] */
+  int64_t q_sb, q_sh;
+  const uint16_t* k; /* bf16 cache view [B,Hkv,T,D]; the token appended by this step sits at T-1 */
+  int64_t k_sb, k_sh, k_st;
+  float* csum;          /* [B,Hkv,NBC,D] per-block key sums, updated in place when add_token */
+  const float* lse_ref; /* [B,Hq,NBC] block log-sum-exp at the head's last refresh (-inf: none) */
+  const float* cs_ref;  /* [B,Hq,NBC] centroid scores at that refresh */
+  const uint8_t* keep;  /* [B,Hkv,NBC] stored set */
+  const float* lse_att; /* [B,Hq] previous step's log-sum-exp over the attended set */
+  int32_t* age;         /* [B,Hkv] steps since the last refresh, updated */
+  const int32_t* flags; /* [Hkv] bit 0 refresh every step, bit 1 token-index-only, bit 2 index union */
+  const uint8_t* idx;   /* [B,NBC] this step's token-index blocks, or NULL */
+  const float* calib;   /* [B,Hkv] correction of the estimate, or NULL */
+  float* est;           /* [B,Hkv] out: uncorrected estimate (max over the group), or NULL */
+  int32_t calib_on;
+  int32_t calib_kind; /* 0 log-odds offset; 1, 2 added to the share */
+  const uint8_t* aix; /* [B,Hkv] heads latched onto the token index, or NULL */
+  float* cs_now;      /* [B,Hq,NBC] out: this step's centroid scores */
+  uint8_t* trig;      /* [B,Hkv] out: refresh decision */
+  int32_t* block_idx; /* [B,Hkv,NBC] out: blocks to read, ascending */
+  int32_t* block_cnt; /* [B,Hkv] out */
+  int32_t B, Hq, Hkv, T, NBC, local, max_age, add_token;
+  float scale, delta;
+} kvskip_plan_params;
+
+/* Refresh planner, after the pass.  Follows kvskip::UpdateParams (kernels/kvskip.h:91-111). */
+typedef struct kvskip_update_params {
+  const float* blk_max; /* [B,Hq,nb] statistics of this step's pass (-inf / 0 on blocks not read) */
+  const float* blk_sum;
+  const uint8_t* trig;  /* [B,Hkv] */
+  const float* cs_now;  /* [B,Hq,NBC] */
+  uint8_t* keep;        /* [B,Hkv,NBC] updated for refreshing heads */
+  float* lse_ref;       /* [B,Hq,NBC] updated for refreshing heads */
+  float* cs_ref;        /* [B,Hq,NBC] updated for refreshing heads */
+  float* lse_att;       /* [B,Hq] updated for every head */
+  const int32_t* flags; /* [Hkv] */
+  const uint8_t* idx;   /* [B,NBC] or NULL */
+  const float* est;     /* [B,Hkv] */
+  float* calib;         /* [B,Hkv] or NULL: no learning */
+  float calib_rate;
+  int32_t calib_free;
+  int32_t calib_kind;
+  uint8_t* aix; /* [B,Hkv] or NULL */
+  float aix_thr;
+  int32_t B, Hq, Hkv, T, NBC, local;
+  float level;
+} kvskip_update_params;
+
+/* Split-K flash-decoding: dense, masked block list, block statistics, statistics only.
+ * Replaces kvskip::launch_decode (kernels/kvskip.h:113; kernels/kvskip_kernel.cu:761-769).
+ * Runs the split merge itself when num_splits > 1 and load_v.  `stages` is accepted for
+ * compatibility (2 or 3); the ring depth is chosen by the library. */
+int kvskip_launch_decode(const kvskip_params* p, int D, int G, int stages, int masked, int stats, int load_v,
+                         void* stream);
+
+/* Single-pass V-skip.  Replaces kvskip::launch_vskip1 (kernels/kvskip.h:118;
+ * kernels/kvskip_kernel.cu:747-752). */
+int kvskip_launch_vskip1(const kvskip_params* p, int D, int G, void* stream);
+
+/* Two-pass V-skip, second pass.  Replaces kvskip::launch_pv (kernels/kvskip.h:117;
+ * kernels/kvskip_kernel.cu:754-759). */
+int kvskip_launch_pv(const kvskip_params* p, int D, int G, void* stream);
+
+/* Refresh planner.  Replace kvskip::launch_plan / launch_update (kernels/kvskip.h:115-116;
+ * kernels/kvskip_planner.cu:309-318). */
+int kvskip_launch_plan(const kvskip_plan_params* p, void* stream);
+int kvskip_launch_update(const kvskip_update_params* p, void* stream);
+
+/* Streaming read of `bytes` (multiple of 16) with `blocks` CTAs: the bandwidth-ceiling probe.
+ * Replaces kvskip::launch_read (kernels/kvskip.h:120; kernels/kvskip_kernel.cu:738-740). */
+int kvskip_launch_read(const void* x, int64_t bytes, uint32_t* out, int blocks, void* stream);
+
+/* Dynamic shared memory of one decode CTA.  Replaces kvskip::max_smem_bytes
+ * (kernels/kvskip.h:119; kernels/kvskip_kernel.cu:742-745). */
+int kvskip_max_smem_bytes(int D, int stages, int load_v);
+
+/* Merge of R partial results per row: the split merge of kernels/kvskip_kernel.cu:294-314 as an
+ * entry point of its own, used for sequence shards gathered from several GPUs (the reference has
+ * no multi-GPU path).  part_acc [R,N,D], part_ml [R,N,2] (max in log2 units, sum), merged in
+ * ascending r; writes out (bf16, optional), out_f32 (optional), lse (optional) of N rows. */
+int kvskip_launch_merge(const float* part_acc, const float* part_ml, int R, int64_t N, int D, uint16_t* out,
+                        float* out_f32, float* lse, void* stream);
+
+/* Token-index blocks of one decode step on the device (the reference builds them with torch ops,
+ * src/lab.py:149-167): ids int64 [n, ids_stride], current token at T-1; out uint8 [n, NBC], a
+ * block is marked if it holds an earlier copy of the current token or the position after one. */
+int kvskip_launch_index_blocks(const int64_t* ids, int64_t ids_stride, int n, int T, uint8_t* out, int NBC,
+                               void* stream);
+
+/* Message of the calling thread's last failed call ("" if none). */
+const char* kvskip_last_error(void);
+
+/* Reads (and clears) the current device's kernel status word after synchronising `stream`:
+ * 0 if every bounded wait inside the kernels completed, otherwise the code of the first that
+ * gave up.  Host-blocking; meant for tests and post-mortems, not for the hot path. */
+int kvskip_device_status(void* stream, unsigned int* status);
+
+/* Library version: major * 10000 + minor * 100 + patch. */
+int kvskip_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KVSKIP_B200_H_ */

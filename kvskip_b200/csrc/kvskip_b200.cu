@@ -1,0 +1,307 @@
+// libkvskip_b200: C ABI over the sm_100a kernels (see include/kvskip_b200.h).
+// Single translation unit: the kernels live in the .cuh files included below.
+#include "../../include/kvskip_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+#include <set>
+#include <string>
+#include <utility>
+
+#include "common.cuh"
+#include "decode_exact.cuh"
+#include "planner.cuh"
+#include "vskip.cuh"
+
+namespace {
+
+thread_local std::string t_error;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  t_error = buf;
+  return code;
+}
+
+#define KVB_CUDA(expr)                                                                       \
+  do {                                                                                       \
+    cudaError_t e_ = (expr);                                                                 \
+    if (e_ != cudaSuccess) return fail(KVSKIP_E_CUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+// Opt a kernel into its dynamic shared-memory size once per (device, kernel).
+int ensure_smem(const void* func, int bytes) {
+  static std::mutex mu;
+  static std::set<std::pair<int, const void*>> done;
+  int dev = 0;
+  KVB_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.count({dev, func})) return KVSKIP_OK;
+  KVB_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  done.insert({dev, func});
+  return KVSKIP_OK;
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// 4-D map over a [B,Hkv,T,D] bf16 view (element strides sb, sh, st; D contiguous); one box is
+// box_d dims x 64 tokens of one (b, head).  Rows at or beyond T read as zero.
+int make_kv_map(CUtensorMap* map, const void* base, int64_t sb, int64_t sh, int64_t st, int B, int Hkv, int T,
+                int D, int box_d, CUtensorMapSwizzle swz) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return fail(KVSKIP_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  if (reinterpret_cast<uintptr_t>(base) % 16) return fail(KVSKIP_E_ARG, "k / v must be 16-byte aligned");
+  if (st % 8 || sh % 8 || sb % 8) return fail(KVSKIP_E_ARG, "k / v strides must be multiples of 8 elements");
+  // a size-1 dim may carry any stride (even 0); give the map a valid one
+  if (T == 1 && st < D) st = D;
+  if (Hkv == 1 && sh <= 0) sh = static_cast<int64_t>(T) * st;
+  if (B == 1 && sb <= 0) sb = static_cast<int64_t>(Hkv) * (sh > 0 ? sh : 8);
+  if (st <= 0 || sh <= 0 || sb <= 0) return fail(KVSKIP_E_ARG, "k / v strides must be positive");
+  const cuuint64_t gdim[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(Hkv),
+                              static_cast<cuuint64_t>(B)};
+  const cuuint64_t gstr[3] = {static_cast<cuuint64_t>(st) * 2, static_cast<cuuint64_t>(sh) * 2,
+                              static_cast<cuuint64_t>(sb) * 2};
+  const cuuint32_t box[4] = {static_cast<cuuint32_t>(box_d), KVSKIP_TILE, 1, 1};
+  const cuuint32_t est[4] = {1, 1, 1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), gdim, gstr, box, est,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(KVSKIP_E_CUDA, "cuTensorMapEncodeTiled failed (%d) for strides %lld/%lld/%lld dims %d/%d/%d/%d",
+                static_cast<int>(r), static_cast<long long>(sb), static_cast<long long>(sh),
+                static_cast<long long>(st), B, Hkv, T, D);
+  return KVSKIP_OK;
+}
+
+int check_common(const kvskip_params* p, int D, int G) {
+  if (!p) return fail(KVSKIP_E_ARG, "null parameter block");
+  if (G != 4) return fail(KVSKIP_E_ARG, "kvskip: only G = 4 query heads per KV head are instantiated");
+  if (D != 64 && D != 128) return fail(KVSKIP_E_ARG, "kvskip: unsupported head dim");
+  if (p->B < 1 || p->Hkv < 1 || p->T < 1 || p->Hq != p->Hkv * G) return fail(KVSKIP_E_ARG, "bad B / Hq / Hkv / T");
+  if (p->num_splits < 1) return fail(KVSKIP_E_ARG, "num_splits >= 1");
+  if (p->B > 65535 || p->Hkv > 65535) return fail(KVSKIP_E_LIMIT, "B and Hkv are grid dims: at most 65535");
+  return KVSKIP_OK;
+}
+
+template <int D, bool MASKED, bool STATS, bool LOAD_V>
+int launch_exact(const kvskip_params& p, cudaStream_t stream) {
+  using Cfg = kvb::ExactCfg<D, LOAD_V>;
+  auto kernel = kvb::decode_exact_kernel<D, MASKED, STATS, LOAD_V>;
+  if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes)) return rc;
+  kvb::TmaMaps maps;
+  if (int rc = make_kv_map(&maps.k, p.k, p.k_sb, p.k_sh, p.k_st, p.B, p.Hkv, p.T, D, D, CU_TENSOR_MAP_SWIZZLE_NONE))
+    return rc;
+  if (LOAD_V) {
+    if (int rc = make_kv_map(&maps.v, p.v, p.v_sb, p.v_sh, p.v_st, p.B, p.Hkv, p.T, D, D, CU_TENSOR_MAP_SWIZZLE_NONE))
+      return rc;
+  } else {
+    maps.v = maps.k;
+  }
+  const dim3 grid(p.num_splits, p.Hkv, p.B);
+  kernel<<<grid, kvb::EX_THREADS, Cfg::kSmemBytes, stream>>>(p, maps);
+  KVB_CUDA(cudaGetLastError());
+  if (LOAD_V && p.num_splits > 1) {
+    kvb::merge_kernel<D><<<p.B * p.Hq, D, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits,
+                                                        static_cast<int64_t>(p.B) * p.Hq, true, p.out, p.out_f32,
+                                                        p.lse);
+    KVB_CUDA(cudaGetLastError());
+  }
+  return KVSKIP_OK;
+}
+
+template <int D>
+int dispatch_exact(const kvskip_params& p, bool masked, bool stats, bool load_v, cudaStream_t s) {
+  if (!masked && !stats && load_v) return launch_exact<D, false, false, true>(p, s);
+  if (!masked && stats && load_v) return launch_exact<D, false, true, true>(p, s);
+  if (!masked && stats && !load_v) return launch_exact<D, false, true, false>(p, s);
+  if (masked && !stats && load_v) return launch_exact<D, true, false, true>(p, s);
+  if (masked && stats && load_v) return launch_exact<D, true, true, true>(p, s);
+  if (masked && stats && !load_v) return launch_exact<D, true, true, false>(p, s);
+  return fail(KVSKIP_E_ARG, "kvskip: unsupported flag combination (load_v=false needs stats=true)");
+}
+
+template <int D>
+int launch_vskip1_t(const kvskip_params& p, cudaStream_t stream) {
+  using Cfg = kvb::Vskip1Cfg<D>;
+  auto kernel = kvb::vskip1_kernel<D>;
+  if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes)) return rc;
+  kvb::TmaMaps maps;
+  if (int rc = make_kv_map(&maps.k, p.k, p.k_sb, p.k_sh, p.k_st, p.B, p.Hkv, p.T, D, D, CU_TENSOR_MAP_SWIZZLE_NONE))
+    return rc;
+  if (int rc = make_kv_map(&maps.v, p.v, p.v_sb, p.v_sh, p.v_st, p.B, p.Hkv, p.T, D, D, CU_TENSOR_MAP_SWIZZLE_NONE))
+    return rc;
+  kernel<<<dim3(p.num_splits, p.Hkv, p.B), kvb::EX_THREADS, Cfg::kSmemBytes, stream>>>(p, maps);
+  KVB_CUDA(cudaGetLastError());
+  if (p.num_splits > 1) {
+    kvb::merge_kernel<D><<<p.B * p.Hq, D, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits,
+                                                        static_cast<int64_t>(p.B) * p.Hq, true, p.out, p.out_f32,
+                                                        p.lse);
+    KVB_CUDA(cudaGetLastError());
+  }
+  return KVSKIP_OK;
+}
+
+template <int D>
+int launch_pv_t(const kvskip_params& p, cudaStream_t stream) {
+  using Cfg = kvb::PvCfg<D>;
+  auto kernel = kvb::pv_kernel<D>;
+  if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes)) return rc;
+  kvb::TmaMaps maps;
+  if (int rc = make_kv_map(&maps.v, p.v, p.v_sb, p.v_sh, p.v_st, p.B, p.Hkv, p.T, D, D, CU_TENSOR_MAP_SWIZZLE_NONE))
+    return rc;
+  maps.k = maps.v;
+  kernel<<<dim3(p.num_splits, p.Hkv, p.B), kvb::EX_THREADS, Cfg::kSmemBytes, stream>>>(p, maps);
+  KVB_CUDA(cudaGetLastError());
+  if (p.num_splits > 1) {
+    kvb::sum_splits_kernel<D><<<p.B * p.Hq, D, 0, stream>>>(p);
+    KVB_CUDA(cudaGetLastError());
+  }
+  return KVSKIP_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int kvskip_version(void) { return 100; }
+
+const char* kvskip_last_error(void) { return t_error.c_str(); }
+
+int kvskip_max_smem_bytes(int D, int stages, int load_v) {
+  (void)stages;
+  if (D == 128) return load_v ? kvb::ExactCfg<128, true>::kSmemBytes : kvb::ExactCfg<128, false>::kSmemBytes;
+  if (D == 64) return load_v ? kvb::ExactCfg<64, true>::kSmemBytes : kvb::ExactCfg<64, false>::kSmemBytes;
+  return 0;
+}
+
+int kvskip_launch_decode(const kvskip_params* p, int D, int G, int stages, int masked, int stats, int load_v,
+                         void* stream) {
+  if (int rc = check_common(p, D, G)) return rc;
+  if (stages != 2 && stages != 3) return fail(KVSKIP_E_ARG, "kvskip: unsupported head dim / stages");
+  if (!load_v && !stats) return fail(KVSKIP_E_ARG, "kvskip: unsupported flag combination (load_v=false needs stats=true)");
+  if (masked && (!p->block_idx || !p->block_cnt)) return fail(KVSKIP_E_ARG, "masked mode needs block_idx and block_cnt");
+  if (stats && (!p->blk_max || !p->blk_sum)) return fail(KVSKIP_E_ARG, "stats mode needs blk_max and blk_sum");
+  if (load_v && !p->out) return fail(KVSKIP_E_ARG, "out is required when load_v");
+  if (p->num_splits > 1 && (!p->part_ml || (load_v && !p->part_acc)))
+    return fail(KVSKIP_E_ARG, "num_splits > 1 needs part_acc / part_ml scratch");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return D == 128 ? dispatch_exact<128>(*p, masked, stats, load_v, s) : dispatch_exact<64>(*p, masked, stats, load_v, s);
+}
+
+int kvskip_launch_vskip1(const kvskip_params* p, int D, int G, void* stream) {
+  if (int rc = check_common(p, D, G)) return rc;
+  if (!p->out || !p->lse) return fail(KVSKIP_E_ARG, "out and lse are required");
+  if (p->num_splits > 1 && (!p->part_ml || !p->part_acc)) return fail(KVSKIP_E_ARG, "num_splits > 1 needs scratch");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return D == 128 ? launch_vskip1_t<128>(*p, s) : launch_vskip1_t<64>(*p, s);
+}
+
+int kvskip_launch_pv(const kvskip_params* p, int D, int G, void* stream) {
+  if (int rc = check_common(p, D, G)) return rc;
+  if (!p->p_in || !p->blk_scale || !p->block_idx || !p->block_cnt || !p->out)
+    return fail(KVSKIP_E_ARG, "pv needs p_in, blk_scale, block_idx, block_cnt, out");
+  if (p->num_splits > 1 && !p->part_acc) return fail(KVSKIP_E_ARG, "num_splits > 1 needs part_acc scratch");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return D == 128 ? launch_pv_t<128>(*p, s) : launch_pv_t<64>(*p, s);
+}
+
+int kvskip_launch_plan(const kvskip_plan_params* p, void* stream) {
+  if (!p) return fail(KVSKIP_E_ARG, "null parameter block");
+  if (p->Hq != 4 * p->Hkv) return fail(KVSKIP_E_ARG, "planner kernels: D = 128, G = 4");
+  const int nb = (p->T + KVSKIP_TILE - 1) / KVSKIP_TILE;
+  if (nb > p->NBC) return fail(KVSKIP_E_ARG, "block capacity exceeded");
+  if (((p->flags == nullptr)) || !p->csum || !p->keep || !p->block_idx || !p->block_cnt || !p->trig || !p->cs_now)
+    return fail(KVSKIP_E_ARG, "plan: missing state tensor");
+  const int smem = kvb::PL_G * nb * static_cast<int>(sizeof(float));
+  if (smem > 220 * 1024) return fail(KVSKIP_E_LIMIT, "plan: more than %d blocks", 220 * 1024 / 16);
+  if (smem > 48 * 1024)
+    if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::plan_kernel), 220 * 1024)) return rc;
+  kvb::plan_kernel<<<dim3(p->Hkv, p->B), kvb::PL_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(*p);
+  KVB_CUDA(cudaGetLastError());
+  return KVSKIP_OK;
+}
+
+int kvskip_launch_update(const kvskip_update_params* p, void* stream) {
+  if (!p) return fail(KVSKIP_E_ARG, "null parameter block");
+  if (p->Hq != 4 * p->Hkv) return fail(KVSKIP_E_ARG, "planner kernels: D = 128, G = 4");
+  const int nb = (p->T + KVSKIP_TILE - 1) / KVSKIP_TILE;
+  if (nb > p->NBC) return fail(KVSKIP_E_ARG, "block capacity exceeded");
+  if (p->calib && (!p->flags || !p->est)) return fail(KVSKIP_E_ARG, "calibration needs flags and est");
+  if (p->aix && !p->idx) return fail(KVSKIP_E_ARG, "aix needs idx");
+  const int smem = 2 * kvb::PL_G * nb * static_cast<int>(sizeof(float)) + nb;
+  if (smem > 220 * 1024) return fail(KVSKIP_E_LIMIT, "update: more than %d blocks", 220 * 1024 / 33);
+  if (smem > 48 * 1024)
+    if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::update_kernel), 220 * 1024)) return rc;
+  kvb::update_kernel<<<dim3(p->Hkv, p->B), kvb::PL_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(*p);
+  KVB_CUDA(cudaGetLastError());
+  return KVSKIP_OK;
+}
+
+int kvskip_launch_read(const void* x, int64_t bytes, uint32_t* out, int blocks, void* stream) {
+  if (!x || !out || bytes % 16 || blocks < 1) return fail(KVSKIP_E_ARG, "read: x, out, bytes %% 16 == 0, blocks >= 1");
+  kvb::read_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const uint4*>(x),
+                                                                          bytes / 16, out);
+  KVB_CUDA(cudaGetLastError());
+  return KVSKIP_OK;
+}
+
+int kvskip_launch_merge(const float* part_acc, const float* part_ml, int R, int64_t N, int D, uint16_t* out,
+                        float* out_f32, float* lse, void* stream) {
+  if (!part_acc || !part_ml || R < 1 || N < 1) return fail(KVSKIP_E_ARG, "merge: bad arguments");
+  if (N > 2147483647LL) return fail(KVSKIP_E_LIMIT, "merge: too many rows");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (D == 128)
+    kvb::merge_kernel<128><<<static_cast<unsigned>(N), 128, 0, s>>>(part_acc, part_ml, R, N, false, out, out_f32, lse);
+  else if (D == 64)
+    kvb::merge_kernel<64><<<static_cast<unsigned>(N), 64, 0, s>>>(part_acc, part_ml, R, N, false, out, out_f32, lse);
+  else
+    return fail(KVSKIP_E_ARG, "kvskip: unsupported head dim");
+  KVB_CUDA(cudaGetLastError());
+  return KVSKIP_OK;
+}
+
+int kvskip_launch_index_blocks(const int64_t* ids, int64_t ids_stride, int n, int T, uint8_t* out, int NBC,
+                               void* stream) {
+  if (!ids || !out || n < 1 || T < 1) return fail(KVSKIP_E_ARG, "index_blocks: bad arguments");
+  if ((T + KVSKIP_TILE - 1) / KVSKIP_TILE > NBC) return fail(KVSKIP_E_ARG, "block capacity exceeded");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  KVB_CUDA(cudaMemsetAsync(out, 0, static_cast<size_t>(n) * NBC, s));
+  kvb::index_blocks_kernel<<<dim3((T + 255) / 256, n), 256, 0, s>>>(ids, ids_stride, T, out, NBC);
+  KVB_CUDA(cudaGetLastError());
+  return KVSKIP_OK;
+}
+
+int kvskip_device_status(void* stream, unsigned int* status) {
+  if (!status) return fail(KVSKIP_E_ARG, "null status pointer");
+  KVB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  KVB_CUDA(cudaMemcpyFromSymbol(status, kvb::g_status, sizeof(unsigned int)));
+  if (*status) {
+    const unsigned int zero = 0;
+    KVB_CUDA(cudaMemcpyToSymbol(kvb::g_status, &zero, sizeof(zero)));
+  }
+  return KVSKIP_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,291 @@
+// Device-side refresh planner: `plan` before the attention pass, `update` after it.
+//
+// Semantics and float operation order follow format37/kvskip's plan_kernel / update_kernel
+// (kernels/kvskip_planner.cu:75-305) so that, given the same inputs, the integer outputs (refresh
+// decision, block list, stored set, age, index latch) are identical and the float outputs agree to
+// the last bit on the same GPU.  The order that matters:
+//   centroid score   lane l multiplies dims 4l..4l+3 (first product rounded, three fused
+//                    multiply-adds), 32-lane butterfly, then times 1/n_b;
+//   drift estimate   128 "fold slots": slot t folds blocks t, t+128, ... into a running (max, sum);
+//                    slots merge per 32 (max, butterfly of rescaled sums), the four groups merge
+//                    serially in ascending order;
+//   top-p cut        per query head lane l owns blocks l, l+32, ...; 32 bisection steps on the
+//                    log-weight threshold in [-80, 0], each a lane-serial sum + butterfly.
+// Layout of the work is ours: `plan` spreads the centroid scores over every warp of the CTA,
+// keeps them in shared memory for the fold, and raises the dynamic shared-memory limit so block
+// counts beyond 3072 (contexts beyond 196 608 tokens) work.
+#pragma once
+#include "common.cuh"
+
+namespace kvb {
+
+constexpr int PL_THREADS = 128;
+constexpr int PL_G = 4;
+constexpr int PL_D = 128;
+
+__device__ __forceinline__ bool pl_always(int blk, int nb, int local) { return blk == 0 || blk >= nb - local; }
+
+__device__ __forceinline__ float pl_logit(float x) {
+  x = fminf(fmaxf(x, 1e-6f), 1.f - 1e-6f);
+  return __logf(x) - __logf(1.f - x);
+}
+
+// running log-sum-exp (m, s), s relative to m
+__device__ __forceinline__ void pl_fold(float& m, float& s, float e) {
+  if (e == -INFINITY) return;
+  if (e > m) {
+    s = s * __expf(m - e) + 1.f;
+    m = e;
+  } else {
+    s += __expf(e - m);
+  }
+}
+
+// Ascending compaction of the blocks satisfying `pred` into bi[]; count to *cnt.  Chunked scan:
+// thread t owns a contiguous chunk, an inclusive Hillis-Steele scan over the 128 chunk counts
+// gives the offsets.  Must be called by all PL_THREADS threads.
+template <typename Pred>
+__device__ __forceinline__ void pl_compact(int nb, int* bi, int* cnt, int* scan, Pred pred) {
+  const int tid = threadIdx.x;
+  const int per = (nb + PL_THREADS - 1) / PL_THREADS;
+  const int a = min(nb, tid * per), e = min(nb, a + per);
+  int c = 0;
+  for (int i = a; i < e; ++i) c += pred(i) ? 1 : 0;
+  scan[tid] = c;
+  __syncthreads();
+  for (int o = 1; o < PL_THREADS; o <<= 1) {
+    const int add = tid >= o ? scan[tid - o] : 0;
+    __syncthreads();
+    scan[tid] += add;
+    __syncthreads();
+  }
+  int off = scan[tid] - c;
+  for (int i = a; i < e; ++i)
+    if (pred(i)) bi[off++] = i;
+  if (tid == PL_THREADS - 1) *cnt = scan[PL_THREADS - 1];
+}
+
+__global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_params p) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nb = (p.T + TILE - 1) / TILE;
+  const int64_t bh = static_cast<int64_t>(b) * p.Hkv + h;
+  float* csum = p.csum + bh * p.NBC * PL_D;
+  const uint8_t* keep = p.keep + bh * p.NBC;
+  int* bi = p.block_idx + bh * p.NBC;
+  extern __shared__ float pl_scores[];   // [PL_G][nb]
+  __shared__ int scan[PL_THREADS];
+  __shared__ float wM[PL_THREADS / 32][PL_G], wS[PL_THREADS / 32][PL_G];
+  __shared__ int s_trig;
+
+  const int fl = p.flags[h];
+  if (fl & 2) {   // token-index head: index blocks + sink + newest, never refreshes
+    const uint8_t* ix = p.idx + static_cast<int64_t>(b) * p.NBC;
+    pl_compact(nb, bi, p.block_cnt + bh, scan, [&](int i) { return ix[i] || pl_always(i, nb, p.local); });
+    if (tid == 0) p.trig[bh] = 0;
+    return;
+  }
+  const bool uni = (fl & 4) || (p.aix && p.aix[bh]);
+  const uint8_t* ix = uni ? p.idx + static_cast<int64_t>(b) * p.NBC : nullptr;
+  auto attended = [&](int blk) { return keep[blk] || pl_always(blk, nb, p.local) || (uni && ix[blk]); };
+
+  if (p.add_token) {   // D == 128 == PL_THREADS: one dim per thread
+    const int t = p.T - 1;
+    const __nv_bfloat16* kr = reinterpret_cast<const __nv_bfloat16*>(p.k) + b * p.k_sb + h * p.k_sh +
+                              static_cast<int64_t>(t) * p.k_st;
+    csum[static_cast<int64_t>(t / TILE) * PL_D + tid] += __bfloat162float(kr[tid]);
+  }
+  __syncthreads();
+
+  // 1. centroid scores, a warp per block, eight blocks per warp in flight
+  float qv[PL_G][4];
+#pragma unroll
+  for (int g = 0; g < PL_G; ++g) {
+    const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(p.q) + b * p.q_sb + (h * PL_G + g) * p.q_sh + 4 * lane;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) qv[g][e] = __bfloat162float(qp[e]) * p.scale;
+  }
+  const int64_t row0 = (static_cast<int64_t>(b) * p.Hq + h * PL_G) * p.NBC;
+  constexpr int U = 8;
+  constexpr int NW = PL_THREADS / 32;
+  for (int base = warp; base < nb; base += NW * U) {
+    float4 c[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int blk = base + NW * u;
+      c[u] = blk < nb ? *reinterpret_cast<const float4*>(csum + static_cast<int64_t>(blk) * PL_D + 4 * lane)
+                      : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int blk = base + NW * u;
+      if (blk < nb) {
+        const float inv_n = 1.f / static_cast<float>(blk == nb - 1 ? p.T - blk * TILE : TILE);
+        float d[PL_G];
+#pragma unroll
+        for (int g = 0; g < PL_G; ++g)
+          d[g] = warp_sum(qv[g][0] * c[u].x + qv[g][1] * c[u].y + qv[g][2] * c[u].z + qv[g][3] * c[u].w) * inv_n;
+        if (lane < PL_G) {
+          const float val = lane == 0 ? d[0] : lane == 1 ? d[1] : lane == 2 ? d[2] : d[3];
+          pl_scores[lane * nb + blk] = val;
+          p.cs_now[row0 + lane * p.NBC + blk] = val;
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  // 2. estimate of the mass outside the attended set
+  float m[PL_G], s[PL_G];
+#pragma unroll
+  for (int g = 0; g < PL_G; ++g) {
+    m[g] = -INFINITY;
+    s[g] = 0.f;
+  }
+  for (int blk = tid; blk < nb; blk += PL_THREADS) {
+    if (attended(blk)) continue;
+#pragma unroll
+    for (int g = 0; g < PL_G; ++g)
+      pl_fold(m[g], s[g],
+              p.lse_ref[row0 + g * p.NBC + blk] + pl_scores[g * nb + blk] - p.cs_ref[row0 + g * p.NBC + blk]);
+  }
+#pragma unroll
+  for (int g = 0; g < PL_G; ++g) {
+    const float M = warp_max(m[g]);
+    const float S = warp_sum(s[g] > 0.f ? s[g] * __expf(m[g] - M) : 0.f);
+    if (lane == 0) {
+      wM[warp][g] = M;
+      wS[warp][g] = S;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    float miss = 0.f;
+    for (int g = 0; g < PL_G; ++g) {
+      float M = -INFINITY, S = 0.f;
+      for (int w = 0; w < NW; ++w)
+        if (wS[w][g] > 0.f) M = fmaxf(M, wM[w][g]);
+      for (int w = 0; w < NW; ++w)
+        if (wS[w][g] > 0.f) S += wS[w][g] * __expf(wM[w][g] - M);
+      if (S > 0.f) {
+        const float est = M + __logf(S);
+        miss = fmaxf(miss, 1.f / (1.f + __expf(p.lse_att[static_cast<int64_t>(b) * p.Hq + h * PL_G + g] - est)));
+      }
+    }
+    if (p.est) p.est[bh] = miss;
+    float dec = miss;
+    if (p.calib && p.calib_on)
+      dec = p.calib_kind ? miss + p.calib[bh] : 1.f / (1.f + __expf(-(pl_logit(miss) + p.calib[bh])));
+    const int a = p.age[bh] + 1;
+    const bool tr = dec > p.delta || a >= p.max_age || (fl & 1);
+    p.age[bh] = tr ? 0 : a;
+    p.trig[bh] = tr ? 1 : 0;
+    s_trig = tr ? 1 : 0;
+  }
+  __syncthreads();
+
+  // 3. block list of the attention pass
+  if (s_trig) {
+    for (int i = tid; i < nb; i += PL_THREADS) bi[i] = i;
+    if (tid == 0) p.block_cnt[bh] = nb;
+    return;
+  }
+  pl_compact(nb, bi, p.block_cnt + bh, scan, attended);
+}
+
+__global__ void __launch_bounds__(PL_THREADS) update_kernel(const kvskip_update_params p) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nb = (p.T + TILE - 1) / TILE;
+  const int64_t bh = static_cast<int64_t>(b) * p.Hkv + h;
+  const int64_t hrow = static_cast<int64_t>(b) * p.Hq + h * PL_G + warp;   // this warp's query head
+  extern __shared__ float up_smem[];
+  float* x = up_smem + warp * nb;                                          // block log-weights of the head
+  float* ey = up_smem + (PL_G + warp) * nb;                                // exp(x - lse) of the head
+  uint8_t* skeep = reinterpret_cast<uint8_t*>(up_smem + 2 * PL_G * nb);   // [nb] union of the new sets
+  uint8_t* keep = p.keep + bh * p.NBC;
+  const bool tr = p.trig[bh];
+  __shared__ float s_real[PL_G];
+
+  float mx = -INFINITY;
+  for (int i = lane; i < nb; i += 32) {
+    const float val = p.blk_max[hrow * nb + i] + __logf(p.blk_sum[hrow * nb + i]);   // -inf where not read
+    x[i] = val;
+    mx = fmaxf(mx, val);
+  }
+  for (int i = tid; i < nb; i += PL_THREADS) skeep[i] = 0;
+  mx = warp_max(mx);
+  __syncthreads();
+
+  if (tr && p.calib) {   // mass the old attended set really missed (a refreshing head read every block)
+    const bool uni = (p.flags[h] & 4) || (p.aix && p.aix[bh]);
+    const uint8_t* ix = uni ? p.idx + static_cast<int64_t>(b) * p.NBC : nullptr;
+    float mi = -INFINITY, si = 0.f, mo = -INFINITY, so = 0.f;
+    for (int i = lane; i < nb; i += 32) {
+      if (keep[i] || pl_always(i, nb, p.local) || (uni && ix[i])) pl_fold(mi, si, x[i]);
+      else pl_fold(mo, so, x[i]);
+    }
+    const float Mi = warp_max(mi), Si = warp_sum(si > 0.f ? si * __expf(mi - Mi) : 0.f);
+    const float Mo = warp_max(mo), So = warp_sum(so > 0.f ? so * __expf(mo - Mo) : 0.f);
+    if (lane == 0) s_real[warp] = So > 0.f ? 1.f / (1.f + __expf((Mi + __logf(Si)) - (Mo + __logf(So)))) : 0.f;
+  }
+  if (tr) {
+    float se = 0.f;
+    for (int i = lane; i < nb; i += 32) se += __expf(x[i] - mx);
+    const float lse = mx + __logf(warp_sum(se));
+    // exp(y) is the same in all 32 bisection steps: evaluate it once, keep the summation order
+    for (int i = lane; i < nb; i += 32) ey[i] = __expf(x[i] - lse);
+    float lo = -80.f, hi = 0.f;   // mass{y >= lo} >= level > mass{y >= hi}, y = x - lse
+    for (int it = 0; it < 32; ++it) {
+      const float mid = 0.5f * (lo + hi);
+      float a = 0.f;
+      for (int i = lane; i < nb; i += 32)
+        if (x[i] - lse >= mid) a += ey[i];
+      if (warp_sum(a) >= p.level) lo = mid; else hi = mid;
+    }
+    for (int i = lane; i < nb; i += 32)
+      if (x[i] - lse >= lo) skeep[i] = 1;
+    for (int i = lane; i < p.NBC; i += 32) {
+      p.lse_ref[hrow * p.NBC + i] = i < nb ? x[i] : -INFINITY;
+      p.cs_ref[hrow * p.NBC + i] = i < nb ? p.cs_now[hrow * p.NBC + i] : 0.f;
+    }
+  }
+  __syncthreads();
+  if (tr && p.calib && tid == 0) {
+    float real = 0.f;
+    for (int g = 0; g < PL_G; ++g) real = fmaxf(real, s_real[g]);
+    const float est = p.est[bh];
+    const float resid = p.calib_kind ? real - est : pl_logit(real) - pl_logit(est);
+    float c = p.calib_kind == 2 ? fmaxf((1.f - p.calib_rate) * p.calib[bh], resid)
+                                : (1.f - p.calib_rate) * p.calib[bh] + p.calib_rate * resid;
+    if (!p.calib_free) c = fmaxf(c, 0.f);
+    p.calib[bh] = c;
+    if (p.aix && c > p.aix_thr) p.aix[bh] = 1;
+  }
+  if (tr)
+    for (int i = tid; i < p.NBC; i += PL_THREADS)
+      keep[i] = (i < nb && (skeep[i] || pl_always(i, nb, p.local))) ? 1 : 0;
+  __syncthreads();
+  float m2 = -INFINITY, s2 = 0.f;
+  for (int i = lane; i < nb; i += 32)
+    if (keep[i] || pl_always(i, nb, p.local)) pl_fold(m2, s2, x[i]);
+  const float M = warp_max(m2);
+  const float S = warp_sum(s2 > 0.f ? s2 * __expf(m2 - M) : 0.f);
+  if (lane == 0) p.lse_att[hrow] = M + __logf(S);
+}
+
+// Token-index blocks of one step: grid (ceil(T/256), n).  A position t < T-1 holding the current
+// token marks its own block and the block of t+1.
+__global__ void __launch_bounds__(256) index_blocks_kernel(const int64_t* __restrict__ ids, int64_t stride,
+                                                           int T, uint8_t* out, int NBC) {
+  const int r = blockIdx.y;
+  const int64_t* x = ids + r * stride;
+  const int64_t cur = x[T - 1];
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < T - 1 && x[t] == cur) {
+    out[static_cast<int64_t>(r) * NBC + t / TILE] = 1;
+    out[static_cast<int64_t>(r) * NBC + (t + 1) / TILE] = 1;
+  }
+}
+
+}  // namespace kvb

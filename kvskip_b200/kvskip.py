@@ -1,0 +1,213 @@
+"""Python front end of the sm_100a decode-attention kernels.
+
+Drop-in for the reference's `kernels/kvskip.py` (format37/kvskip kernels/kvskip.py:24-208): same
+module-level names, signatures, defaults and return dictionaries, so `src/kvskip_attn.py` and the
+`bench/` scripts of the reference run on top of it unchanged (`from kernels import kvskip` resolves
+to this module through the `kernels/` package at the repository root).
+
+    decode(q, k, v, scale)                                  dense
+    decode(q, k, v, scale, plan=make_plan(keep))            only the listed blocks are read
+    decode(q, k, v, scale, stats=True)                      + per-block max and sum-exp
+    decode(q, k, v, scale, stats=True, load_v=False)        statistics only: K is read, V is not
+    vskip_one_pass / vskip_two_pass / pv                    V-skip variants
+
+q is [B, Hq, D] or [B, Hq, 1, D]; k, v are [B, Hkv, T, D] views with any batch/head/token strides
+and D contiguous.  Blocks are 64 tokens counted from position 0.
+
+There is no CPU path: every call needs the compiled extension and a CUDA device, and raises
+otherwise.
+"""
+
+import importlib.util
+import math
+import os
+from dataclasses import dataclass
+from pathlib import Path
+
+import torch
+
+HERE = Path(__file__).resolve().parent
+TILE = 64
+_EXT = None
+
+
+def ext():
+    """The compiled extension module (decode, vskip1, pv, plan, update, read_bw, ...).
+
+    Loaded from the in-tree `_kvskip_ext.so`; if it is missing and a CUDA toolkit is present it is
+    built once (`python -m kvskip_b200.build`).  Raises RuntimeError if it cannot be had: nothing
+    in this package computes without it."""
+    global _EXT
+    if _EXT is None:
+        so = HERE / "_kvskip_ext.so"
+        if not so.exists() or not (HERE / "libkvskip_b200.so").exists():
+            if os.environ.get("KVSKIP_NO_BUILD"):
+                raise RuntimeError(f"kvskip_b200: {so} is missing and KVSKIP_NO_BUILD is set")
+            try:
+                from . import build as _build
+                _build.build_all(verbose=bool(os.environ.get("KVSKIP_VERBOSE")))
+            except Exception as e:  # noqa: BLE001
+                raise RuntimeError("kvskip_b200: the CUDA extension is not built and building it failed "
+                                   f"(run `python -m kvskip_b200.build`): {e}") from e
+        spec = importlib.util.spec_from_file_location("_kvskip_ext", so)
+        mod = importlib.util.module_from_spec(spec)
+        try:
+            spec.loader.exec_module(mod)
+        except Exception as e:  # noqa: BLE001
+            raise RuntimeError(f"kvskip_b200: cannot load {so}: {e}") from e
+        _EXT = mod
+    return _EXT
+
+
+def num_sms() -> int:
+    return torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+
+
+def num_splits_for(bh: int, n_tiles: int, sms: int | None = None, max_splits: int = 64,
+                   min_tiles: int = 4) -> int:
+    """Split count for bh = B*Hkv sequences of n_tiles blocks each, one CTA per SM.
+
+    Candidates are scored by how full the last wave is (CTAs / (waves * SMs)) minus a small
+    penalty per split, so that of two equally full layouts the one with fewer partials to merge
+    wins; a split never gets fewer than `min_tiles` blocks."""
+    sms = sms or num_sms()
+    choice, top = 1, -1.0
+    s = 1
+    while s <= max_splits:
+        if s > 1 and -(-n_tiles // s) < min_tiles:
+            break
+        ctas = bh * s
+        fill = ctas / (-(-ctas // sms) * sms)
+        score = fill - 0.002 * s
+        if score > top + 1e-9:
+            choice, top = s, score
+        s += 1
+    return choice
+
+
+@dataclass
+class Plan:
+    """Block list of the masked kernel."""
+    block_idx: torch.Tensor   # int32 [B, Hkv, >= max_cnt]: blocks to read first, ascending
+    block_cnt: torch.Tensor   # int32 [B, Hkv]
+    max_cnt: int              # longest list (sizes the split count)
+    nb: int
+
+
+def make_plan(keep: torch.Tensor, sync: bool = True) -> Plan:
+    """bool [B, Hkv, nb] -> Plan.  sync=True reads the longest list length back to size the splits;
+    sync=False sizes them for nb blocks and never touches the host."""
+    nb = keep.shape[-1]
+    cnt = keep.sum(-1, dtype=torch.int32).contiguous()
+    # stable sort of "dropped" flags: kept blocks come first and stay in ascending order
+    order = torch.argsort(keep.logical_not().to(torch.int8), dim=-1, stable=True).to(torch.int32).contiguous()
+    return Plan(order, cnt, int(cnt.max()) if sync else nb, nb)
+
+
+def _q3(q):
+    return q.squeeze(2) if q.dim() == 4 else q
+
+
+def decode(q, k, v, scale: float, *, plan: Plan | None = None, stats: bool = False, load_v: bool = True,
+           num_splits: int | None = None, stages: int = 2, out_f32: bool = False, write_p: bool = False) -> dict:
+    """One layer's decode attention.  Returns dict(out bf16 [B,Hq,D] (None without load_v),
+    lse fp32 [B,Hq], num_splits[, blk_max, blk_sum fp32 [B,Hq,nb]][, out_f32][, p fp16 [B,Hq,nb*64]])."""
+    q = _q3(q)
+    B, Hkv, T = q.shape[0], k.shape[1], k.shape[2]
+    if num_splits is None:
+        n_items = math.ceil(T / TILE) if plan is None else plan.max_cnt
+        num_splits = num_splits_for(B * Hkv, n_items)
+    bi, bc = (None, None) if plan is None else (plan.block_idx, plan.block_cnt)
+    out, lse, bmax, bsum, o32, pbuf = ext().decode(q, k, v, float(scale), bi, bc, stats, load_v,
+                                                   int(num_splits), int(stages), out_f32, write_p)
+    res = {"out": out if load_v else None, "lse": lse, "num_splits": num_splits}
+    if stats:
+        res["blk_max"], res["blk_sum"] = bmax, bsum
+    if out_f32:
+        res["out_f32"] = o32
+    if write_p:
+        res["p"] = pbuf
+    return res
+
+
+def block_weights(blk_max: torch.Tensor, blk_sum: torch.Tensor) -> torch.Tensor:
+    """Softmax mass of every block, [B, Hq, nb], from the statistics outputs."""
+    return torch.softmax(blk_max + torch.log(blk_sum), dim=-1)
+
+
+def always_keep(nb: int, local: int, device) -> torch.Tensor:
+    """Blocks every sparse mode reads: block 0 (sink) and the `local` newest."""
+    a = torch.zeros(nb, dtype=torch.bool, device=device)
+    a[0] = True
+    a[-local:] = True
+    return a
+
+
+def select_blocks(logw: torch.Tensor, G: int, rule: str, value: float, local: int = 2) -> torch.Tensor:
+    """Block selection per KV head (union over its G query heads) from unnormalised block
+    log-weights [B, Hq, nb].  "tau": weight >= value; "topp": fewest blocks whose mass reaches
+    value.  Sink and `local` newest blocks are always selected.  Returns bool [B, Hq//G, nb]."""
+    B, Hq, nb = logw.shape
+    w = torch.softmax(logw, dim=-1)
+    if rule == "tau":
+        per_head = w >= value
+    elif rule == "topp":
+        sorted_w, perm = w.sort(dim=-1, descending=True)
+        before = sorted_w.cumsum(-1) - sorted_w            # mass of the heavier blocks
+        per_head = torch.zeros_like(before, dtype=torch.bool).scatter(-1, perm, before < value)
+    else:
+        raise ValueError(rule)
+    return per_head.view(B, Hq // G, G, nb).any(2) | always_keep(nb, local, logw.device)
+
+
+def pv(P, v, blk_scale, plan: Plan, num_splits: int | None = None, out_f32: bool = False):
+    if num_splits is None:
+        num_splits = num_splits_for(v.shape[0] * v.shape[1], plan.max_cnt)
+    return ext().pv(P, v, blk_scale, plan.block_idx, plan.block_cnt, int(num_splits), out_f32)
+
+
+def vskip_two_pass(q, k, v, scale: float, rule: str = "topp", value: float = 0.99, local: int = 2,
+                   sync: bool = True, out_f32: bool = False) -> dict:
+    """Two-pass V-skip: a statistics pass over all of K that also writes P = exp(s - block max) in
+    fp16, block selection per GQA union, then a pass over P and V of the selected blocks."""
+    q = _q3(q)
+    B, Hq, _ = q.shape
+    Hkv = k.shape[1]
+    G = Hq // Hkv
+    first = decode(q, k, v, scale, stats=True, load_v=False, write_p=True)
+    logw = first["blk_max"] + torch.log(first["blk_sum"])
+    keep = select_blocks(logw, G, rule, value, local)
+    keep_q = keep.repeat_interleave(G, dim=1)
+    lse_kept = logw.masked_fill(~keep_q, float("-inf")).logsumexp(-1, keepdim=True)
+    weight = torch.exp(first["blk_max"] - lse_kept).masked_fill(~keep_q, 0.0)
+    weight = weight.view(B, Hkv, G, -1).transpose(2, 3).contiguous()          # [B, Hkv, nb, G]
+    out, o32 = pv(first["p"], v, weight, make_plan(keep, sync=sync), out_f32=out_f32)
+    res = {"out": out, "keep": keep, "kept_frac": keep.float().mean().item() if sync else None}
+    if out_f32:
+        res["out_f32"] = o32
+    return res
+
+
+def vskip_one_pass(q, k, v, scale: float, tau: float = 1e-4, local: int = 2, num_splits: int | None = None,
+                   out_f32: bool = False, count: bool = False, lse_prev: torch.Tensor | None = None,
+                   sync: bool = True) -> dict:
+    """Single-pass V-skip: K is read once; the V block of a tile is read only if some query head of
+    the group gives the block an estimated weight >= tau.  The normaliser estimate is `lse_prev`
+    (per query head, e.g. the "lse" this function returned one step earlier); without it every
+    CTA uses the sink block's log-sum-exp, a lower bound that keeps every block the exact rule
+    keeps.  count=True adds "v_tiles" [B, Hkv] (and "kept_frac" when sync)."""
+    q = _q3(q)
+    B, Hkv, T = q.shape[0], k.shape[1], k.shape[2]
+    nb = math.ceil(T / TILE)
+    if num_splits is None:
+        num_splits = num_splits_for(B * Hkv, nb)
+    out, lse, o32, cnt = ext().vskip1(q, k, v, float(scale), float(tau), int(local), int(num_splits),
+                                      out_f32, count, lse_prev)
+    res = {"out": out, "lse": lse, "num_splits": num_splits}
+    if out_f32:
+        res["out_f32"] = o32
+    if count:
+        res["v_tiles"] = cnt
+        if sync:
+            res["kept_frac"] = (cnt.sum() / (B * Hkv * nb)).item()
+    return res

@@ -1,0 +1,203 @@
+"""Host-side driver of the refresh policy: plan -> masked attention with block statistics -> update.
+
+Mirrors what the reference's caller does around the kernels (format37/kvskip
+src/kvskip_attn.py:402-478, `refresh_fused_step` with `_pack_fused` / `_grow_fused`, and the first
+step of `refresh_pre_step`, :339-354): the first decode step of a layer runs a dense pass with
+block statistics and builds the planner state with torch ops; every later step is three launches
+on the current stream with no host synchronisation.  The state tensors keep the reference's names
+and layouts, so they can be handed to either implementation.
+
+The compute backend is `ops`: by default the CUDA extension (there is no CPU path in this
+package).  Tests pass a CPU stand-in with the same three callables to check the driver logic.
+"""
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+
+from . import kvskip as K
+
+BLOCK = 64
+CALIB_KINDS = {"logit": 0, "add": 1, "peak": 2}
+
+
+@dataclass
+class RefreshConfig:
+    level: float = 0.99            # top-p mass of a stored set
+    delta: float = 0.05            # refresh when the estimated missed mass exceeds this
+    max_age: int = 32              # forced refresh after this many steps
+    local: int = 2                 # newest blocks always read
+    dense_heads: tuple = ()        # kv heads refreshed on every step
+    index_heads: tuple = ()        # kv heads driven by the token index
+    index_union: bool = False      # index blocks join the attended set instead of replacing it
+    calib: float | None = None     # rate of the online correction of the estimate (None: off)
+    calib_hold: int = 0            # steps before the correction is applied
+    calib_warm: tuple = ()         # (W, A): max age A during the first W steps
+    calib_free: bool = False
+    calib_kind: str = "logit"      # "logit" | "add" | "peak"
+    calib_auto_ix: float | None = None   # latch a head onto the token index when its correction exceeds this
+    margin: int = 64               # spare block capacity of the state tensors
+
+
+class CudaOps:
+    """The product backend: the compiled extension."""
+
+    def decode(self, q, k, v, scale, plan=None, stats=False):
+        return K.decode(q, k, v, scale, plan=plan, stats=stats)
+
+    def plan(self, *a):
+        return K.ext().plan(*a)
+
+    def update(self, *a):
+        return K.ext().update(*a)
+
+
+def centroid_sums(k: torch.Tensor) -> torch.Tensor:
+    """Per-block sums of keys, fp32 [B, Hkv, nb, D] (the last block may be partial)."""
+    B, H, T, D = k.shape
+    nb, full = math.ceil(T / BLOCK), T // BLOCK
+    out = torch.zeros(B, H, nb, D, dtype=torch.float32, device=k.device)
+    if full:
+        out[:, :, :full] = k[:, :, :full * BLOCK].unflatten(2, (full, BLOCK)).sum(3, dtype=torch.float32)
+    if T > full * BLOCK:
+        out[:, :, full] = k[:, :, full * BLOCK:].sum(2, dtype=torch.float32)
+    return out
+
+
+def centroid_scores(q32, csum, T, scale):
+    """q . (block key mean) * scale, [B, Hq, nb]."""
+    nb = csum.shape[2]
+    sizes = torch.full((nb,), float(BLOCK), device=csum.device)
+    sizes[-1] = T - BLOCK * (nb - 1)
+    cen = csum / sizes[None, None, :, None]
+    B, Hq, D = q32.shape
+    Hkv = cen.shape[1]
+    return torch.einsum("bkgd,bknd->bkgn", q32.view(B, Hkv, Hq // Hkv, D), cen).reshape(B, Hq, nb) * scale
+
+
+@dataclass
+class RefreshLayer:
+    cfg: RefreshConfig
+    ops: object = None
+    state: dict | None = None
+    t: int = 0
+    last: dict = field(default_factory=dict)     # tensors of the latest step (block lists, stats), for inspection
+
+    def __post_init__(self):
+        if self.ops is None:
+            self.ops = CudaOps()
+
+    # ---- first decode step: dense + statistics, state built with torch ops ------------------
+    def _init(self, q, k, v, scale):
+        cfg = self.cfg
+        B, Hq, D = q.shape
+        Hkv, T = k.shape[1], k.shape[2]
+        G = Hq // Hkv
+        nb = math.ceil(T / BLOCK)
+        dev = q.device
+        r = self.ops.decode(q, k, v, scale, stats=True)
+        logw = r["blk_max"] + torch.log(r["blk_sum"])
+        csum = centroid_sums(k)
+        keep = K.select_blocks(logw, G, "topp", cfg.level, cfg.local)
+        cs = centroid_scores(q.float(), csum, T, scale)
+        always = K.always_keep(nb, cfg.local, dev)
+        lse_att = logw.masked_fill(~(keep | always).repeat_interleave(G, dim=1), float("-inf")).logsumexp(-1)
+        NBC = nb + cfg.margin
+
+        def padded(x, fill, dtype):
+            out = torch.full((*x.shape[:2], NBC, *x.shape[3:]), fill, dtype=dtype, device=dev)
+            out[:, :, :x.shape[2]] = x
+            return out
+
+        flags = torch.zeros(Hkv, dtype=torch.int32, device=dev)
+        for h in cfg.dense_heads:
+            flags[h] = 1
+        for h in cfg.index_heads:
+            flags[h] = 4 if cfg.index_union else 2
+        self.state = dict(
+            NBC=NBC, flags=flags, scale=float(scale),
+            keep=padded(keep, 0, torch.uint8),
+            lse_ref=padded(logw, float("-inf"), torch.float32),
+            cs_ref=padded(cs, 0.0, torch.float32),
+            csum=padded(csum, 0.0, torch.float32),
+            lse_att=lse_att.float().contiguous(),
+            age=torch.zeros(B, Hkv, dtype=torch.int32, device=dev),
+            calib=torch.zeros(B, Hkv, dtype=torch.float32, device=dev),
+            est=torch.zeros(B, Hkv, dtype=torch.float32, device=dev),
+            aix=torch.zeros(B, Hkv, dtype=torch.uint8, device=dev),
+            cs_now=torch.zeros(B, Hq, NBC, dtype=torch.float32, device=dev),
+            trig=torch.zeros(B, Hkv, dtype=torch.uint8, device=dev),
+            block_idx=torch.zeros(B, Hkv, NBC, dtype=torch.int32, device=dev),
+            block_cnt=torch.zeros(B, Hkv, dtype=torch.int32, device=dev))
+        self.t = 0
+        self.last = {"blk_max": r["blk_max"], "blk_sum": r["blk_sum"], "lse": r["lse"], "first": True}
+        return r["out"]
+
+    def _grow(self, NBC):
+        fills = dict(keep=0, lse_ref=float("-inf"), cs_ref=0.0, csum=0.0, cs_now=0.0, block_idx=0)
+        s = self.state
+        for name, fill in fills.items():
+            x = s[name]
+            out = torch.full((*x.shape[:2], NBC, *x.shape[3:]), fill, dtype=x.dtype, device=x.device)
+            out[:, :, :x.shape[2]] = x
+            s[name] = out
+        s["NBC"] = NBC
+
+    def max_age_now(self) -> int:
+        cfg = self.cfg
+        if cfg.calib_warm and self.t < cfg.calib_warm[0]:
+            return min(cfg.max_age, cfg.calib_warm[1])
+        return cfg.max_age
+
+    def uses_index(self) -> bool:
+        return bool(self.cfg.index_heads) or self.cfg.calib_auto_ix is not None
+
+    # ---- one decode step ------------------------------------------------------------------
+    def step(self, q, k, v, scale, idx_blocks=None):
+        """q [B,Hq,D]; k, v [B,Hkv,T,D] views that already hold the token of this step at T-1.
+        idx_blocks: bool/uint8 [B, >= nb] token-index blocks of this step (index heads / auto latch).
+        Returns out bf16 [B,Hq,D]."""
+        if q.dim() == 4:
+            q = q.squeeze(2)
+        if self.state is None:
+            return self._init(q, k, v, scale)
+        cfg, s = self.cfg, self.state
+        B, T = k.shape[0], k.shape[2]
+        nb = math.ceil(T / BLOCK)
+        if nb > s["NBC"]:
+            self._grow(nb + cfg.margin)
+        idx = None
+        if self.uses_index():
+            if idx_blocks is None:
+                raise ValueError("this configuration needs idx_blocks on every step")
+            if idx_blocks.dtype == torch.uint8 and idx_blocks.shape[1] == s["NBC"] and idx_blocks.is_contiguous():
+                idx = idx_blocks
+            else:
+                idx = torch.zeros(B, s["NBC"], dtype=torch.uint8, device=q.device)
+                idx[:, :nb] = idx_blocks[:, :nb]
+        self.t += 1
+        cal = cfg.calib is not None
+        kind = CALIB_KINDS[cfg.calib_kind]
+        auto = cfg.calib_auto_ix is not None
+        self.ops.plan(q, k, s["csum"], s["lse_ref"], s["cs_ref"], s["keep"], s["lse_att"], s["age"], s["flags"],
+                      s["cs_now"], s["trig"], s["block_idx"], s["block_cnt"], float(scale), float(cfg.delta),
+                      int(self.max_age_now()), int(cfg.local), True, idx, s["calib"] if cal else None, s["est"],
+                      bool(cal and self.t >= cfg.calib_hold), kind, s["aix"] if auto else None)
+        r = self.ops.decode(q, k, v, scale, plan=K.Plan(s["block_idx"], s["block_cnt"], nb, nb), stats=True)
+        self.ops.update(r["blk_max"], r["blk_sum"], s["trig"], s["cs_now"], s["keep"], s["lse_ref"], s["cs_ref"],
+                        s["lse_att"], T, float(cfg.level), int(cfg.local), s["flags"], idx, s["est"],
+                        s["calib"] if cal else None, float(cfg.calib or 0.0), bool(cfg.calib_free), kind,
+                        s["aix"] if auto else None, float(cfg.calib_auto_ix or 0.0))
+        self.last = {"blk_max": r["blk_max"], "blk_sum": r["blk_sum"], "lse": r["lse"], "first": False}
+        return r["out"]
+
+    def read_mask(self, nb: int) -> torch.Tensor:
+        """bool [B,Hkv,nb]: the blocks the latest step read (from block_idx / block_cnt)."""
+        s = self.state
+        bi, bc = s["block_idx"], s["block_cnt"]
+        n = bi.shape[-1]
+        valid = torch.arange(n, device=bi.device)[None, None, :] < bc[..., None]
+        m = torch.zeros(*bi.shape[:2], n + 1, dtype=torch.bool, device=bi.device)
+        m.scatter_(-1, torch.where(valid, bi.long(), n), True)
+        return m[..., :nb]
