@@ -1,0 +1,95 @@
+"""Multi-GPU partitioning of the decode step (one process per GPU, torch.distributed).
+
+The reference is single-GPU; this is the part of the design it has no counterpart for.
+
+Two partitionings, matching how the path shards:
+  * by (batch, KV head): every (b, kv head) is independent in every kernel, so ranks own disjoint
+    slices of the cache and of the planner state and run the unchanged kernels -- no collective.
+  * by sequence, for one very long context: rank r owns a contiguous range of 64-token blocks,
+    runs the unchanged attention kernel on its range and produces, per (b, query head), the
+    triple (m, l, acc) with m the running max in log2 units, l the sum and acc the un-normalised
+    output; the triples are all-gathered (NCCL over NVLink: R x B*Hq x (D+2) floats, 16.6 KB per
+    rank at batch 1) and merged on every rank with the split-merge arithmetic in ascending rank
+    order.  A normalised local result is itself such a triple: (lse / ln 2, 1, out).
+"""
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from . import kvskip as K
+
+LOG2E = 1.4426950408889634
+BLOCK = 64
+
+
+def batch_slice(B: int, rank: int, world: int) -> slice:
+    """Contiguous slice of the batch owned by `rank` (sizes differ by at most one)."""
+    base, extra = divmod(B, world)
+    start = rank * base + min(rank, extra)
+    return slice(start, start + base + (1 if rank < extra else 0))
+
+
+def unit_slices(B: int, Hkv: int, rank: int, world: int):
+    """(batch slice, head slice) of the B*Hkv independent units for `rank`: whole batch elements
+    when there are enough of them, otherwise KV heads of the same batch elements."""
+    if B >= world:
+        return batch_slice(B, rank, world), slice(0, Hkv)
+    if (B * Hkv) % world:
+        raise ValueError(f"B*Hkv={B * Hkv} units do not divide over {world} ranks")
+    per = B * Hkv // world                 # heads per rank
+    if Hkv % per:
+        raise ValueError("a rank's heads must lie inside one batch element")
+    first = rank * per
+    b, h0 = divmod(first, Hkv)
+    return slice(b, b + 1), slice(h0, h0 + per)
+
+
+def block_range(nb: int, rank: int, world: int):
+    """Blocks [lo, hi) of a sequence of nb blocks owned by `rank`."""
+    per = -(-nb // world)
+    lo = min(nb, rank * per)
+    return lo, min(nb, lo + per)
+
+
+def local_partial(q, k_local, v_local, scale, plan=None, num_splits=None):
+    """Attention over this rank's part of the sequence as a packed (acc, m, l) triple:
+    fp32 [B*Hq, D+2] with acc = normalised local output, m = local lse in log2 units, l = 1
+    (l = 0 and m = -inf when the rank read nothing)."""
+    r = K.decode(q, k_local, v_local, scale, plan=plan, num_splits=num_splits, out_f32=True)
+    B, Hq, D = r["out_f32"].shape
+    lse = r["lse"].reshape(B * Hq, 1)
+    empty = torch.isinf(lse)
+    m = lse * LOG2E
+    l = torch.where(empty, torch.zeros_like(lse), torch.ones_like(lse))
+    return torch.cat([r["out_f32"].reshape(B * Hq, D), m, l], dim=-1).contiguous()
+
+
+def merge_partials(parts: torch.Tensor, B: int, Hq: int):
+    """parts fp32 [R, B*Hq, D+2] -> dict(out bf16 [B,Hq,D], out_f32, lse [B,Hq]) with the split
+    merge, ranks in ascending order."""
+    R, N, W = parts.shape
+    D = W - 2
+    acc = parts[..., :D].contiguous()
+    ml = parts[..., D:].contiguous()
+    out, o32, lse = K.ext().merge(acc, ml)
+    return {"out": out.view(B, Hq, D), "out_f32": o32.view(B, Hq, D), "lse": lse.view(B, Hq)}
+
+
+def decode_sequence_sharded(q, k_local, v_local, scale, plan=None, group=None, num_splits=None):
+    """One decode step with the sequence split over the ranks of `group`.  k_local / v_local
+    hold this rank's block range; `plan` (optional) lists local block indices.  Every rank
+    returns the full result."""
+    B, Hq = q.shape[0], q.shape[1]
+    part = local_partial(q, k_local, v_local, scale, plan=plan, num_splits=num_splits)
+    world = dist.get_world_size(group)
+    parts = torch.empty(world, *part.shape, dtype=part.dtype, device=part.device)
+    dist.all_gather_into_tensor(parts, part, group=group)
+    return merge_partials(parts, B, Hq)
+
+
+def shard_plan(keep: torch.Tensor, rank: int, world: int):
+    """Global bool mask [B,Hkv,nb] -> this rank's local mask over its block range (rebased)."""
+    lo, hi = block_range(keep.shape[-1], rank, world)
+    return keep[..., lo:hi]

@@ -521,8 +521,8 @@ void kvo_plan_f32(const uint16_t* q, int64_t q_sb, int64_t q_sh,
  * order: lane l of query head g owns blocks l, l+32, ...
  * In place: keep, lse_ref, cs_ref (refreshing heads), lse_att (all heads), calib, aix.
  * blk_max / blk_sum are [B,Hq,nb] (row stride nb), the state tensors [.,.,NBC].
- * Optional out topp_margin [B,Hq]: smallest |y_i - lo| over blocks (how close the top-p cut is
- * to a block's log-weight; 0 would mean a tie).
+ * Optional out topp_margin [B,Hq]: min(mass of the kept set - level, level - mass without the
+ * lightest kept block): how close the top-p cut is to keeping one block more or fewer.
  * ---------------------------------------------------------------------------------------- */
 void kvo_update_f32(const float* blk_max, const float* blk_sum, const uint8_t* trig,
                     const float* cs_now, uint8_t* keep, float* lse_ref, float* cs_ref,
@@ -586,12 +586,18 @@ void kvo_update_f32(const float* blk_max, const float* blk_sum, const uint8_t* t
             }
             if (butterfly32(acc) >= level) lo = mid; else hi = mid;
           }
-          float closest = INFINITY;
+          /* how far the cut is from flipping: mass of the kept set above `level`, and `level` above
+             the mass without the lightest kept block */
+          double mass_in = 0.0, ymin = INFINITY;
           for (int i = 0; i < nb; ++i) {
             const float y = xg[i] - lse;
-            if (y >= lo) skeep[i] = 1;
-            if (y != -INFINITY) closest = fminf(closest, fabsf(y - lo));
+            if (y >= lo) {
+              skeep[i] = 1;
+              mass_in += exp((double)y);
+              if (y < ymin) ymin = y;
+            }
           }
+          const float closest = (float)fmin(mass_in - (double)level, (double)level - (mass_in - exp(ymin)));
           if (topp_margin) topp_margin[hrow] = closest;
           for (int i = 0; i < NBC; ++i) {
             lse_ref[hrow * NBC + i] = i < nb ? xg[i] : -INFINITY;
