@@ -1,0 +1,525 @@
+#!/usr/bin/env python
+"""Benchmark of the decode-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-cases]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One "step" is one layer's decode step: dense split-K attention over a 64k-token bf16 KV cache,
+Llama-3.1-8B geometry (32 query heads, 8 KV heads, head dim 128), batch 16 per GPU.  With N GPUs
+the batch is sharded (16 sequences per GPU, no collective): weak scaling.  The metric is achieved
+HBM bandwidth on the K+V bytes one step must read (the reference's convention,
+bench/harness.py:59-67), whole job; `ms_per_step` is the per-layer step time.
+
+Rank 0 prints ONE JSON line.  Keys beyond the basic contract:
+  roofline      the decode kernel against the measured HBM copy bandwidth of this pool
+  cpu_baseline  the CPU restatement (oracle/) timed on the host cores on a bounded sample
+  e2e           the same step through the public Python API with the step's inputs (q and the new
+                token's K/V rows) copied from pinned host memory and the output copied back
+  clocks        SM clock and throttle reasons sampled with nvidia-smi while the step was running
+  cases         other configurations of the same path (sweep, masked, V-skip, planner loop,
+                sequence-sharded long context), each with its own µs and GB/s
+"""
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HQ, HKV, D = 32, 8, 128
+T_HEAD = 65536
+B_PER_GPU = 16
+METRIC = "hbm_GBps_dense_decode_64k_per_layer_step"
+
+
+def kv_bytes(B, T, frac=1.0):
+    return 2 * B * HKV * T * D * 2 * frac
+
+
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:  # noqa: BLE001
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi in a loop while the GPU works; read-only."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:  # noqa: BLE001
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:  # noqa: BLE001
+            self.proc.kill()
+        sm, mx, reasons, power = [], None, set(), []
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ts, line in self.rows:
+            if not (t0 <= ts <= t1):
+                continue
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+                power.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(power) if power else None,
+                "window": "timed region plus ~1.5 s of the same step"}
+
+
+def reference_arm(args):
+    """The CPU restatement of the path (oracle/), all host threads, on a bounded sample."""
+    import torch  # noqa: F401
+    import oracle
+    from kvskip_b200 import synth
+    Bs = 2
+    q, k, v, scale = synth.dense_case(1234, Bs, T_HEAD)
+    for _ in range(max(1, min(args.warmup, 2))):
+        oracle.decode_f64(q, k, v, scale)
+    t0 = time.time()
+    for _ in range(args.steps):
+        oracle.decode_f64(q, k, v, scale)
+    dt = time.time() - t0
+    val = kv_bytes(Bs, T_HEAD) * args.steps / dt / 1e9
+    sample = (f"dense decode, batch {Bs} of the {B_PER_GPU} sequences per GPU, 64k context, fp64 arithmetic, "
+              f"{args.steps} steps")
+    line = {"metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic", "impl": "reference",
+            "config": {"workload": "dense split-K decode, Llama-3.1-8B shape (32q/8kv heads, D 128), 64k context, "
+                                   "bf16 K/V; CPU arm runs a bounded sample of the batch",
+                       "sample": sample},
+            "cpu_baseline": {"value": val, "unit": "GB/s", "cores": oracle.num_threads(), "kind": "port",
+                             "sample": sample},
+            "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def time_cuda(fn, iters, flush=None, warmup=3):
+    """Reference protocol (bench/harness.py:38-56): optional L2 sweep, event, op, event; median."""
+    import torch
+    for _ in range(warmup):
+        fn()
+    st = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    en = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    for i in range(iters):
+        if flush is not None:
+            flush()
+        st[i].record()
+        fn()
+        en[i].record()
+    torch.cuda.synchronize()
+    t = sorted(s.elapsed_time(e) * 1e3 for s, e in zip(st, en))
+    return {"us": statistics.median(t), "us_p10": t[int(0.1 * len(t))], "us_p90": t[min(len(t) - 1, int(0.9 * len(t)))]}
+
+
+def single_gpu_cases(dev, peak):
+    """Other configurations of the path on one GPU (parity of each is covered by tests/)."""
+    import torch
+    from kvskip_b200 import kvskip as K
+    from kvskip_b200 import synth
+    from kvskip_b200.refresh import RefreshConfig, RefreshLayer
+    cases = []
+    sweep_buf = torch.ones(512 * 2**20 // 4, dtype=torch.float32, device=dev)
+    sweep_out = torch.empty((), dtype=torch.float32, device=dev)
+
+    def flush():
+        torch.sum(sweep_buf, dim=0, out=sweep_out)      # a read sweep 4x the L2 leaves it full of clean lines
+
+    def add(name, us, nbytes, **kw):
+        gbs = nbytes / (us["us"] * 1e-6) / 1e9
+        cases.append({"case": name, "us": round(us["us"], 2), "us_p10": round(us["us_p10"], 2),
+                      "us_p90": round(us["us_p90"], 2), "GBps": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
+                      **kw})
+
+    g = torch.Generator(device=dev).manual_seed(2)
+    # read ceiling of this GPU with the library's own streaming-read kernel
+    x = torch.ones(2 * 2**30 // 2, dtype=torch.bfloat16, device=dev)
+    o = torch.zeros(1, dtype=torch.int32, device=dev)
+    best = None
+    for blocks in (148 * 4, 148 * 8, 148 * 16, 148 * 32):
+        r = time_cuda(lambda: K.ext().read_bw(x, o, blocks), 10)
+        if best is None or r["us"] < best[0]["us"]:
+            best = (r, blocks)
+    add("read_bw streaming-read ceiling, 2 GiB", best[0], x.numel() * 2, blocks=best[1])
+    del x
+    # dense sweep: batch {1,4,16} x context {8k,32k,64k}
+    for T in (8192, 32768, 65536):
+        for B in (1, 4, 16):
+            q = (torch.randn(B, HQ, D, device=dev, generator=g) / math.sqrt(D)).to(torch.bfloat16)
+            k = torch.randn(B, HKV, T, D, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+            v = torch.randn(B, HKV, T, D, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+            ns = K.num_splits_for(B * HKV, T // 64)
+            add(f"dense B={B} T={T}", time_cuda(lambda: K.decode(q, k, v, D ** -0.5), 30, flush), kv_bytes(B, T),
+                splits=ns)
+            del q, k, v
+    # masked + statistics and single-pass V-skip: batch 1, 64k, planted bodies (union about 55 %)
+    q, k, v, scale, keep = synth.body_union_case(3, T_HEAD)
+    q, k, v, keep = q.to(dev), k.to(dev), v.to(dev), keep.to(dev)
+    plan = K.make_plan(keep)
+    kept = float(keep.float().mean())
+    add("masked+stats B=1 T=65536", time_cuda(lambda: K.decode(q, k, v, scale, plan=plan, stats=True), 30, flush),
+        kv_bytes(1, T_HEAD, kept), kept=round(kept, 4), bytes="K+V of listed blocks")
+    add("masked B=1 T=65536", time_cuda(lambda: K.decode(q, k, v, scale, plan=plan), 30, flush),
+        kv_bytes(1, T_HEAD, kept), kept=round(kept, 4), bytes="K+V of listed blocks")
+    lse = K.decode(q, k, v, scale)["lse"]
+    vk = K.vskip_one_pass(q, k, v, scale, tau=1e-4, lse_prev=lse, count=True)["kept_frac"]
+    add("vskip1 (previous-step normaliser, tau 1e-4) B=1 T=65536",
+        time_cuda(lambda: K.vskip_one_pass(q, k, v, scale, tau=1e-4, lse_prev=lse), 30, flush),
+        kv_bytes(1, T_HEAD, 0.5 * (1 + vk)), v_kept=round(vk, 4), bytes="all K + V of voted blocks")
+    del q, k, v
+    # planner loop: 32 layers, 32k context, 128 steps of plan -> masked+stats -> update
+    L, T0, steps = 32, 32768, 128
+    walks = [synth.planner_walk_device(100 + l, T0, steps, dev) for l in range(L)]
+    ids = synth.token_ids_with_repeats(99, 1, T0 + steps).to(dev)
+    nbm = math.ceil((T0 + steps) / 64)
+    cfg = RefreshConfig(calib=0.05, calib_warm=(32, 8), calib_kind="peak", calib_auto_ix=0.1)
+
+    def run(count):
+        layers = [RefreshLayer(cfg) for _ in range(L)]
+        idx = torch.zeros(1, nbm + cfg.margin, dtype=torch.uint8, device=dev)
+        read = torch.zeros((), dtype=torch.int64, device=dev)
+        total = 0
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        for t in range(steps):
+            if t == 8:
+                ev[0].record()
+            T = T0 + t + 1
+            K.ext().index_blocks(ids, T, idx)
+            for l in range(L):
+                w = walks[l]
+                if l == 0:      # layer 0 is always dense
+                    K.decode(w.q[t], w.k[:, :, :T], w.v[:, :, :T], w.scale)
+                    continue
+                layers[l].step(w.q[t], w.k[:, :, :T], w.v[:, :, :T], w.scale, idx)
+                if count and t >= 8:
+                    read += layers[l].state["block_cnt"].sum()
+                    total += HKV * math.ceil(T / 64)
+        ev[1].record()
+        torch.cuda.synchronize()
+        return ev[0].elapsed_time(ev[1]) * 1e3 / ((steps - 8) * L), (int(read), total)
+
+    us, _ = run(False)
+    _, (read, total) = run(True)
+    frac = read / max(1, total)
+    nbytes = kv_bytes(1, T0 + steps // 2, frac)
+    cases.append({"case": "planner loop: 32 layers x 128 steps, 32k context, layer 0 dense, peak calibration, auto index",
+                  "us": round(us, 2), "blocks_read": round(frac, 4), "GBps": round(nbytes / (us * 1e-6) / 1e9, 1),
+                  "frac_of_peak": round(nbytes / (us * 1e-6) / 1e9 / peak, 4),
+                  "note": "mean per layer-step over steps 8..127, launches issued from Python, no host sync; "
+                          "bytes = K+V of the blocks read by the planner layers"})
+    return cases
+
+
+def multi_gpu_cases(dev, rank, world, peak):
+    """Sequence-sharded long context (one exchange step) and batch-64 masked (no collective)."""
+    import torch
+    import torch.distributed as dist
+    from kvskip_b200 import kvskip as K
+    from kvskip_b200 import shard
+    cases = []
+    g = torch.Generator(device=dev).manual_seed(1000 + rank)
+    # (b) one sequence of 512k tokens, this rank's contiguous block range
+    T = 524288
+    lo, hi = shard.block_range(T // 64, rank, world)
+    Tl = (hi - lo) * 64
+    gq = torch.Generator(device=dev).manual_seed(7)
+    q = (torch.randn(1, HQ, D, device=dev, generator=gq) / math.sqrt(D)).to(torch.bfloat16)
+    k = torch.randn(1, HKV, Tl, D, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    v = torch.randn(1, HKV, Tl, D, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    fn = lambda: shard.decode_sequence_sharded(q, k, v, D ** -0.5)  # noqa: E731
+    for _ in range(5):
+        fn()
+    iters = 30
+    dist.barrier()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e) * 1e3 / iters], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    us = float(t)
+    gbs = kv_bytes(1, T) / (us * 1e-6) / 1e9
+    cases.append({"case": f"sequence-sharded dense B=1 T={T} over {world} GPUs (all-gather of (m,l,acc) + merge)",
+                  "us": round(us, 2), "GBps": round(gbs, 1), "frac_of_peak": round(gbs / (peak * world), 4),
+                  "scaling": "strong", "note": "back-to-back steps, inputs larger than L2"})
+    del k, v
+    # (a) batch 64 x 64k masked at 30 % stored blocks, 64/world sequences per GPU, no collective
+    Bl = shard.batch_slice(64, rank, world)
+    Bn = Bl.stop - Bl.start
+    q = (torch.randn(Bn, HQ, D, device=dev, generator=g) / math.sqrt(D)).to(torch.bfloat16)
+    k = torch.randn(Bn, HKV, T_HEAD, D, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    v = torch.randn(Bn, HKV, T_HEAD, D, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    keep = torch.rand(Bn, HKV, T_HEAD // 64, device=dev, generator=g) < 0.30
+    keep[..., 0] = True
+    keep[..., -2:] = True
+    plan = K.make_plan(keep)
+    kept = keep.float().mean()
+    dist.all_reduce(kept, op=dist.ReduceOp.SUM)
+    kept = float(kept) / world
+    fn = lambda: K.decode(q, k, v, D ** -0.5, plan=plan)  # noqa: E731
+    for _ in range(5):
+        fn()
+    dist.barrier()
+    torch.cuda.synchronize()
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e) * 1e3 / iters], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    us = float(t)
+    gbs = kv_bytes(64, T_HEAD, kept) / (us * 1e-6) / 1e9
+    cases.append({"case": f"masked 30% stored, batch 64 x 64k sharded by batch over {world} GPUs, no collective",
+                  "us": round(us, 2), "GBps": round(gbs, 1), "frac_of_peak": round(gbs / (peak * world), 4),
+                  "kept": round(kept, 4), "scaling": "strong"})
+    return cases
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cases", action="store_true", help="skip the additional configurations")
+    ap.add_argument("--batch", type=int, default=B_PER_GPU, help="sequences per GPU of the headline workload")
+    ap.add_argument("--profile", action="store_true",
+                    help="profiling run: warm-up and timed steps of the headline workload only (use with a small "
+                         "--batch under ncu), prints a short JSON line")
+    ap.add_argument("--mode", default="dense", choices=["dense", "masked", "masked_stats", "vskip1"],
+                    help="kernel variant of a --profile run")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank == 0:
+            reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from kvskip_b200 import kvskip as K
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    K.ext()
+    peak, peak_kind = measured_peak()
+
+    B, T = args.batch, T_HEAD
+    g = torch.Generator(device=dev).manual_seed(42 + rank)
+    q = (torch.randn(B, HQ, D, device=dev, generator=g) / math.sqrt(D)).to(torch.bfloat16)
+    k = torch.empty(B, HKV, T, D, device=dev, dtype=torch.bfloat16)
+    v = torch.empty(B, HKV, T, D, device=dev, dtype=torch.bfloat16)
+    for b in range(B):      # per-sequence generation keeps the fp32 temporaries small
+        k[b] = torch.randn(HKV, T, D, device=dev, generator=g)
+        v[b] = torch.randn(HKV, T, D, device=dev, generator=g)
+    scale = D ** -0.5
+    nsplit = K.num_splits_for(B * HKV, T // 64)
+    step = lambda: K.decode(q, k, v, scale)  # noqa: E731
+    nbytes = kv_bytes(B, T)
+
+    if args.profile:
+        from kvskip_b200 import synth  # noqa: F401
+        if args.mode != "dense":
+            keep = torch.rand(B, HKV, T // 64, device=dev, generator=g) < 0.55
+            keep[..., 0] = True
+            keep[..., -2:] = True
+            plan = K.make_plan(keep)
+            nbytes = kv_bytes(B, T, float(keep.float().mean()))
+            if args.mode == "masked":
+                step = lambda: K.decode(q, k, v, scale, plan=plan)  # noqa: E731
+            elif args.mode == "masked_stats":
+                step = lambda: K.decode(q, k, v, scale, plan=plan, stats=True)  # noqa: E731
+            else:
+                lse = K.decode(q, k, v, scale)["lse"]
+                step = lambda: K.vskip_one_pass(q, k, v, scale, lse_prev=lse)  # noqa: E731
+                nbytes = kv_bytes(B, T)
+        for _ in range(args.warmup):
+            step()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(args.steps):
+            step()
+        e.record()
+        torch.cuda.synchronize()
+        us = s.elapsed_time(e) * 1e3 / args.steps
+        print(json.dumps({"profile": args.mode, "batch": B, "context": T, "us_per_step": us,
+                          "GBps": nbytes / (us * 1e-6) / 1e9, "kv_bytes": int(nbytes)}), flush=True)
+        return
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    for _ in range(args.warmup):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t_w0 = time.time()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(args.steps):
+        step()
+    e.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = s.elapsed_time(e)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_max = float(t)
+    else:
+        ms_max = ms
+    # keep the same step running ~1.5 s so the clock sampler sees it under load (not timed)
+    if rank == 0:
+        t_end = time.time() + 1.5
+        while time.time() < t_end:
+            for _ in range(20):
+                step()
+            torch.cuda.synchronize()
+    clocks = sampler.stop(t_w0, time.time()) if rank == 0 else None
+
+    # end to end through the public API: the step's inputs come from pinned host memory
+    q_h = torch.randn(B, HQ, D).to(torch.bfloat16).pin_memory()
+    kn_h = torch.randn(B, HKV, 1, D).to(torch.bfloat16).pin_memory()
+    vn_h = torch.randn(B, HKV, 1, D).to(torch.bfloat16).pin_memory()
+    out_h = torch.empty(B, HQ, D, dtype=torch.bfloat16).pin_memory()
+    q_d = torch.empty_like(q)
+
+    def e2e_step():
+        q_d.copy_(q_h, non_blocking=True)
+        k[:, :, T - 1:T].copy_(kn_h, non_blocking=True)
+        v[:, :, T - 1:T].copy_(vn_h, non_blocking=True)
+        out_h.copy_(K.decode(q_d, k, v, scale)["out"], non_blocking=True)
+        torch.cuda.synchronize()
+    for _ in range(3):
+        e2e_step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s2.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e2.record()
+    torch.cuda.synchronize()
+    ms2 = s2.elapsed_time(e2)
+    if world > 1:
+        t = torch.tensor([ms2], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms2 = float(t)
+    h2d = q_h.numel() * 2 + kn_h.numel() * 2 + vn_h.numel() * 2
+    d2h = out_h.numel() * 2
+
+    cases = []
+    if not args.no_cases:
+        del k, v
+        torch.cuda.empty_cache()
+        if world == 1:
+            cases = single_gpu_cases(dev, peak)
+        else:
+            cases = multi_gpu_cases(dev, rank, world, peak)
+
+    if rank == 0:
+        per_step_ms = ms_max / args.steps
+        value = world * nbytes * args.steps / (ms_max * 1e-3) / 1e9
+        achieved = nbytes / (ms / args.steps * 1e-3) / 1e9
+        cpu = None
+        if world == 1:
+            import oracle
+            from kvskip_b200 import synth
+            Bs, reps = 2, 12
+            cq, ck, cv, cs = synth.dense_case(1234, Bs, T_HEAD)
+            oracle.decode_f64(cq, ck, cv, cs)
+            t0 = time.time()
+            for _ in range(reps):
+                oracle.decode_f64(cq, ck, cv, cs)
+            dt = time.time() - t0
+            cpu = {"value": kv_bytes(Bs, T_HEAD) * reps / dt / 1e9, "unit": "GB/s", "cores": oracle.num_threads(),
+                   "kind": "port",
+                   "sample": f"dense decode, batch {Bs} of the {B} sequences, 64k context, fp64 arithmetic, {reps} steps"}
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": per_step_ms, "us_per_layer_step": per_step_ms * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": "dense split-K decode, Llama-3.1-8B shape (32q/8kv heads, D 128), 64k context, "
+                                   f"bf16 K/V, batch {B} per GPU sharded by batch (no collective)",
+                       "global_batch": B * world, "context": T, "num_splits": nsplit,
+                       "l2": f"inputs ({nbytes / 1e9:.2f} GB per GPU) larger than the 126 MB L2: no flush between steps",
+                       "kv_bytes_per_step_per_gpu": int(nbytes)},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "of": peak_kind, "traffic": None,
+                         "kernel": "decode_exact_kernel<128,dense> (+ merge_kernel, same timed launch pair)",
+                         "note": "algorithmic bytes = K+V of one step; duration = CUDA events over the timed "
+                                 "region / steps on the launching stream"},
+            "cpu_baseline": cpu,
+            "e2e": {"value": world * nbytes * args.steps / (ms2 * 1e-3) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "note": "q and the new token's K/V rows from pinned host memory, output back to pinned host "
+                            "memory, host sync every step; the KV cache is resident state"},
+            "gpu_launches": args.steps * (2 if nsplit > 1 else 1),
+            "clocks": clocks,
+            "cases": cases,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

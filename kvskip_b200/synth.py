@@ -200,3 +200,42 @@ def index_blocks(ids: torch.Tensor, T: int, n_out: int) -> torch.Tensor:
     out = torch.zeros(ids.shape[0], n_out, dtype=torch.uint8, device=ids.device)
     out[:, :nb] = blk
     return out
+
+
+def planner_walk_device(seed: int, T0: int, steps: int, device, B: int = 1, Hq: int = 32, Hkv: int = 8, D: int = 128,
+                        n_targets: int = 4, target_frac: float = 0.12, gain: float = 100.0,
+                        sink_gain: float = 110.0, sigma: float = 0.02, jump_every: int = 24,
+                        jump_frac: float = 0.30) -> WalkLayer:
+    """planner_walk with the same construction, drawn on `device` with torch's generator (for the
+    benchmark's 32-layer loop, where host generation would take minutes).  Not bit-identical to
+    planner_walk: tests that compare against stored goldens use the numpy version."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    G = Hq // Hkv
+    T = T0 + steps
+    nb0 = T0 // BLOCK
+    k = torch.randn(B, Hkv, T, D, device=device, generator=g)
+    u = torch.nn.functional.normalize(torch.randn(B, Hkv, n_targets, D, device=device, generator=g), dim=-1)
+    n_t = max(1, int(round(target_frac * nb0)))
+    kb = k[:, :, :nb0 * BLOCK].view(B, Hkv, nb0, BLOCK, D)
+    for j in range(n_targets):
+        sel = torch.rand(B, Hkv, nb0, device=device, generator=g).argsort(-1)[..., :n_t]        # random block set
+        add = torch.zeros(B, Hkv, nb0, device=device)
+        add.scatter_(-1, sel, 1.0)
+        kb += gain * add[..., None, None] * u[:, :, j, None, None, :]
+    k[:, :, :BLOCK] += sink_gain * torch.nn.functional.normalize(u.mean(2), dim=-1)[:, :, None, :]
+    kbf = k.to(torch.bfloat16)
+    del k, kb
+    v = torch.randn(B, Hkv, T, D, device=device, generator=g).to(torch.bfloat16)
+    aim = torch.randint(0, n_targets, (B, Hkv), device=device, generator=g)
+    off = torch.randn(B, Hkv, G, D, device=device, generator=g) / math.sqrt(D) * 0.5
+    walk = torch.zeros(B, Hkv, G, D, device=device)
+    qs = torch.empty(steps, B, Hq, D, device=device)
+    for t in range(steps):
+        if t and t % jump_every == 0:
+            jump = torch.rand(B, Hkv, device=device, generator=g) < jump_frac
+            step = 1 + torch.randint(0, n_targets - 1, (B, Hkv), device=device, generator=g)
+            aim = torch.where(jump, (aim + step) % n_targets, aim)
+        walk += sigma * torch.randn(B, Hkv, G, D, device=device, generator=g)
+        base = torch.gather(u, 2, aim[..., None, None].expand(B, Hkv, 1, D))
+        qs[t] = (base + off + walk).reshape(B, Hq, D)
+    return WalkLayer(kbf, v, qs.to(torch.bfloat16), D ** -0.5)
