@@ -167,6 +167,14 @@ int kvskip_launch_merge(const float* part_acc, const float* part_ml, int R, int6
 int kvskip_launch_index_blocks(const int64_t* ids, int64_t ids_stride, int n, int T, uint8_t* out, int NBC,
                                void* stream);
 
+/* Process-wide options (no counterpart in the reference).
+ *   "decode_path"  0 (default): tensor-core kernel for D = 128, exact-order kernel otherwise;
+ *                  1: exact-order kernel everywhere -- scores, block statistics and outputs are
+ *                     bit-identical to the reference's kernels on the same GPU;
+ *                  2: tensor-core kernel, error where it does not exist. */
+int kvskip_set_option(const char* name, int value);
+int kvskip_get_option(const char* name);
+
 /* Message of the calling thread's last failed call ("" if none). */
 const char* kvskip_last_error(void);
 

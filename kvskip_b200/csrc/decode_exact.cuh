@@ -120,6 +120,19 @@ decode_exact_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps)
     const int blk = block_at(i);
     const int t0 = blk * TILE;
     const uint16_t* tK = reinterpret_cast<const uint16_t*>(tiles + s * Cfg::kStageBytes);
+    if constexpr (MASKED && STATS) {
+      // statistics of the blocks the list skips: -inf / 0 between the previous listed block and this
+      // one (the last item also covers the tail), so the caller need not pre-fill the arrays
+      const int prev = (i0 + i) > 0 ? list[i0 + i - 1] : -1;
+      const int next = (i0 + i + 1 == n_items) ? p.nb : blk;
+      for (int o = tid; o < (next - prev - 1) * G; o += EX_THREADS) {
+        const int gblk = prev + 1 + o / G;
+        if (gblk == blk) continue;
+        const int64_t at = (static_cast<int64_t>(b) * p.Hq + h * G + o % G) * p.nb + gblk;
+        p.blk_max[at] = -INFINITY;
+        p.blk_sum[at] = 0.f;
+      }
+    }
 
     // ---- scores: warp w covers rows 16w..16w+15, four rows per pass, eight lanes per row
 #pragma unroll
@@ -216,6 +229,14 @@ decode_exact_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps)
     }
   }
   (void)alive;   // after a timed-out wait the partial state is still written; g_status says so
+  if constexpr (MASKED && STATS) {
+    if (n_items == 0 && split == 0)   // empty list: the first split clears every block of this KV head
+      for (int o = tid; o < p.nb * G; o += EX_THREADS) {
+        const int64_t at = (static_cast<int64_t>(b) * p.Hq + h * G + o % G) * p.nb + o / G;
+        p.blk_max[at] = -INFINITY;
+        p.blk_sum[at] = 0.f;
+      }
+  }
 
   // ---- epilogue: sum the four warps' accumulators through shared memory (tile ring is idle:
   // every issued load has been waited for)

@@ -1,0 +1,376 @@
+// Split-K flash-decoding, fast path: warp-specialised, TMA-fed, tensor-core arithmetic.
+//
+// Why tensor cores on an HBM-bound kernel: the CUDA-core formulation needs ~3850 warp
+// instructions per 64-token block (measured with ncu on the exact-order kernel: 30 % issue-slot
+// use with one warp per scheduler, DRAM at 34 % of peak), i.e. >= 960 issue cycles per block per
+// SM against ~1450 cycles of HBM time per block per SM at full bandwidth -- the grouped q.K and
+// P.V products are issue-bound.  With the tokens of a block on the M axis of mma.m16n8k16
+// (S^T = K Q^T, O^T = V^T P^T; the 4 query heads padded to N = 8) the same block costs ~400 warp
+// instructions, and the kernel goes back to being bound by the loads.
+//
+// Structure of one CTA (one (split, kv head, batch) triple, all 4 query heads of the KV head):
+//   * warp TC_CONSUMERS is the producer: one lane walks the CTA's block range (or its slice of the
+//     block list) and issues, per block, four tiled TMA loads (K and V, two 64-dim halves each,
+//     128-byte swizzle so ldmatrix is bank-conflict free) into a 6-stage ring; every stage has a
+//     `full` mbarrier completed by the copy engine's byte count and an `empty` mbarrier the
+//     consuming warp arrives on.
+//   * warps 0..TC_CONSUMERS-1 are consumers.  A consumer owns whole blocks (block i of the range
+//     goes to warp i mod TC_CONSUMERS) and keeps its own running max / sum / accumulator for the 4
+//     heads, so nothing inside the loop synchronises across warps and block statistics are
+//     warp-local.  Per block: 32 ldmatrix + 32 MMA for the scores, online softmax on the
+//     accumulator fragments (shuffles only across the 8 lanes that share a head), P split into
+//     bf16 high + low parts (fp32-grade weights), movmatrix to turn the score fragment into the B
+//     operand, 32 ldmatrix.trans + 64 MMA for the output.
+//   * epilogue: the consumers' states are merged through shared memory in warp order, then
+//     written as the final output (one split) or as this split's partial (max, sum, acc).
+// Only D = 128, G = 4.  Scores differ from the exact-order path in the last bits (the tensor
+// core's accumulation order); outputs and block log-sum-exps stay within the 2e-3 tolerance.
+#pragma once
+#include "common.cuh"
+#include "decode_exact.cuh"
+
+namespace kvb {
+
+constexpr int TC_CONSUMERS = 8;
+constexpr int TC_THREADS = (TC_CONSUMERS + 1) * 32;
+constexpr int TC_HALF_BYTES = TILE * 64 * 2;        // one TMA box: 64 tokens x 64 dims bf16 = 8 KB
+
+template <bool LOAD_V>
+struct TcCfg {
+  static constexpr int kStageBytes = TC_HALF_BYTES * (LOAD_V ? 4 : 2);
+  static constexpr int kStages = LOAD_V ? 6 : 12;
+  static constexpr int kRedBytes = TC_CONSUMERS * 4 * 128 * 4;     // epilogue staging, aliases the ring
+  static constexpr int kAuxBytes = TC_CONSUMERS * 8 * 4 + 2 * kStages * 8;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kAuxBytes + 1024 /* alignment slack */;
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t movm_t(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+// (lo, hi) floats -> packed bf16x2 (lo in the low half), round to nearest even
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// max / sum over the 8 lanes that share lane % 4 (= the same pair of heads)
+__device__ __forceinline__ float quadcol_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+  return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+}
+__device__ __forceinline__ float quadcol_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 4);
+  v += __shfl_xor_sync(0xffffffffu, v, 8);
+  return v + __shfl_xor_sync(0xffffffffu, v, 16);
+}
+
+template <bool MASKED, bool STATS, bool LOAD_V>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps) {
+  using Cfg = TcCfg<LOAD_V>;
+  constexpr int G = 4, D = 128;
+  constexpr int S = Cfg::kStages;
+  constexpr int NC = TC_CONSUMERS;
+
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* ring = smem;                                              // [S] stages, 1024-byte aligned
+  float* sM = reinterpret_cast<float*>(smem + S * Cfg::kStageBytes);       // [NC][4]
+  float* sL = sM + NC * 4;                                                 // [NC][4]
+  uint64_t* full = reinterpret_cast<uint64_t*>(sL + NC * 4);               // [S]
+  uint64_t* empty = full + S;                                              // [S]
+
+  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  int n_items;
+  const int32_t* list = nullptr;
+  if constexpr (MASKED) {
+    n_items = p.block_cnt[b * p.Hkv + h];
+    list = p.block_idx + static_cast<int64_t>(b * p.Hkv + h) * p.max_blocks;
+  } else {
+    n_items = (p.T + TILE - 1) / TILE;
+  }
+  const int per = (n_items + p.num_splits - 1) / p.num_splits;
+  const int i0 = min(n_items, split * per);
+  const int n = min(n_items, i0 + per) - i0;
+
+  if (tid == 0) {
+    tma_prefetch_desc(&maps.k);
+    if constexpr (LOAD_V) tma_prefetch_desc(&maps.v);
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  // per-thread state of a consumer: two heads (columns 2*(lane&3), +1 of the 8-wide N axis)
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};            // thread-partial sums, reduced across lanes in the epilogue
+  float acc[8][4];                        // O^T fragments: 8 tiles of 16 dims x 8 heads
+#pragma unroll
+  for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[mt][c] = 0.f;
+
+  if (warp == NC) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      for (int i = 0; i < n; ++i) {
+        const int s = i % S;
+        if (i >= S && !mbar_wait(&empty[s], ((i / S) - 1) & 1, 0x200u + s)) break;
+        const int t0 = (MASKED ? list[i0 + i] : i0 + i) * TILE;
+        unsigned char* dst = ring + s * Cfg::kStageBytes;
+        mbar_expect_tx(&full[s], Cfg::kStageBytes);
+        tma_load_4d(dst, &maps.k, &full[s], 0, t0, h, b);
+        tma_load_4d(dst + TC_HALF_BYTES, &maps.k, &full[s], 64, t0, h, b);
+        if constexpr (LOAD_V) {
+          tma_load_4d(dst + 2 * TC_HALF_BYTES, &maps.v, &full[s], 0, t0, h, b);
+          tma_load_4d(dst + 3 * TC_HALF_BYTES, &maps.v, &full[s], 64, t0, h, b);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ consumers
+    // Q^T as the B operand of the score MMA: column n = lane/4 is a head (4..7 are zero padding),
+    // rows k = 2*(lane%4)+{0,1} (+8) of each 16-dim step
+    uint32_t bq[8][2];
+    {
+      const int head = lane >> 2;
+      const uint16_t* qp = p.q + b * p.q_sb + (h * G + (head & 3)) * p.q_sh + 2 * (lane & 3);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        bq[ks][0] = head < G ? *reinterpret_cast<const uint32_t*>(qp + ks * 16) : 0u;
+        bq[ks][1] = head < G ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8) : 0u;
+      }
+    }
+    const int lrow = lane & 7, lmat = lane >> 3;
+    const int64_t hq0 = static_cast<int64_t>(b) * p.Hq + h * G;
+    const bool col_ok = (lane & 3) < 2;          // this thread's two columns are real heads
+    const int head0 = 2 * (lane & 3);
+
+    for (int i = warp; i < n; i += NC) {
+      const int s = i % S;
+      const int blk = MASKED ? list[i0 + i] : i0 + i;
+      const int t0 = blk * TILE;
+      if constexpr (MASKED && STATS) {
+        // statistics of the blocks this list skips: -inf / 0 between the previous listed block and
+        // this one (and after the last listed block), so the caller need not pre-fill the arrays
+        const int prev = (i0 + i) > 0 ? list[i0 + i - 1] : -1;
+        const int next = (i0 + i + 1 == n_items) ? p.nb : blk;   // last item also covers the tail
+        for (int gblk = prev + 1 + lane; gblk < next; gblk += 32) {
+          if (gblk == blk) continue;
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            p.blk_max[(hq0 + g) * p.nb + gblk] = -INFINITY;
+            p.blk_sum[(hq0 + g) * p.nb + gblk] = 0.f;
+          }
+        }
+      }
+      if (!mbar_wait(&full[s], (i / S) & 1, 0x210u + s)) break;
+      const uint32_t kbase = smem_u32(ring + s * Cfg::kStageBytes);
+
+      // ---- S^T = K Q^T: 4 tiles of 16 tokens x 8 heads
+      float sc[4][4];
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sc[mt][c] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t hbase = kbase + (ks >> 2) * TC_HALF_BYTES;
+        const int chunk = (ks & 3) * 2 + (lmat >> 1);
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+          const int row = mt * 16 + (lmat & 1) * 8 + lrow;
+          uint32_t a[4];
+          ldsm_x4(a, hbase + row * 128 + ((chunk ^ lrow) << 4));
+          mma_bf16(sc[mt], a, bq[ks][0], bq[ks][1]);
+        }
+      }
+      // scale to log2 units, mask the tokens past T (last block only)
+      const bool ragged = t0 + TILE > p.T;
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float v = sc[mt][c] * p.scale_log2;
+          if (ragged && t0 + mt * 16 + (lane >> 2) + (c >> 1) * 8 >= p.T) v = -INFINITY;
+          sc[mt][c] = v;
+        }
+      // ---- online softmax, two heads per thread
+      float mb[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float v = fmaxf(sc[0][e], sc[0][e + 2]);
+#pragma unroll
+        for (int mt = 1; mt < 4; ++mt) v = fmaxf(v, fmaxf(sc[mt][e], sc[mt][e + 2]));
+        mb[e] = quadcol_max(v);
+      }
+      float alpha[2], mu[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float m_new = fmaxf(m_run[e], mb[e]);
+        mu[e] = (m_new == -INFINITY) ? 0.f : m_new;
+        alpha[e] = ex2(m_run[e] - mu[e]);
+        m_run[e] = m_new;
+      }
+      if constexpr (STATS) {
+        float es[2] = {0.f, 0.f};
+        const float mtu[2] = {mb[0] == -INFINITY ? 0.f : mb[0], mb[1] == -INFINITY ? 0.f : mb[1]};
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const float ev = ex2(sc[mt][c] - mtu[c & 1]);
+            es[c & 1] += ev;
+            if (p.p_out && col_ok) {
+              __half* po = reinterpret_cast<__half*>(p.p_out) + (hq0 + head0 + (c & 1)) * p.t_pad + t0;
+              po[mt * 16 + (lane >> 2) + (c >> 1) * 8] = __float2half_rn(ev);
+            }
+          }
+        es[0] = quadcol_sum(es[0]);
+        es[1] = quadcol_sum(es[1]);
+        if (lane < 2) {   // lanes 0 and 1 hold heads (0,1) and (2,3)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            p.blk_max[(hq0 + head0 + e) * p.nb + blk] = mb[e] * LN2;
+            p.blk_sum[(hq0 + head0 + e) * p.nb + blk] = es[e];
+          }
+        }
+      }
+      float ls[2] = {0.f, 0.f};
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float pv = ex2(sc[mt][c] - mu[c & 1]);
+          sc[mt][c] = pv;
+          ls[c & 1] += pv;
+        }
+      l_run[0] = l_run[0] * alpha[0] + ls[0];
+      l_run[1] = l_run[1] * alpha[1] + ls[1];
+
+      if constexpr (LOAD_V) {
+        // ---- O^T = alpha * O^T + V^T P^T
+        if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+          for (int mt = 0; mt < 8; ++mt) {
+            acc[mt][0] *= alpha[0]; acc[mt][1] *= alpha[1];
+            acc[mt][2] *= alpha[0]; acc[mt][3] *= alpha[1];
+          }
+        }
+        const uint32_t vbase = kbase + 2 * TC_HALF_BYTES;
+#pragma unroll
+        for (int kt = 0; kt < 4; ++kt) {
+          // P of tokens kt*16..+15 as high + low bf16 parts, transposed into the B layout
+          const uint32_t h0 = pack_bf16(sc[kt][0], sc[kt][1]);
+          const uint32_t h1 = pack_bf16(sc[kt][2], sc[kt][3]);
+          const uint32_t l0 = pack_bf16(sc[kt][0] - bf_lo(h0), sc[kt][1] - bf_hi(h0));
+          const uint32_t l1 = pack_bf16(sc[kt][2] - bf_lo(h1), sc[kt][3] - bf_hi(h1));
+          const uint32_t bh0 = movm_t(h0), bh1 = movm_t(h1), bl0 = movm_t(l0), bl1 = movm_t(l1);
+          const int tok = kt * 16 + (lmat >> 1) * 8 + lrow;
+#pragma unroll
+          for (int mt = 0; mt < 8; ++mt) {
+            const int dchunk = mt * 2 + (lmat & 1);
+            uint32_t a[4];
+            ldsm_x4_t(a, vbase + (dchunk >> 3) * TC_HALF_BYTES + tok * 128 + (((dchunk & 7) ^ lrow) << 4));
+            mma_bf16(acc[mt], a, bh0, bh1);
+            mma_bf16(acc[mt], a, bl0, bl1);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+    }
+    if constexpr (MASKED && STATS) {
+      // an empty list: the first split clears every block of this KV head
+      if (n_items == 0 && split == 0 && warp == 0)
+        for (int gblk = lane; gblk < p.nb; gblk += 32)
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            p.blk_max[(hq0 + g) * p.nb + gblk] = -INFINITY;
+            p.blk_sum[(hq0 + g) * p.nb + gblk] = 0.f;
+          }
+    }
+    l_run[0] = quadcol_sum(l_run[0]);
+    l_run[1] = quadcol_sum(l_run[1]);
+    if (lane < 2) {
+      sM[warp * 4 + head0] = m_run[0];
+      sM[warp * 4 + head0 + 1] = m_run[1];
+      sL[warp * 4 + head0] = l_run[0];
+      sL[warp * 4 + head0 + 1] = l_run[1];
+    }
+  }
+  __syncthreads();   // every block has been consumed: the ring is free for the merge of the warps
+
+  if constexpr (LOAD_V) {
+    float* red = reinterpret_cast<float*>(ring);   // [NC][G][D]
+    if (warp < NC && (lane & 3) < 2) {
+      const int head0 = 2 * (lane & 3);
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          red[(warp * G + head0 + (c & 1)) * D + mt * 16 + (lane >> 2) + (c >> 1) * 8] = acc[mt][c];
+    }
+    __syncthreads();
+    for (int o = tid; o < G * D; o += TC_THREADS) {
+      const int g = o / D, d = o % D;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < NC; ++w) M = fmaxf(M, sM[w * 4 + g]);
+      const float mu = (M == -INFINITY) ? 0.f : M;
+      float sum = 0.f, l = 0.f;
+#pragma unroll
+      for (int w = 0; w < NC; ++w) {
+        const float f = ex2(sM[w * 4 + g] - mu);
+        sum += red[(w * G + g) * D + d] * f;
+        l += sL[w * 4 + g] * f;
+      }
+      const int64_t hq = static_cast<int64_t>(b) * p.Hq + h * G + g;
+      if (p.num_splits == 1) {
+        const float o32 = l > 0.f ? sum / l : 0.f;
+        reinterpret_cast<__nv_bfloat16*>(p.out)[hq * D + d] = __float2bfloat16(o32);
+        if (p.out_f32) p.out_f32[hq * D + d] = o32;
+      } else {
+        p.part_acc[(hq * p.num_splits + split) * D + d] = sum;
+      }
+    }
+  }
+  if (tid < G) {
+    float M = -INFINITY;
+    for (int w = 0; w < NC; ++w) M = fmaxf(M, sM[w * 4 + tid]);
+    const float mu = (M == -INFINITY) ? 0.f : M;
+    float l = 0.f;
+    for (int w = 0; w < NC; ++w) l += sL[w * 4 + tid] * ex2(sM[w * 4 + tid] - mu);
+    const int64_t hq = static_cast<int64_t>(b) * p.Hq + h * G + tid;
+    if (p.num_splits == 1) {
+      if (p.lse) p.lse[hq] = l > 0.f ? (M + log2f(l)) * LN2 : -INFINITY;
+    } else {
+      p.part_ml[(hq * p.num_splits + split) * 2] = M;
+      p.part_ml[(hq * p.num_splits + split) * 2 + 1] = l;
+    }
+  }
+}
+
+}  // namespace kvb

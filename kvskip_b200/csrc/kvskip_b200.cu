@@ -6,7 +6,9 @@
 #include <cuda_runtime.h>
 
 #include <cstdarg>
+#include <atomic>
 #include <cstdio>
+#include <cstring>
 #include <mutex>
 #include <set>
 #include <string>
@@ -14,6 +16,7 @@
 
 #include "common.cuh"
 #include "decode_exact.cuh"
+#include "decode_tc.cuh"
 #include "planner.cuh"
 #include "vskip.cuh"
 
@@ -131,6 +134,43 @@ int launch_exact(const kvskip_params& p, cudaStream_t stream) {
   return KVSKIP_OK;
 }
 
+template <bool MASKED, bool STATS, bool LOAD_V>
+int launch_tc(const kvskip_params& p, cudaStream_t stream) {
+  using Cfg = kvb::TcCfg<LOAD_V>;
+  auto kernel = kvb::decode_tc_kernel<MASKED, STATS, LOAD_V>;
+  if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes)) return rc;
+  kvb::TmaMaps maps;
+  if (int rc = make_kv_map(&maps.k, p.k, p.k_sb, p.k_sh, p.k_st, p.B, p.Hkv, p.T, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  if (LOAD_V) {
+    if (int rc = make_kv_map(&maps.v, p.v, p.v_sb, p.v_sh, p.v_st, p.B, p.Hkv, p.T, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  } else {
+    maps.v = maps.k;
+  }
+  kernel<<<dim3(p.num_splits, p.Hkv, p.B), kvb::TC_THREADS, Cfg::kSmemBytes, stream>>>(p, maps);
+  KVB_CUDA(cudaGetLastError());
+  if (LOAD_V && p.num_splits > 1) {
+    kvb::merge_kernel<128><<<p.B * p.Hq, 128, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits,
+                                                          static_cast<int64_t>(p.B) * p.Hq, true, p.out, p.out_f32,
+                                                          p.lse);
+    KVB_CUDA(cudaGetLastError());
+  }
+  return KVSKIP_OK;
+}
+
+int dispatch_tc(const kvskip_params& p, bool masked, bool stats, bool load_v, cudaStream_t s) {
+  if (!masked && !stats && load_v) return launch_tc<false, false, true>(p, s);
+  if (!masked && stats && load_v) return launch_tc<false, true, true>(p, s);
+  if (!masked && stats && !load_v) return launch_tc<false, true, false>(p, s);
+  if (masked && !stats && load_v) return launch_tc<true, false, true>(p, s);
+  if (masked && stats && load_v) return launch_tc<true, true, true>(p, s);
+  if (masked && stats && !load_v) return launch_tc<true, true, false>(p, s);
+  return fail(KVSKIP_E_ARG, "kvskip: unsupported flag combination (load_v=false needs stats=true)");
+}
+
+std::atomic<int> g_decode_path{0};   // 0 auto (tensor-core path where it exists), 1 exact-order, 2 tensor-core
+
 template <int D>
 int dispatch_exact(const kvskip_params& p, bool masked, bool stats, bool load_v, cudaStream_t s) {
   if (!masked && !stats && load_v) return launch_exact<D, false, false, true>(p, s);
@@ -207,7 +247,25 @@ int kvskip_launch_decode(const kvskip_params* p, int D, int G, int stages, int m
   if (p->num_splits > 1 && (!p->part_ml || (load_v && !p->part_acc)))
     return fail(KVSKIP_E_ARG, "num_splits > 1 needs part_acc / part_ml scratch");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int path = g_decode_path.load(std::memory_order_relaxed);
+  if (D == 128 && path != 1) return dispatch_tc(*p, masked, stats, load_v, s);
+  if (path == 2) return fail(KVSKIP_E_ARG, "the tensor-core path exists for D = 128 only");
   return D == 128 ? dispatch_exact<128>(*p, masked, stats, load_v, s) : dispatch_exact<64>(*p, masked, stats, load_v, s);
+}
+
+int kvskip_set_option(const char* name, int value) {
+  if (!name) return fail(KVSKIP_E_ARG, "null option name");
+  if (!std::strcmp(name, "decode_path")) {
+    if (value < 0 || value > 2) return fail(KVSKIP_E_ARG, "decode_path: 0 auto, 1 exact-order, 2 tensor-core");
+    g_decode_path.store(value, std::memory_order_relaxed);
+    return KVSKIP_OK;
+  }
+  return fail(KVSKIP_E_ARG, "unknown option %s", name);
+}
+
+int kvskip_get_option(const char* name) {
+  if (name && !std::strcmp(name, "decode_path")) return g_decode_path.load(std::memory_order_relaxed);
+  return fail(KVSKIP_E_ARG, "unknown option");
 }
 
 int kvskip_launch_vskip1(const kvskip_params* p, int D, int G, void* stream) {

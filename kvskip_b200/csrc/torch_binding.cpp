@@ -86,9 +86,9 @@ std::vector<at::Tensor> decode(const at::Tensor& q, const at::Tensor& k, const a
   if (load_v) out = at::empty({B, Hq, D}, q.options());
   if (load_v && want_f32) out32 = at::empty({B, Hq, D}, f32);
   at::Tensor lse = at::empty({B, Hq}, f32);
-  if (stats) {
-    bmax = at::full({B, Hq, nb}, -std::numeric_limits<float>::infinity(), f32);
-    bsum = at::zeros({B, Hq, nb}, f32);
+  if (stats) {   // the kernels write every entry themselves (-inf / 0 on blocks a list skips)
+    bmax = at::empty({B, Hq, nb}, f32);
+    bsum = at::empty({B, Hq, nb}, f32);
   }
   if (write_p) pbuf = at::empty({B, Hq, nb * KVSKIP_TILE}, q.options().dtype(at::kHalf));
   if (num_splits > 1) {
@@ -378,6 +378,16 @@ void index_blocks(const at::Tensor& ids, int64_t T, at::Tensor& out) {
                                       cur_stream()));
 }
 
+void set_option(const std::string& name, int64_t value) {
+  raise_on(kvskip_set_option(name.c_str(), static_cast<int>(value)));
+}
+
+int64_t get_option(const std::string& name) {
+  const int v = kvskip_get_option(name.c_str());
+  TORCH_CHECK(v >= 0, kvskip_last_error());
+  return v;
+}
+
 int64_t device_status() {
   unsigned int st = 0;
   raise_on(kvskip_device_status(cur_stream(), &st));
@@ -410,5 +420,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("block_cnt"), py::arg("num_splits") = 1, py::arg("want_f32") = false);
   m.def("merge", &merge, "merge of R partial (max, sum, acc) rows", py::arg("part_acc"), py::arg("part_ml"));
   m.def("index_blocks", &index_blocks, "token-index blocks of one step", py::arg("ids"), py::arg("T"), py::arg("out"));
+  m.def("set_option", &set_option, "process-wide option, e.g. (\"decode_path\", 1) for the exact-order kernels",
+        py::arg("name"), py::arg("value"));
+  m.def("get_option", &get_option, py::arg("name"));
   m.def("device_status", &device_status, "synchronise and return the kernels' status word (0 = fine)");
 }

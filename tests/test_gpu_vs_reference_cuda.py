@@ -31,6 +31,14 @@ def libs():
     return CAbi(), CAbi(REF_SO, prefix="kvref")
 
 
+@pytest.fixture(autouse=True)
+def exact_path():
+    """Bit-level parity is a property of the exact-order kernels."""
+    K.ext().set_option("decode_path", 1)
+    yield
+    K.ext().set_option("decode_path", 0)
+
+
 class AbiOps:
     """RefreshLayer backend over a CAbi instance (ours or the reference's)."""
 
@@ -126,3 +134,45 @@ def test_planner_loop_bits(libs, name):
         assert torch.equal(la.read_mask(nb), lb.read_mask(nb)), f"block list differs at step {t}"
         trig_total += int(la.state["trig"].sum())
     assert 0 < trig_total < steps * B * 8 * 0.6      # the case exercises both kinds of steps
+
+
+def _time_us(fn, iters=20):
+    for _ in range(3):
+        fn()
+    st = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    en = [torch.cuda.Event(enable_timing=True) for _ in range(iters)]
+    for i in range(iters):
+        st[i].record()
+        fn()
+        en[i].record()
+    torch.cuda.synchronize()
+    return sorted(s.elapsed_time(e) * 1e3 for s, e in zip(st, en))[iters // 2]
+
+
+def test_not_slower_than_reference_kernels(libs):
+    """The kernel to beat: the reference's own source compiled for sm_100a, same GPU, same inputs
+    (larger than L2), same split count.  Writes the numbers next to the other run artefacts."""
+    import json
+    mine, ref = libs
+    K.ext().set_option("decode_path", 0)
+    rows = []
+    for B, T in ((1, 65536), (4, 65536), (16, 32768)):
+        g = torch.Generator(device=DEV).manual_seed(B)
+        q = (torch.randn(B, 32, 128, device=DEV, generator=g) / 11.3).to(torch.bfloat16)
+        k = torch.randn(B, 8, T, 128, device=DEV, generator=g).to(torch.bfloat16)
+        v = torch.randn(B, 8, T, 128, device=DEV, generator=g).to(torch.bfloat16)
+        ns = K.num_splits_for(B * 8, T // 64, sms=148)
+        keep = torch.rand(B, 8, T // 64, device=DEV, generator=g) < 0.5
+        bi, bc = synth.keep_to_plan(keep.cpu())
+        bi, bc = bi.to(DEV), bc.to(DEV)
+        for name, kw, frac in (("dense", {}, 1.0), ("masked+stats", dict(block_idx=bi, block_cnt=bc, stats=True),
+                                                  float(keep.float().mean()))):
+            t_ref = _time_us(lambda: ref.decode(q, k, v, 0.088, num_splits=ns, **kw))
+            t_our = _time_us(lambda: mine.decode(q, k, v, 0.088, num_splits=ns, **kw))
+            gb = 2 * B * 8 * T * 128 * 2 * frac / 1e9
+            rows.append(dict(case=f"{name} B={B} T={T}", splits=ns, ref_us=round(t_ref, 1), ours_us=round(t_our, 1),
+                             ref_GBps=round(gb / t_ref * 1e6, 1), ours_GBps=round(gb / t_our * 1e6, 1)))
+            assert t_our <= t_ref * 1.05, rows[-1]
+    out = Path(__file__).resolve().parent.parent / "gpurun_out"
+    if out.is_dir():
+        (out / "ours_vs_reference_kernels.json").write_text(json.dumps(rows, indent=1))
