@@ -11,7 +11,7 @@
 // Structure of one CTA (one (split, kv head, batch) triple, all 4 query heads of the KV head):
 //   * warp TC_CONSUMERS is the producer: one lane walks the CTA's block range (or its slice of the
 //     block list) and issues, per block, four tiled TMA loads (K and V, two 64-dim halves each,
-//     128-byte swizzle so ldmatrix is bank-conflict free) into a 6-stage ring; every stage has a
+//     128-byte swizzle so ldmatrix is bank-conflict free) into a 6-stage ring (one stage per consumer warp); every stage has a
 //     `full` mbarrier completed by the copy engine's byte count and an `empty` mbarrier the
 //     consuming warp arrives on.
 //   * warps 0..TC_CONSUMERS-1 are consumers.  A consumer owns whole blocks (block i of the range
@@ -31,7 +31,10 @@
 
 namespace kvb {
 
-constexpr int TC_CONSUMERS = 8;
+// Consumer warps.  The stage count of every configuration is a multiple of this, so all uses of a
+// stage are consumed by the same warp: an mbarrier wait names a phase by its parity only, and a
+// warp that never saw the previous use of a stage could otherwise pass a wait for the next one.
+constexpr int TC_CONSUMERS = 6;
 constexpr int TC_THREADS = (TC_CONSUMERS + 1) * 32;
 constexpr int TC_HALF_BYTES = TILE * 64 * 2;        // one TMA box: 64 tokens x 64 dims bf16 = 8 KB
 
@@ -41,6 +44,7 @@ struct TcCfg {
   static constexpr int kStages = LOAD_V ? 6 : 12;
   static constexpr int kRedBytes = TC_CONSUMERS * 4 * 128 * 4;     // epilogue staging, aliases the ring
   static constexpr int kAuxBytes = TC_CONSUMERS * 8 * 4 + 2 * kStages * 8;
+  static_assert(kStages % TC_CONSUMERS == 0, "a stage must always be consumed by the same warp");
   static constexpr int kSmemBytes = kStages * kStageBytes + kAuxBytes + 1024 /* alignment slack */;
 };
 
