@@ -133,6 +133,27 @@ typedef struct kvskip_update_params {
 int kvskip_launch_decode(const kvskip_params* p, int D, int G, int stages, int masked, int stats, int load_v,
                          void* stream);
 
+/* The same launch for callers that cannot allocate device memory when they call: a serving
+ * engine that hands out all of its memory at start-up and treats a later cudaMalloc as a bug, a
+ * latency-critical loop that cannot afford the implicit synchronisation of an allocation, or a
+ * plugin interface that only passes input and output buffers.  No counterpart in the reference,
+ * whose binding allocates split scratch on every call.
+ * Takes the same arguments as kvskip_launch_decode; p->part_acc and p->part_ml are ignored.
+ * When num_splits > 1 the split partials go to an array built into the library (one per device
+ * that loads it, held until exit) instead of caller scratch:
+ *   - limit: B*Hq*num_splits*(D+2) <= KVSKIP_NOALLOC_MAX_FLOATS (4 MiB of floats), else
+ *     KVSKIP_E_LIMIT with a message saying so;
+ *   - the first call on a device looks the array's address up (cudaGetSymbolAddress, with that
+ *     device current) and opts the kernel into its shared-memory size; make that first call
+ *     before starting any stream capture;
+ *   - all calls on a device share the array: two calls whose kernels overlap on the GPU (different
+ *     streams) race on it; calls on one stream are ordered and safe.  The array keeps the last
+ *     call's contents and nothing in it needs clearing.
+ * Calls no cudaMalloc / cudaFree and no allocating library routine. */
+#define KVSKIP_NOALLOC_MAX_FLOATS (1 << 20)
+int kvskip_launch_decode_noalloc(const kvskip_params* p, int D, int G, int stages, int masked, int stats,
+                                 int load_v, void* stream);
+
 /* Single-pass V-skip.  Replaces kvskip::launch_vskip1 (kernels/kvskip.h:118;
  * kernels/kvskip_kernel.cu:747-752). */
 int kvskip_launch_vskip1(const kvskip_params* p, int D, int G, void* stream);

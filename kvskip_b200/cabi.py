@@ -83,6 +83,22 @@ class CAbi:
         p.v_sb, p.v_sh, p.v_st = v.stride(0), v.stride(1), v.stride(2)
         p.B, p.Hq, p.Hkv, p.T = q.shape[0], q.shape[1], k.shape[1], k.shape[2]
 
+    def decode_noalloc(self, q, k, v, scale, out, lse, block_idx=None, block_cnt=None, num_splits=1, out_f32=None):
+        """kvskip_launch_decode_noalloc: the caller passes every buffer (out bf16 [B,Hq,D], lse fp32
+        [B,Hq], optional out_f32); nothing is allocated here or in the library, the split
+        partials live in the library's built-in array."""
+        B, Hq, D = q.shape
+        Hkv, T = k.shape[1], k.shape[2]
+        p = Params()
+        self._qkv(p, q, k, v)
+        p.scale_log2 = scale * 1.4426950408889634
+        if block_idx is not None:
+            p.block_idx, p.block_cnt, p.max_blocks = _ptr(block_idx), _ptr(block_cnt), block_idx.shape[2]
+        p.num_splits = num_splits
+        p.out, p.out_f32, p.lse = _ptr(out), _ptr(out_f32), _ptr(lse)
+        p.nb, p.t_pad = math.ceil(T / TILE), math.ceil(T / TILE) * TILE
+        self._call("decode_noalloc", C.byref(p), D, Hq // Hkv, 2, int(block_idx is not None), 0, 1, _stream())
+
     def decode(self, q, k, v, scale, block_idx=None, block_cnt=None, stats=False, load_v=True, num_splits=1,
                stages=2, want_f32=False, write_p=False):
         """Same arguments and return list as the extension's decode()."""

@@ -253,6 +253,58 @@ int kvskip_launch_decode(const kvskip_params* p, int D, int G, int stages, int m
   return D == 128 ? dispatch_exact<128>(*p, masked, stats, load_v, s) : dispatch_exact<64>(*p, masked, stats, load_v, s);
 }
 
+// ---- split-K decode for callers that cannot allocate device memory -------------------------
+// The split scratch of this entry point: one array per device that loads the library, held
+// until the process exits.  Partials of every (row, split) are fully rewritten by each call, so
+// nothing in it has to start at zero; it keeps the last call's contents.
+static __device__ __align__(256) float g_noalloc_scratch[KVSKIP_NOALLOC_MAX_FLOATS];
+
+namespace {
+// device address of g_noalloc_scratch per device ordinal, looked up once with that device current
+// (in host code the array's name is only a handle for the runtime, not a device address)
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mu;
+
+int noalloc_scratch(float** out) {
+  int dev = 0;
+  KVB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(KVSKIP_E_LIMIT, "device ordinal %d beyond %d", dev, kMaxDevices);
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (!g_noalloc_ptr[dev]) {
+    void* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess || !ptr)
+      return fail(KVSKIP_E_CUDA, "cudaGetSymbolAddress(g_noalloc_scratch): %s", cudaGetErrorString(e));
+    g_noalloc_ptr[dev] = static_cast<float*>(ptr);
+  }
+  *out = g_noalloc_ptr[dev];
+  return KVSKIP_OK;
+}
+}  // namespace
+
+int kvskip_launch_decode_noalloc(const kvskip_params* p, int D, int G, int stages, int masked, int stats, int load_v,
+                                 void* stream) {
+  if (int rc = check_common(p, D, G)) return rc;
+  kvskip_params q = *p;
+  q.part_acc = nullptr;
+  q.part_ml = nullptr;
+  if (q.num_splits > 1) {
+    const int64_t rows = static_cast<int64_t>(q.B) * q.Hq * q.num_splits;
+    const int64_t need = rows * (D + 2);
+    if (need > static_cast<int64_t>(KVSKIP_NOALLOC_MAX_FLOATS))
+      return fail(KVSKIP_E_LIMIT,
+                  "kvskip_launch_decode_noalloc: B*Hq*num_splits*(D+2) = %lld floats of split scratch exceed the "
+                  "built-in %lld; use fewer splits or kvskip_launch_decode with caller scratch",
+                  static_cast<long long>(need), static_cast<long long>(KVSKIP_NOALLOC_MAX_FLOATS));
+    float* base = nullptr;
+    if (int rc = noalloc_scratch(&base)) return rc;
+    q.part_acc = base;                 // [B,Hq,S,D]
+    q.part_ml = base + rows * D;       // [B,Hq,S,2]
+  }
+  return kvskip_launch_decode(&q, D, G, stages, masked, stats, load_v, stream);
+}
+
 int kvskip_set_option(const char* name, int value) {
   if (!name) return fail(KVSKIP_E_ARG, "null option name");
   if (!std::strcmp(name, "decode_path")) {
