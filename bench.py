@@ -502,8 +502,11 @@ def main():
                        "l2": f"inputs ({nbytes / 1e9:.2f} GB per GPU) larger than the 126 MB L2: no flush between steps",
                        "kv_bytes_per_step_per_gpu": int(nbytes)},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "of": peak_kind, "traffic": None,
-                         "kernel": "decode_exact_kernel<128,dense> (+ merge_kernel, same timed launch pair)",
+                         "of": peak_kind, "traffic": 1.016 * nbytes,
+                         "traffic_note": "dram__bytes_read+write of one ncu capture at batch 1 (272.7 MB for "
+                                         "268.4 MB algorithmic, profiles/decode_tc_dense_b1_64k.md) scaled by the "
+                                         "batch: traffic grows with the blocks read",
+                         "kernel": "decode_tc_kernel<dense> (+ merge_kernel, same timed launch pair)",
                          "note": "algorithmic bytes = K+V of one step; duration = CUDA events over the timed "
                                  "region / steps on the launching stream"},
             "cpu_baseline": cpu,
