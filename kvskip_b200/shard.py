@@ -53,11 +53,23 @@ def block_range(nb: int, rank: int, world: int):
     return lo, min(nb, lo + per)
 
 
-def local_partial(q, k_local, v_local, scale, plan=None, num_splits=None):
+class CudaBackend:
+    """The product backend: the compiled extension (there is no CPU path in this package; tests of
+    the host logic pass a stand-in with the same two callables)."""
+
+    def decode(self, q, k, v, scale, plan=None, num_splits=None):
+        return K.decode(q, k, v, scale, plan=plan, num_splits=num_splits, out_f32=True)
+
+    def merge(self, acc, ml):
+        return K.ext().merge(acc, ml)
+
+
+def local_partial(q, k_local, v_local, scale, plan=None, num_splits=None, backend=None):
     """Attention over this rank's part of the sequence as a packed (acc, m, l) triple:
     fp32 [B*Hq, D+2] with acc = normalised local output, m = local lse in log2 units, l = 1
     (l = 0 and m = -inf when the rank read nothing)."""
-    r = K.decode(q, k_local, v_local, scale, plan=plan, num_splits=num_splits, out_f32=True)
+    backend = backend or CudaBackend()
+    r = backend.decode(q, k_local, v_local, scale, plan=plan, num_splits=num_splits)
     B, Hq, D = r["out_f32"].shape
     lse = r["lse"].reshape(B * Hq, 1)
     empty = torch.isinf(lse)
@@ -66,27 +78,27 @@ def local_partial(q, k_local, v_local, scale, plan=None, num_splits=None):
     return torch.cat([r["out_f32"].reshape(B * Hq, D), m, l], dim=-1).contiguous()
 
 
-def merge_partials(parts: torch.Tensor, B: int, Hq: int):
+def merge_partials(parts: torch.Tensor, B: int, Hq: int, backend=None):
     """parts fp32 [R, B*Hq, D+2] -> dict(out bf16 [B,Hq,D], out_f32, lse [B,Hq]) with the split
     merge, ranks in ascending order."""
     R, N, W = parts.shape
     D = W - 2
     acc = parts[..., :D].contiguous()
     ml = parts[..., D:].contiguous()
-    out, o32, lse = K.ext().merge(acc, ml)
+    out, o32, lse = (backend or CudaBackend()).merge(acc, ml)
     return {"out": out.view(B, Hq, D), "out_f32": o32.view(B, Hq, D), "lse": lse.view(B, Hq)}
 
 
-def decode_sequence_sharded(q, k_local, v_local, scale, plan=None, group=None, num_splits=None):
+def decode_sequence_sharded(q, k_local, v_local, scale, plan=None, group=None, num_splits=None, backend=None):
     """One decode step with the sequence split over the ranks of `group`.  k_local / v_local
     hold this rank's block range; `plan` (optional) lists local block indices.  Every rank
     returns the full result."""
     B, Hq = q.shape[0], q.shape[1]
-    part = local_partial(q, k_local, v_local, scale, plan=plan, num_splits=num_splits)
+    part = local_partial(q, k_local, v_local, scale, plan=plan, num_splits=num_splits, backend=backend)
     world = dist.get_world_size(group)
-    parts = torch.empty(world, *part.shape, dtype=part.dtype, device=part.device)
-    dist.all_gather_into_tensor(parts, part, group=group)
-    return merge_partials(parts, B, Hq)
+    parts = torch.empty(world * part.shape[0], part.shape[1], dtype=part.dtype, device=part.device)
+    dist.all_gather_into_tensor(parts, part, group=group)       # rank-major concatenation
+    return merge_partials(parts.view(world, *part.shape), B, Hq, backend=backend)
 
 
 def shard_plan(keep: torch.Tensor, rank: int, world: int):

@@ -425,3 +425,32 @@ def test_full_size_64k_dense_and_masked():
 
 def test_no_wait_timed_out():
     assert K.ext().device_status() == 0
+
+
+@pytest.mark.parametrize("R", [2, 8])
+def test_sequence_shards_emulated_on_one_gpu(R):
+    """The sequence-sharded path with the ranks emulated on one GPU: every shard's local pass, the
+    (acc, m, l) triples stacked as an all-gather would deliver them, one merge.  Against the CPU
+    oracle on the whole sequence and against the unsharded kernel."""
+    from kvskip_b200 import shard
+    q, k, v, scale, keep = synth.sink_body_case(13, T=8192 + 100, B=2)
+    qc, kc, vc = cuda(q, k, v)
+    nb = keep.shape[-1]
+    parts, partsm = [], []
+    for r in range(R):
+        lo, hi = shard.block_range(nb, r, R)
+        kl, vl = kc[:, :, lo * 64:hi * 64], vc[:, :, lo * 64:hi * 64]
+        parts.append(shard.local_partial(qc, kl, vl, scale))
+        lk = shard.shard_plan(keep, r, R).to(DEV)
+        partsm.append(shard.local_partial(qc, kl, vl, scale, plan=K.make_plan(lk)))
+    got = shard.merge_partials(torch.stack(parts), 2, 32)
+    gotm = shard.merge_partials(torch.stack(partsm), 2, 32)
+    ref = oracle.decode_f64(q, k, v, scale)
+    bi, bc = synth.keep_to_plan(keep)
+    refm = oracle.decode_f64(q, k, v, scale, bi, bc)
+    assert rel_err(got["out"], ref["out"]) < TOL_BF16 and rel_err(got["out_f32"], ref["out"]) < TOL_F32
+    assert rel_err(gotm["out"], refm["out"]) < TOL_BF16 and rel_err(gotm["out_f32"], refm["out"]) < TOL_F32
+    assert torch.allclose(got["lse"].double().cpu(), ref["lse"], rtol=0, atol=2e-4)
+    assert torch.allclose(gotm["lse"].double().cpu(), refm["lse"], rtol=0, atol=2e-4)
+    one = K.decode(qc, kc, vc, scale, out_f32=True)
+    assert rel_err(got["out_f32"], one["out_f32"].double().cpu()) < 2e-5
