@@ -209,46 +209,52 @@ def single_gpu_cases(dev, peak):
         time_cuda(lambda: K.vskip_one_pass(q, k, v, scale, tau=1e-4, lse_prev=lse), 30, flush),
         kv_bytes(1, T_HEAD, 0.5 * (1 + vk)), v_kept=round(vk, 4), bytes="all K + V of voted blocks")
     del q, k, v
-    # planner loop: 32 layers, 32k context, 128 steps of plan -> masked+stats -> update
-    L, T0, steps = 32, 32768, 128
-    walks = [synth.planner_walk_device(100 + l, T0, steps, dev) for l in range(L)]
-    ids = synth.token_ids_with_repeats(99, 1, T0 + steps).to(dev)
-    nbm = math.ceil((T0 + steps) / 64)
+    # planner loops: plan -> masked+stats attention -> update per layer and step, no host sync
     cfg = RefreshConfig(calib=0.05, calib_warm=(32, 8), calib_kind="peak", calib_auto_ix=0.1)
 
-    def run(count):
-        layers = [RefreshLayer(cfg) for _ in range(L)]
-        idx = torch.zeros(1, nbm + cfg.margin, dtype=torch.uint8, device=dev)
-        read = torch.zeros((), dtype=torch.int64, device=dev)
-        total = 0
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-        for t in range(steps):
-            if t == 8:
-                ev[0].record()
-            T = T0 + t + 1
-            K.ext().index_blocks(ids, T, idx)
-            for l in range(L):
-                w = walks[l]
-                if l == 0:      # layer 0 is always dense
-                    K.decode(w.q[t], w.k[:, :, :T], w.v[:, :, :T], w.scale)
-                    continue
-                layers[l].step(w.q[t], w.k[:, :, :T], w.v[:, :, :T], w.scale, idx)
-                if count and t >= 8:
-                    read += layers[l].state["block_cnt"].sum()
-                    total += HKV * math.ceil(T / 64)
-        ev[1].record()
-        torch.cuda.synchronize()
-        return ev[0].elapsed_time(ev[1]) * 1e3 / ((steps - 8) * L), (int(read), total)
+    def planner_case(L, B, T0, steps, skip, label):
+        walks = [synth.planner_walk_device(100 + l, T0, steps, dev, B=B) for l in range(L)]
+        ids = synth.token_ids_with_repeats(99, B, T0 + steps).to(dev)
 
-    us, _ = run(False)
-    _, (read, total) = run(True)
-    frac = read / max(1, total)
-    nbytes = kv_bytes(1, T0 + steps // 2, frac)
-    cases.append({"case": "planner loop: 32 layers x 128 steps, 32k context, layer 0 dense, peak calibration, auto index",
-                  "us": round(us, 2), "blocks_read": round(frac, 4), "GBps": round(nbytes / (us * 1e-6) / 1e9, 1),
-                  "frac_of_peak": round(nbytes / (us * 1e-6) / 1e9 / peak, 4),
-                  "note": "mean per layer-step over steps 8..127, launches issued from Python, no host sync; "
-                          "bytes = K+V of the blocks read by the planner layers"})
+        def run(count):
+            layers = [RefreshLayer(cfg) for _ in range(L)]
+            idx = torch.zeros(B, math.ceil((T0 + 1) / 64) + cfg.margin, dtype=torch.uint8, device=dev)  # the layers' NBC
+            read = torch.zeros((), dtype=torch.int64, device=dev)
+            total = 0
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            for t in range(steps):
+                if t == skip:
+                    ev[0].record()
+                T = T0 + t + 1
+                K.ext().index_blocks(ids, T, idx)
+                for l in range(L):
+                    w = walks[l]
+                    if l == 0:      # layer 0 is always dense
+                        K.decode(w.q[t], w.k[:, :, :T], w.v[:, :, :T], w.scale)
+                        continue
+                    layers[l].step(w.q[t], w.k[:, :, :T], w.v[:, :, :T], w.scale, idx)
+                    if count and t >= skip:
+                        read += layers[l].state["block_cnt"].sum()
+                        total += B * HKV * math.ceil(T / 64)
+            ev[1].record()
+            torch.cuda.synchronize()
+            return ev[0].elapsed_time(ev[1]) * 1e3 / ((steps - skip) * L), (int(read), total)
+
+        us, _ = run(False)
+        _, (read, total) = run(True)
+        frac = read / max(1, total)
+        # bytes actually read per layer-step, averaged over the L layers (layer 0 reads everything)
+        nbytes = kv_bytes(B, T0 + steps // 2, (frac * (L - 1) + 1.0) / L)
+        cases.append({"case": label, "us": round(us, 2), "blocks_read_planner_layers": round(frac, 4),
+                      "GBps": round(nbytes / (us * 1e-6) / 1e9, 1),
+                      "frac_of_peak": round(nbytes / (us * 1e-6) / 1e9 / peak, 4),
+                      "note": f"mean per layer-step over steps {skip}..{steps - 1}; one extension call per layer-step "
+                              "(3 launches), issued from Python, no host sync; bytes = K+V of the blocks read"})
+
+    planner_case(32, 1, 32768, 128, 8, "planner loop: 32 layers x 128 steps, batch 1, 32k context, layer 0 dense, "
+                                       "peak calibration, auto index")
+    planner_case(8, 8, 32768, 64, 8, "planner loop: 8 layers x 64 steps, batch 8, 32k context")
+    planner_case(4, 8, 65536, 48, 8, "planner loop: 4 layers x 48 steps, batch 8, 64k context")
     return cases
 
 
@@ -506,7 +512,7 @@ def main():
                          "traffic_note": "dram__bytes_read+write of one ncu capture at batch 1 (272.7 MB for "
                                          "268.4 MB algorithmic, profiles/decode_tc_dense_b1_64k.md) scaled by the "
                                          "batch: traffic grows with the blocks read",
-                         "kernel": "decode_tc_kernel<dense> (+ merge_kernel, same timed launch pair)",
+                         "kernel": "decode_tc_kernel<dense> (split merge inside the kernel)",
                          "note": "algorithmic bytes = K+V of one step; duration = CUDA events over the timed "
                                  "region / steps on the launching stream"},
             "cpu_baseline": cpu,
@@ -514,7 +520,7 @@ def main():
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "note": "q and the new token's K/V rows from pinned host memory, output back to pinned host "
                             "memory, host sync every step; the KV cache is resident state"},
-            "gpu_launches": args.steps * (2 if nsplit > 1 else 1),
+            "gpu_launches": args.steps,   # one decode kernel per step; the split merge runs inside it
             "clocks": clocks,
             "cases": cases,
         }

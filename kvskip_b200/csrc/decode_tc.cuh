@@ -87,7 +87,7 @@ __device__ __forceinline__ float quadcol_sum(float v) {
 
 template <bool MASKED, bool STATS, bool LOAD_V>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps) {
+decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* __restrict__ split_done) {
   using Cfg = TcCfg<LOAD_V>;
   constexpr int G = 4, D = 128;
   constexpr int S = Cfg::kStages;
@@ -373,6 +373,42 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps) {
     } else {
       p.part_ml[(hq * p.num_splits + split) * 2] = M;
       p.part_ml[(hq * p.num_splits + split) * 2 + 1] = l;
+    }
+  }
+
+  // ---- split merge by the last CTA of this (batch, kv head) to finish: same arithmetic and the
+  // same ascending-split order as merge_kernel, without a second launch.  split_done[] counts the
+  // finished splits and is put back to zero by the CTA that merges.
+  if constexpr (LOAD_V) {
+    if (p.num_splits > 1 && split_done != nullptr) {
+      __shared__ int s_last;
+      __threadfence();            // this CTA's partials are visible device-wide before it is counted
+      __syncthreads();
+      if (tid == 0) s_last = atomicAdd(&split_done[b * p.Hkv + h], 1) == p.num_splits - 1;
+      __syncthreads();
+      if (s_last) {
+        __threadfence();
+        const int S2 = p.num_splits;
+        for (int o = tid; o < G * D; o += TC_THREADS) {
+          const int g = o / D, d = o % D;
+          const int64_t hq = static_cast<int64_t>(b) * p.Hq + h * G + g;
+          const float* ml = p.part_ml + hq * S2 * 2;
+          float m = -INFINITY;
+          for (int s2 = 0; s2 < S2; ++s2) m = fmaxf(m, __ldcg(ml + 2 * s2));
+          const float mu = (m == -INFINITY) ? 0.f : m;
+          float l = 0.f, a = 0.f;
+          for (int s2 = 0; s2 < S2; ++s2) {
+            const float w = ex2(__ldcg(ml + 2 * s2) - mu);
+            l += __ldcg(ml + 2 * s2 + 1) * w;
+            a += __ldcg(p.part_acc + (hq * S2 + s2) * D + d) * w;
+          }
+          const float o32 = l > 0.f ? a / l : 0.f;
+          reinterpret_cast<__nv_bfloat16*>(p.out)[hq * D + d] = __float2bfloat16(o32);
+          if (p.out_f32) p.out_f32[hq * D + d] = o32;
+          if (d == 0 && p.lse) p.lse[hq] = l > 0.f ? (m + log2f(l)) * LN2 : -INFINITY;
+        }
+        if (tid == 0) split_done[b * p.Hkv + h] = 0;
+      }
     }
   }
 }

@@ -19,6 +19,7 @@
 #include "decode_tc.cuh"
 #include "planner.cuh"
 #include "vskip.cuh"
+#include "vskip_tc.cuh"
 
 namespace {
 
@@ -134,6 +135,34 @@ int launch_exact(const kvskip_params& p, cudaStream_t stream) {
   return KVSKIP_OK;
 }
 
+// Counters of finished splits for the in-kernel merge: zero at load, put back to zero by the CTA
+// that merges.  Sixteen regions used round-robin by successive launches, so launches that overlap
+// on different streams do not share counters.
+constexpr int kMergeRegion = 4096;
+constexpr int kMergeRegions = 16;
+__device__ int g_split_done[kMergeRegion * kMergeRegions];
+std::atomic<unsigned> g_merge_seq{0};
+
+int split_done_region(int units, int** out) {
+  static std::mutex mu;
+  static int* base[64] = {};
+  *out = nullptr;
+  if (units > kMergeRegion) return KVSKIP_OK;          // too many (batch, head) pairs: separate merge launch
+  int dev = 0;
+  KVB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return KVSKIP_OK;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!base[dev]) {
+      void* ptr = nullptr;
+      KVB_CUDA(cudaGetSymbolAddress(&ptr, g_split_done));
+      base[dev] = static_cast<int*>(ptr);
+    }
+  }
+  *out = base[dev] + (g_merge_seq.fetch_add(1, std::memory_order_relaxed) % kMergeRegions) * kMergeRegion;
+  return KVSKIP_OK;
+}
+
 template <bool MASKED, bool STATS, bool LOAD_V>
 int launch_tc(const kvskip_params& p, cudaStream_t stream) {
   using Cfg = kvb::TcCfg<LOAD_V>;
@@ -148,9 +177,12 @@ int launch_tc(const kvskip_params& p, cudaStream_t stream) {
   } else {
     maps.v = maps.k;
   }
-  kernel<<<dim3(p.num_splits, p.Hkv, p.B), kvb::TC_THREADS, Cfg::kSmemBytes, stream>>>(p, maps);
+  int* done = nullptr;
+  if (LOAD_V && p.num_splits > 1)
+    if (int rc = split_done_region(p.B * p.Hkv, &done)) return rc;
+  kernel<<<dim3(p.num_splits, p.Hkv, p.B), kvb::TC_THREADS, Cfg::kSmemBytes, stream>>>(p, maps, done);
   KVB_CUDA(cudaGetLastError());
-  if (LOAD_V && p.num_splits > 1) {
+  if (LOAD_V && p.num_splits > 1 && done == nullptr) {
     kvb::merge_kernel<128><<<p.B * p.Hq, 128, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits,
                                                           static_cast<int64_t>(p.B) * p.Hq, true, p.out, p.out_f32,
                                                           p.lse);
@@ -198,6 +230,28 @@ int launch_vskip1_t(const kvskip_params& p, cudaStream_t stream) {
     kvb::merge_kernel<D><<<p.B * p.Hq, D, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits,
                                                         static_cast<int64_t>(p.B) * p.Hq, true, p.out, p.out_f32,
                                                         p.lse);
+    KVB_CUDA(cudaGetLastError());
+  }
+  return KVSKIP_OK;
+}
+
+int launch_vskip1_tc(const kvskip_params& p, cudaStream_t stream) {
+  auto kernel = kvb::vskip1_tc_kernel;
+  if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), kvb::Vs1TcCfg::kSmemBytes)) return rc;
+  kvb::TmaMaps maps;
+  if (int rc = make_kv_map(&maps.k, p.k, p.k_sb, p.k_sh, p.k_st, p.B, p.Hkv, p.T, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  if (int rc = make_kv_map(&maps.v, p.v, p.v_sb, p.v_sh, p.v_st, p.B, p.Hkv, p.T, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  int* done = nullptr;
+  if (p.num_splits > 1)
+    if (int rc = split_done_region(p.B * p.Hkv, &done)) return rc;
+  kernel<<<dim3(p.num_splits, p.Hkv, p.B), kvb::TC_THREADS, kvb::Vs1TcCfg::kSmemBytes, stream>>>(p, maps, done);
+  KVB_CUDA(cudaGetLastError());
+  if (p.num_splits > 1 && done == nullptr) {
+    kvb::merge_kernel<128><<<p.B * p.Hq, 128, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits,
+                                                          static_cast<int64_t>(p.B) * p.Hq, true, p.out, p.out_f32,
+                                                          p.lse);
     KVB_CUDA(cudaGetLastError());
   }
   return KVSKIP_OK;
@@ -325,6 +379,7 @@ int kvskip_launch_vskip1(const kvskip_params* p, int D, int G, void* stream) {
   if (!p->out || !p->lse) return fail(KVSKIP_E_ARG, "out and lse are required");
   if (p->num_splits > 1 && (!p->part_ml || !p->part_acc)) return fail(KVSKIP_E_ARG, "num_splits > 1 needs scratch");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (D == 128 && g_decode_path.load(std::memory_order_relaxed) != 1) return launch_vskip1_tc(*p, s);
   return D == 128 ? launch_vskip1_t<128>(*p, s) : launch_vskip1_t<64>(*p, s);
 }
 
@@ -344,11 +399,12 @@ int kvskip_launch_plan(const kvskip_plan_params* p, void* stream) {
   if (nb > p->NBC) return fail(KVSKIP_E_ARG, "block capacity exceeded");
   if (((p->flags == nullptr)) || !p->csum || !p->keep || !p->block_idx || !p->block_cnt || !p->trig || !p->cs_now)
     return fail(KVSKIP_E_ARG, "plan: missing state tensor");
-  const int smem = kvb::PL_G * nb * static_cast<int>(sizeof(float));
-  if (smem > 220 * 1024) return fail(KVSKIP_E_LIMIT, "plan: more than %d blocks", 220 * 1024 / 16);
-  if (smem > 48 * 1024)
-    if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::plan_kernel), 220 * 1024)) return rc;
-  kvb::plan_kernel<<<dim3(p->Hkv, p->B), kvb::PL_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(*p);
+  if (p->B > 65535 || p->Hkv > 65535) return fail(KVSKIP_E_LIMIT, "B and Hkv are grid dims: at most 65535");
+  int* done = nullptr;
+  if (int rc = split_done_region(p->B * p->Hkv, &done)) return rc;
+  if (!done) return fail(KVSKIP_E_LIMIT, "plan: more than %d (batch, kv head) pairs per call", kMergeRegion);
+  const int chunks = (nb + kvb::PL_CHUNK - 1) / kvb::PL_CHUNK;
+  kvb::plan_kernel<<<dim3(chunks, p->Hkv, p->B), kvb::PL_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(*p, done);
   KVB_CUDA(cudaGetLastError());
   return KVSKIP_OK;
 }
@@ -407,9 +463,12 @@ int kvskip_device_status(void* stream, unsigned int* status) {
   if (!status) return fail(KVSKIP_E_ARG, "null status pointer");
   KVB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   KVB_CUDA(cudaMemcpyFromSymbol(status, kvb::g_status, sizeof(unsigned int)));
-  if (*status) {
+  if (*status) {   // a kernel gave up mid-way: clear the word and the split counters it may have left
     const unsigned int zero = 0;
     KVB_CUDA(cudaMemcpyToSymbol(kvb::g_status, &zero, sizeof(zero)));
+    void* ptr = nullptr;
+    KVB_CUDA(cudaGetSymbolAddress(&ptr, g_split_done));
+    KVB_CUDA(cudaMemset(ptr, 0, sizeof(int) * kMergeRegion * kMergeRegions));
   }
   return KVSKIP_OK;
 }

@@ -65,21 +65,28 @@ __device__ __forceinline__ void pl_compact(int nb, int* bi, int* cnt, int* scan,
   if (tid == PL_THREADS - 1) *cnt = scan[PL_THREADS - 1];
 }
 
-__global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_params p) {
-  const int h = blockIdx.x, b = blockIdx.y;
+constexpr int PL_CHUNK = 32;   // blocks whose centroid scores one CTA computes (4 warps x 8 in flight)
+
+// grid (ceil(nb / PL_CHUNK), Hkv, B).  Every CTA computes the centroid scores of its chunk of
+// blocks and stores them to cs_now; the last CTA of a (batch, kv head) to finish (counted in
+// done[], which it puts back to zero) folds the estimate, decides and writes the block list.
+// The arithmetic of a score and of the fold is unchanged, only spread over more SMs: one CTA per
+// head reading nb * 512 bytes of key sums is latency-bound at long contexts.
+__global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_params p, int* __restrict__ done) {
+  const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nb = (p.T + TILE - 1) / TILE;
   const int64_t bh = static_cast<int64_t>(b) * p.Hkv + h;
   float* csum = p.csum + bh * p.NBC * PL_D;
   const uint8_t* keep = p.keep + bh * p.NBC;
   int* bi = p.block_idx + bh * p.NBC;
-  extern __shared__ float pl_scores[];   // [PL_G][nb]
   __shared__ int scan[PL_THREADS];
   __shared__ float wM[PL_THREADS / 32][PL_G], wS[PL_THREADS / 32][PL_G];
-  __shared__ int s_trig;
+  __shared__ int s_flag;
 
   const int fl = p.flags[h];
-  if (fl & 2) {   // token-index head: index blocks + sink + newest, never refreshes
+  if (fl & 2) {   // token-index head: index blocks + sink + newest, never refreshes; one CTA does it
+    if (chunk != 0) return;
     const uint8_t* ix = p.idx + static_cast<int64_t>(b) * p.NBC;
     pl_compact(nb, bi, p.block_cnt + bh, scan, [&](int i) { return ix[i] || pl_always(i, nb, p.local); });
     if (tid == 0) p.trig[bh] = 0;
@@ -89,15 +96,16 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
   const uint8_t* ix = uni ? p.idx + static_cast<int64_t>(b) * p.NBC : nullptr;
   auto attended = [&](int blk) { return keep[blk] || pl_always(blk, nb, p.local) || (uni && ix[blk]); };
 
-  if (p.add_token) {   // D == 128 == PL_THREADS: one dim per thread
-    const int t = p.T - 1;
+  const int blk0 = chunk * PL_CHUNK;
+  const int tok_blk = (p.T - 1) / TILE;
+  if (p.add_token && tok_blk >= blk0 && tok_blk < blk0 + PL_CHUNK) {   // D == 128 == PL_THREADS
     const __nv_bfloat16* kr = reinterpret_cast<const __nv_bfloat16*>(p.k) + b * p.k_sb + h * p.k_sh +
-                              static_cast<int64_t>(t) * p.k_st;
-    csum[static_cast<int64_t>(t / TILE) * PL_D + tid] += __bfloat162float(kr[tid]);
+                              static_cast<int64_t>(p.T - 1) * p.k_st;
+    csum[static_cast<int64_t>(tok_blk) * PL_D + tid] += __bfloat162float(kr[tid]);
   }
   __syncthreads();
 
-  // 1. centroid scores, a warp per block, eight blocks per warp in flight
+  // 1. centroid scores of this chunk: a warp per block, lane owns dims 4*lane..4*lane+3
   float qv[PL_G][4];
 #pragma unroll
   for (int g = 0; g < PL_G; ++g) {
@@ -106,19 +114,18 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
     for (int e = 0; e < 4; ++e) qv[g][e] = __bfloat162float(qp[e]) * p.scale;
   }
   const int64_t row0 = (static_cast<int64_t>(b) * p.Hq + h * PL_G) * p.NBC;
-  constexpr int U = 8;
-  constexpr int NW = PL_THREADS / 32;
-  for (int base = warp; base < nb; base += NW * U) {
+  constexpr int U = PL_CHUNK / 4;
+  {
     float4 c[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int blk = base + NW * u;
+      const int blk = blk0 + warp + 4 * u;
       c[u] = blk < nb ? *reinterpret_cast<const float4*>(csum + static_cast<int64_t>(blk) * PL_D + 4 * lane)
                       : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int blk = base + NW * u;
+      const int blk = blk0 + warp + 4 * u;
       if (blk < nb) {
         const float inv_n = 1.f / static_cast<float>(blk == nb - 1 ? p.T - blk * TILE : TILE);
         float d[PL_G];
@@ -127,15 +134,21 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
           d[g] = warp_sum(qv[g][0] * c[u].x + qv[g][1] * c[u].y + qv[g][2] * c[u].z + qv[g][3] * c[u].w) * inv_n;
         if (lane < PL_G) {
           const float val = lane == 0 ? d[0] : lane == 1 ? d[1] : lane == 2 ? d[2] : d[3];
-          pl_scores[lane * nb + blk] = val;
           p.cs_now[row0 + lane * p.NBC + blk] = val;
         }
       }
     }
   }
+  // count this chunk; only the last one of the head goes on
+  __threadfence();
   __syncthreads();
+  if (tid == 0) s_flag = atomicAdd(&done[bh], 1) == static_cast<int>(gridDim.x) - 1;
+  __syncthreads();
+  if (!s_flag) return;
+  __threadfence();
+  if (tid == 0) done[bh] = 0;
 
-  // 2. estimate of the mass outside the attended set
+  // 2. estimate of the mass outside the attended set: fold slot t takes blocks t, t+128, ...
   float m[PL_G], s[PL_G];
 #pragma unroll
   for (int g = 0; g < PL_G; ++g) {
@@ -147,8 +160,10 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
 #pragma unroll
     for (int g = 0; g < PL_G; ++g)
       pl_fold(m[g], s[g],
-              p.lse_ref[row0 + g * p.NBC + blk] + pl_scores[g * nb + blk] - p.cs_ref[row0 + g * p.NBC + blk]);
+              p.lse_ref[row0 + g * p.NBC + blk] + __ldcg(p.cs_now + row0 + g * p.NBC + blk) -
+                  p.cs_ref[row0 + g * p.NBC + blk]);
   }
+  constexpr int NW = PL_THREADS / 32;
 #pragma unroll
   for (int g = 0; g < PL_G; ++g) {
     const float M = warp_max(m[g]);
@@ -180,12 +195,12 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
     const bool tr = dec > p.delta || a >= p.max_age || (fl & 1);
     p.age[bh] = tr ? 0 : a;
     p.trig[bh] = tr ? 1 : 0;
-    s_trig = tr ? 1 : 0;
+    s_flag = tr ? 1 : 0;
   }
   __syncthreads();
 
   // 3. block list of the attention pass
-  if (s_trig) {
+  if (s_flag) {
     for (int i = tid; i < nb; i += PL_THREADS) bi[i] = i;
     if (tid == 0) p.block_cnt[bh] = nb;
     return;
@@ -236,12 +251,26 @@ __global__ void __launch_bounds__(PL_THREADS) update_kernel(const kvskip_update_
     // exp(y) is the same in all 32 bisection steps: evaluate it once, keep the summation order
     for (int i = lane; i < nb; i += 32) ey[i] = __expf(x[i] - lse);
     float lo = -80.f, hi = 0.f;   // mass{y >= lo} >= level > mass{y >= hi}, y = x - lse
-    for (int it = 0; it < 32; ++it) {
+    int n_lo = 0, n_hi = 0;       // blocks with y >= lo, y >= hi
+    for (int i = lane; i < nb; i += 32) {
+      n_lo += (x[i] - lse >= lo) ? 1 : 0;
+      n_hi += (x[i] - lse >= hi) ? 1 : 0;
+    }
+    n_lo = __reduce_add_sync(0xffffffffu, n_lo);
+    n_hi = __reduce_add_sync(0xffffffffu, n_hi);
+    // Once no block lies between lo and hi every further step sees the same set, so the kept set
+    // {y >= lo} can no longer change: stop (the 32-step result is identical, lo itself is not output).
+    for (int it = 0; it < 32 && n_lo != n_hi; ++it) {
       const float mid = 0.5f * (lo + hi);
       float a = 0.f;
+      int n_mid = 0;
       for (int i = lane; i < nb; i += 32)
-        if (x[i] - lse >= mid) a += ey[i];
-      if (warp_sum(a) >= p.level) lo = mid; else hi = mid;
+        if (x[i] - lse >= mid) {
+          a += ey[i];
+          ++n_mid;
+        }
+      n_mid = __reduce_add_sync(0xffffffffu, n_mid);
+      if (warp_sum(a) >= p.level) { lo = mid; n_lo = n_mid; } else { hi = mid; n_hi = n_mid; }
     }
     for (int i = lane; i < nb; i += 32)
       if (x[i] - lse >= lo) skeep[i] = 1;

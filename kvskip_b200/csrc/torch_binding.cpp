@@ -344,6 +344,27 @@ void update(const at::Tensor& blk_max, const at::Tensor& blk_sum, const at::Tens
   raise_on(kvskip_launch_update(&p, cur_stream()));
 }
 
+// One layer's refresh-policy step in a single call: plan -> masked attention with block
+// statistics over plan's block list -> update, three launches on the current stream and no host
+// synchronisation (what the reference's caller issues as three Python calls,
+// src/kvskip_attn.py:463-473).  Returns [out, lse, blk_max, blk_sum].
+std::vector<at::Tensor> refresh_step(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, at::Tensor& csum,
+                                     at::Tensor& lse_ref, at::Tensor& cs_ref, at::Tensor& keep, at::Tensor& lse_att,
+                                     at::Tensor& age, const at::Tensor& flags, at::Tensor& cs_now, at::Tensor& trig,
+                                     at::Tensor& block_idx, at::Tensor& block_cnt, double scale, double delta,
+                                     int64_t max_age, int64_t local, double level, int64_t num_splits,
+                                     const c10::optional<at::Tensor>& idx, const c10::optional<at::Tensor>& calib,
+                                     const c10::optional<at::Tensor>& est, bool calib_on, int64_t calib_kind,
+                                     double calib_rate, bool calib_free, const c10::optional<at::Tensor>& aix,
+                                     double aix_thr) {
+  plan(q, k, csum, lse_ref, cs_ref, keep, lse_att, age, flags, cs_now, trig, block_idx, block_cnt, scale, delta, max_age,
+       local, true, idx, calib, est, calib_on, calib_kind, aix);
+  auto r = decode(q, k, v, scale, block_idx, block_cnt, true, true, num_splits, 2, false, false);
+  update(r[2], r[3], trig, cs_now, keep, lse_ref, cs_ref, lse_att, k.size(2), level, local, flags, idx, est, calib,
+         calib_rate, calib_free, calib_kind, aix, aix_thr);
+  return {r[0], r[1], r[2], r[3]};
+}
+
 void read_bw(const at::Tensor& x, at::Tensor& out, int64_t blocks) {
   TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.nbytes() % 16 == 0, "x: contiguous CUDA, 16-byte multiple");
   const c10::cuda::CUDAGuard guard(x.device());
@@ -418,6 +439,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("write_p") = false);
   m.def("pv", &pv, "two-pass V-skip, pass 2", py::arg("P"), py::arg("v"), py::arg("blk_scale"), py::arg("block_idx"),
         py::arg("block_cnt"), py::arg("num_splits") = 1, py::arg("want_f32") = false);
+  m.def("refresh_step", &refresh_step, "plan -> masked+stats attention -> update for one layer, one call",
+        py::arg("q"), py::arg("k"), py::arg("v"), py::arg("csum"), py::arg("lse_ref"), py::arg("cs_ref"),
+        py::arg("keep"), py::arg("lse_att"), py::arg("age"), py::arg("flags"), py::arg("cs_now"), py::arg("trig"),
+        py::arg("block_idx"), py::arg("block_cnt"), py::arg("scale"), py::arg("delta"), py::arg("max_age"),
+        py::arg("local"), py::arg("level"), py::arg("num_splits"), py::arg("idx") = py::none(),
+        py::arg("calib") = py::none(), py::arg("est") = py::none(), py::arg("calib_on") = false,
+        py::arg("calib_kind") = 0, py::arg("calib_rate") = 0.0, py::arg("calib_free") = false,
+        py::arg("aix") = py::none(), py::arg("aix_thr") = 0.0);
   m.def("merge", &merge, "merge of R partial (max, sum, acc) rows", py::arg("part_acc"), py::arg("part_ml"));
   m.def("index_blocks", &index_blocks, "token-index blocks of one step", py::arg("ids"), py::arg("T"), py::arg("out"));
   m.def("set_option", &set_option, "process-wide option, e.g. (\"decode_path\", 1) for the exact-order kernels",

@@ -52,6 +52,10 @@ class CudaOps:
     def update(self, *a):
         return K.ext().update(*a)
 
+    def fused_step(self, *a, **kw):
+        """plan -> masked+stats attention -> update in one extension call."""
+        return K.ext().refresh_step(*a, **kw)
+
 
 def centroid_sums(k: torch.Tensor) -> torch.Tensor:
     """Per-block sums of keys, fp32 [B, Hkv, nb, D] (the last block may be partial)."""
@@ -180,6 +184,16 @@ class RefreshLayer:
         cal = cfg.calib is not None
         kind = CALIB_KINDS[cfg.calib_kind]
         auto = cfg.calib_auto_ix is not None
+        if hasattr(self.ops, "fused_step"):
+            ns = K.num_splits_for(B * k.shape[1], nb)        # sized for every block: no host sync
+            out, lse, bmax, bsum = self.ops.fused_step(
+                q, k, v, s["csum"], s["lse_ref"], s["cs_ref"], s["keep"], s["lse_att"], s["age"], s["flags"],
+                s["cs_now"], s["trig"], s["block_idx"], s["block_cnt"], float(scale), float(cfg.delta),
+                int(self.max_age_now()), int(cfg.local), float(cfg.level), int(ns), idx, s["calib"] if cal else None,
+                s["est"], bool(cal and self.t >= cfg.calib_hold), kind, float(cfg.calib or 0.0),
+                bool(cfg.calib_free), s["aix"] if auto else None, float(cfg.calib_auto_ix or 0.0))
+            self.last = {"blk_max": bmax, "blk_sum": bsum, "lse": lse, "first": False}
+            return out
         self.ops.plan(q, k, s["csum"], s["lse_ref"], s["cs_ref"], s["keep"], s["lse_att"], s["age"], s["flags"],
                       s["cs_now"], s["trig"], s["block_idx"], s["block_cnt"], float(scale), float(cfg.delta),
                       int(self.max_age_now()), int(cfg.local), True, idx, s["calib"] if cal else None, s["est"],
