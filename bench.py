@@ -335,10 +335,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cases", action="store_true", help="skip the additional configurations")
     ap.add_argument("--batch", type=int, default=B_PER_GPU, help="sequences per GPU of the headline workload")
+    ap.add_argument("--context", type=int, default=0, help="context length of a --profile --mode planner run")
     ap.add_argument("--profile", action="store_true",
                     help="profiling run: warm-up and timed steps of the headline workload only (use with a small "
                          "--batch under ncu), prints a short JSON line")
-    ap.add_argument("--mode", default="dense", choices=["dense", "masked", "masked_stats", "vskip1"],
+    ap.add_argument("--mode", default="dense", choices=["dense", "masked", "masked_stats", "vskip1", "planner"],
                     help="kernel variant of a --profile run")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -377,6 +378,26 @@ def main():
     step = lambda: K.decode(q, k, v, scale)  # noqa: E731
     nbytes = kv_bytes(B, T)
 
+    if args.profile and args.mode == "planner":
+        from kvskip_b200 import synth
+        from kvskip_b200.refresh import RefreshConfig, RefreshLayer
+        del k, v
+        T0 = args.context or (T_HEAD // 2 if B > 4 else T_HEAD)
+        walk = synth.planner_walk_device(5, T0, args.warmup + args.steps + 1, dev, B=B)
+        layer = RefreshLayer(RefreshConfig())
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        for t in range(args.warmup + args.steps + 1):
+            if t == args.warmup + 1:
+                ev[0].record()
+            Tt = T0 + t + 1
+            layer.step(walk.q[t], walk.k[:, :, :Tt], walk.v[:, :, :Tt], walk.scale)
+        ev[1].record()
+        torch.cuda.synchronize()
+        print(json.dumps({"profile": "planner", "batch": B, "context": T0,
+                          "us_per_layer_step": ev[0].elapsed_time(ev[1]) * 1e3 / args.steps,
+                          "blocks_read_last": float(layer.state["block_cnt"].sum()) / (B * HKV * math.ceil(Tt / 64))}),
+              flush=True)
+        return
     if args.profile:
         from kvskip_b200 import synth  # noqa: F401
         if args.mode != "dense":

@@ -404,7 +404,11 @@ int kvskip_launch_plan(const kvskip_plan_params* p, void* stream) {
   if (int rc = split_done_region(p->B * p->Hkv, &done)) return rc;
   if (!done) return fail(KVSKIP_E_LIMIT, "plan: more than %d (batch, kv head) pairs per call", kMergeRegion);
   const int chunks = (nb + kvb::PL_CHUNK - 1) / kvb::PL_CHUNK;
-  kvb::plan_kernel<<<dim3(chunks, p->Hkv, p->B), kvb::PL_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(*p, done);
+  const int smem = (nb + 15) & ~15;   // attended flags of one head
+  if (smem > 200 * 1024) return fail(KVSKIP_E_LIMIT, "plan: more than %d blocks", 200 * 1024);
+  if (smem > 40 * 1024)
+    if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::plan_kernel), 200 * 1024)) return rc;
+  kvb::plan_kernel<<<dim3(chunks, p->Hkv, p->B), kvb::PL_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(*p, done);
   KVB_CUDA(cudaGetLastError());
   return KVSKIP_OK;
 }
@@ -416,7 +420,7 @@ int kvskip_launch_update(const kvskip_update_params* p, void* stream) {
   if (nb > p->NBC) return fail(KVSKIP_E_ARG, "block capacity exceeded");
   if (p->calib && (!p->flags || !p->est)) return fail(KVSKIP_E_ARG, "calibration needs flags and est");
   if (p->aix && !p->idx) return fail(KVSKIP_E_ARG, "aix needs idx");
-  const int smem = 2 * kvb::PL_G * nb * static_cast<int>(sizeof(float)) + nb;
+  const int smem = 2 * kvb::PL_G * nb * static_cast<int>(sizeof(float)) + 2 * nb;
   if (smem > 220 * 1024) return fail(KVSKIP_E_LIMIT, "update: more than %d blocks", 220 * 1024 / 33);
   if (smem > 48 * 1024)
     if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::update_kernel), 220 * 1024)) return rc;

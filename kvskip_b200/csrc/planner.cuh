@@ -11,9 +11,12 @@
 //                    serially in ascending order;
 //   top-p cut        per query head lane l owns blocks l, l+32, ...; 32 bisection steps on the
 //                    log-weight threshold in [-80, 0], each a lane-serial sum + butterfly.
-// Layout of the work is ours: `plan` spreads the centroid scores over every warp of the CTA,
-// keeps them in shared memory for the fold, and raises the dynamic shared-memory limit so block
-// counts beyond 3072 (contexts beyond 196 608 tokens) work.
+// Layout of the work is ours.  Both kernels are chains of dependent memory latencies rather than
+// bandwidth: `plan` spreads the centroid scores over ceil(nb/32) CTAs per head and lets the last
+// one to finish do the fold; the per-block "attended" flags are staged in shared memory with
+// independent coalesced loads, and the fold loads its operands four blocks ahead, so a head costs
+// a handful of memory round trips instead of one per block.  No per-head shared-memory table of
+// scores is needed, so block counts beyond 3072 (contexts beyond 196 608 tokens) work.
 #pragma once
 #include "common.cuh"
 
@@ -114,29 +117,40 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
     for (int e = 0; e < 4; ++e) qv[g][e] = __bfloat162float(qp[e]) * p.scale;
   }
   const int64_t row0 = (static_cast<int64_t>(b) * p.Hq + h * PL_G) * p.NBC;
+  // Warp w takes the 8 consecutive blocks blk0 + 8w .. +7: 8 blocks x 4 heads = 32 dot products,
+  // each the butterfly sum (lane distances 16, 8, 4, 2, 1) of 32 per-lane partials.  Instead of 32
+  // butterflies in which every lane computes every sum, the 32 sums are reduced together: at
+  // distance 16 a lane keeps the 16 sums whose index has the lane's bit 4 and hands the other 16
+  // to its partner, and so on.  Every addition has the same two operands in the same order as in
+  // the butterfly, so the bits are the same; lane j ends up with sum j.
   constexpr int U = PL_CHUNK / 4;
+  static_assert(U * PL_G == 32, "one dot product per lane");
   {
-    float4 c[U];
+    float a[32];   // a[4 * u + g]: this lane's partial of block u, head g
+    const int wb = blk0 + warp * U;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int blk = blk0 + warp + 4 * u;
-      c[u] = blk < nb ? *reinterpret_cast<const float4*>(csum + static_cast<int64_t>(blk) * PL_D + 4 * lane)
-                      : make_float4(0.f, 0.f, 0.f, 0.f);
+      const int blk = wb + u;
+      const float4 c = blk < nb ? *reinterpret_cast<const float4*>(csum + static_cast<int64_t>(blk) * PL_D + 4 * lane)
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int g = 0; g < PL_G; ++g)
+        a[4 * u + g] = qv[g][0] * c.x + qv[g][1] * c.y + qv[g][2] * c.z + qv[g][3] * c.w;
     }
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int blk = blk0 + warp + 4 * u;
-      if (blk < nb) {
-        const float inv_n = 1.f / static_cast<float>(blk == nb - 1 ? p.T - blk * TILE : TILE);
-        float d[PL_G];
+    for (int o = 16; o > 0; o >>= 1) {
+      const bool up = (lane & o) != 0;
 #pragma unroll
-        for (int g = 0; g < PL_G; ++g)
-          d[g] = warp_sum(qv[g][0] * c[u].x + qv[g][1] * c[u].y + qv[g][2] * c[u].z + qv[g][3] * c[u].w) * inv_n;
-        if (lane < PL_G) {
-          const float val = lane == 0 ? d[0] : lane == 1 ? d[1] : lane == 2 ? d[2] : d[3];
-          p.cs_now[row0 + lane * p.NBC + blk] = val;
-        }
+      for (int j = 0; j < o; ++j) {
+        const float mine = up ? a[j + o] : a[j];
+        const float theirs = up ? a[j] : a[j + o];
+        a[j] = mine + __shfl_xor_sync(0xffffffffu, theirs, o);
       }
+    }
+    const int blk = wb + (lane >> 2), g = lane & 3;
+    if (blk < nb) {
+      const float inv_n = 1.f / static_cast<float>(blk == nb - 1 ? p.T - blk * TILE : TILE);
+      p.cs_now[row0 + g * p.NBC + blk] = a[0] * inv_n;
     }
   }
   // count this chunk; only the last one of the head goes on
@@ -148,20 +162,39 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
   __threadfence();
   if (tid == 0) done[bh] = 0;
 
+  // attended flags of every block into shared memory: independent, coalesced loads
+  extern __shared__ unsigned char pl_att[];   // [nb]
+  for (int i = tid; i < nb; i += PL_THREADS) pl_att[i] = attended(i) ? 1 : 0;
+  __syncthreads();
+
   // 2. estimate of the mass outside the attended set: fold slot t takes blocks t, t+128, ...
+  // (operands of four blocks are loaded before the dependent exp chain of the fold starts)
   float m[PL_G], s[PL_G];
 #pragma unroll
   for (int g = 0; g < PL_G; ++g) {
     m[g] = -INFINITY;
     s[g] = 0.f;
   }
-  for (int blk = tid; blk < nb; blk += PL_THREADS) {
-    if (attended(blk)) continue;
+  for (int base = tid; base < nb; base += 4 * PL_THREADS) {
+    float e[4][PL_G];
+    bool use[4];
 #pragma unroll
-    for (int g = 0; g < PL_G; ++g)
-      pl_fold(m[g], s[g],
-              p.lse_ref[row0 + g * p.NBC + blk] + __ldcg(p.cs_now + row0 + g * p.NBC + blk) -
-                  p.cs_ref[row0 + g * p.NBC + blk]);
+    for (int j = 0; j < 4; ++j) {
+      const int blk = base + j * PL_THREADS;
+      use[j] = blk < nb && !pl_att[blk];
+      if (use[j]) {
+#pragma unroll
+        for (int g = 0; g < PL_G; ++g)
+          e[j][g] = p.lse_ref[row0 + g * p.NBC + blk] + __ldcg(p.cs_now + row0 + g * p.NBC + blk) -
+                    p.cs_ref[row0 + g * p.NBC + blk];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (use[j]) {
+#pragma unroll
+        for (int g = 0; g < PL_G; ++g) pl_fold(m[g], s[g], e[j][g]);
+      }
   }
   constexpr int NW = PL_THREADS / 32;
 #pragma unroll
@@ -205,7 +238,7 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
     if (tid == 0) p.block_cnt[bh] = nb;
     return;
   }
-  pl_compact(nb, bi, p.block_cnt + bh, scan, attended);
+  pl_compact(nb, bi, p.block_cnt + bh, scan, [&](int i) { return pl_att[i] != 0; });
 }
 
 __global__ void __launch_bounds__(PL_THREADS) update_kernel(const kvskip_update_params p) {
@@ -218,26 +251,34 @@ __global__ void __launch_bounds__(PL_THREADS) update_kernel(const kvskip_update_
   float* x = up_smem + warp * nb;                                          // block log-weights of the head
   float* ey = up_smem + (PL_G + warp) * nb;                                // exp(x - lse) of the head
   uint8_t* skeep = reinterpret_cast<uint8_t*>(up_smem + 2 * PL_G * nb);   // [nb] union of the new sets
+  uint8_t* sflag = skeep + nb;   // [nb] bit 0: stored or always read, bit 1: joined through the token index
   uint8_t* keep = p.keep + bh * p.NBC;
   const bool tr = p.trig[bh];
   __shared__ float s_real[PL_G];
 
   float mx = -INFINITY;
+#pragma unroll 8
   for (int i = lane; i < nb; i += 32) {
     const float val = p.blk_max[hrow * nb + i] + __logf(p.blk_sum[hrow * nb + i]);   // -inf where not read
     x[i] = val;
     mx = fmaxf(mx, val);
   }
-  for (int i = tid; i < nb; i += PL_THREADS) skeep[i] = 0;
+  {  // set membership flags once, with independent coalesced loads, instead of a global load per fold step
+    const bool uni = tr && p.calib && ((p.flags[h] & 4) || (p.aix && p.aix[bh]));
+    const uint8_t* ix = uni ? p.idx + static_cast<int64_t>(b) * p.NBC : nullptr;
+#pragma unroll 4
+    for (int i = tid; i < nb; i += PL_THREADS) {
+      skeep[i] = 0;
+      sflag[i] = ((keep[i] || pl_always(i, nb, p.local)) ? 1 : 0) | ((uni && ix[i]) ? 2 : 0);
+    }
+  }
   mx = warp_max(mx);
   __syncthreads();
 
   if (tr && p.calib) {   // mass the old attended set really missed (a refreshing head read every block)
-    const bool uni = (p.flags[h] & 4) || (p.aix && p.aix[bh]);
-    const uint8_t* ix = uni ? p.idx + static_cast<int64_t>(b) * p.NBC : nullptr;
     float mi = -INFINITY, si = 0.f, mo = -INFINITY, so = 0.f;
     for (int i = lane; i < nb; i += 32) {
-      if (keep[i] || pl_always(i, nb, p.local) || (uni && ix[i])) pl_fold(mi, si, x[i]);
+      if (sflag[i]) pl_fold(mi, si, x[i]);
       else pl_fold(mo, so, x[i]);
     }
     const float Mi = warp_max(mi), Si = warp_sum(si > 0.f ? si * __expf(mi - Mi) : 0.f);
@@ -292,12 +333,15 @@ __global__ void __launch_bounds__(PL_THREADS) update_kernel(const kvskip_update_
     if (p.aix && c > p.aix_thr) p.aix[bh] = 1;
   }
   if (tr)
-    for (int i = tid; i < p.NBC; i += PL_THREADS)
-      keep[i] = (i < nb && (skeep[i] || pl_always(i, nb, p.local))) ? 1 : 0;
+    for (int i = tid; i < p.NBC; i += PL_THREADS) {
+      const uint8_t kept = (i < nb && (skeep[i] || pl_always(i, nb, p.local))) ? 1 : 0;
+      keep[i] = kept;
+      if (i < nb) sflag[i] = kept;
+    }
   __syncthreads();
   float m2 = -INFINITY, s2 = 0.f;
   for (int i = lane; i < nb; i += 32)
-    if (keep[i] || pl_always(i, nb, p.local)) pl_fold(m2, s2, x[i]);
+    if (sflag[i] & 1) pl_fold(m2, s2, x[i]);
   const float M = warp_max(m2);
   const float S = warp_sum(s2 > 0.f ? s2 * __expf(m2 - M) : 0.f);
   if (lane == 0) p.lse_att[hrow] = M + __logf(S);
