@@ -192,7 +192,10 @@ int kvskip_launch_index_blocks(const int64_t* ids, int64_t ids_stride, int n, in
  *   "decode_path"  0 (default): tensor-core kernel for D = 128, exact-order kernel otherwise;
  *                  1: exact-order kernel everywhere -- scores, block statistics and outputs are
  *                     bit-identical to the reference's kernels on the same GPU;
- *                  2: tensor-core kernel, error where it does not exist. */
+ *                  2: tensor-core kernel, error where it does not exist.
+ *   "pdl"          1 (default): the attention and planner kernels are launched with programmatic
+ *                  stream serialisation, so their set-up overlaps the tail of the previous kernel
+ *                  on the stream (they wait for it before reading memory); 0: plain launches. */
 int kvskip_set_option(const char* name, int value);
 int kvskip_get_option(const char* name);
 

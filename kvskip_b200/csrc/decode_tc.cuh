@@ -104,6 +104,21 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
+  if (tid == 0) {
+    tma_prefetch_desc(&maps.k);
+    if constexpr (LOAD_V) tma_prefetch_desc(&maps.v);
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  // Launched with programmatic stream serialisation: everything above overlaps the tail of the
+  // previous kernel on the stream; nothing that kernel may have written is read before this wait.
+  pdl_wait_prior();
+  pdl_launch_dependents();
+
   int n_items;
   const int32_t* list = nullptr;
   if constexpr (MASKED) {
@@ -116,16 +131,6 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
   const int i0 = min(n_items, split * per);
   const int n = min(n_items, i0 + per) - i0;
 
-  if (tid == 0) {
-    tma_prefetch_desc(&maps.k);
-    if constexpr (LOAD_V) tma_prefetch_desc(&maps.v);
-    for (int s = 0; s < S; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
-    }
-    mbar_fence_init();
-  }
-  __syncthreads();
 
   // per-thread state of a consumer: two heads (columns 2*(lane&3), +1 of the 8-wide N axis)
   float m_run[2] = {-INFINITY, -INFINITY};

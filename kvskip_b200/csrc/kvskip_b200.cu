@@ -135,6 +135,27 @@ int launch_exact(const kvskip_params& p, cudaStream_t stream) {
   return KVSKIP_OK;
 }
 
+std::atomic<int> g_use_pdl{1};
+
+// Launch that lets the kernel's prologue overlap the tail of the previous kernel on the stream
+// (programmatic dependent launch).  Only for kernels that execute griddepcontrol.wait before
+// their first read of global memory.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_use_pdl.load(std::memory_order_relaxed) ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Counters of finished splits for the in-kernel merge: zero at load, put back to zero by the CTA
 // that merges.  Sixteen regions used round-robin by successive launches, so launches that overlap
 // on different streams do not share counters.
@@ -180,8 +201,8 @@ int launch_tc(const kvskip_params& p, cudaStream_t stream) {
   int* done = nullptr;
   if (LOAD_V && p.num_splits > 1)
     if (int rc = split_done_region(p.B * p.Hkv, &done)) return rc;
-  kernel<<<dim3(p.num_splits, p.Hkv, p.B), kvb::TC_THREADS, Cfg::kSmemBytes, stream>>>(p, maps, done);
-  KVB_CUDA(cudaGetLastError());
+  KVB_CUDA(launch_overlapped(kernel, dim3(p.num_splits, p.Hkv, p.B), dim3(kvb::TC_THREADS), Cfg::kSmemBytes, stream, p,
+                             maps, done));
   if (LOAD_V && p.num_splits > 1 && done == nullptr) {
     kvb::merge_kernel<128><<<p.B * p.Hq, 128, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits,
                                                           static_cast<int64_t>(p.B) * p.Hq, true, p.out, p.out_f32,
@@ -246,8 +267,8 @@ int launch_vskip1_tc(const kvskip_params& p, cudaStream_t stream) {
   int* done = nullptr;
   if (p.num_splits > 1)
     if (int rc = split_done_region(p.B * p.Hkv, &done)) return rc;
-  kernel<<<dim3(p.num_splits, p.Hkv, p.B), kvb::TC_THREADS, kvb::Vs1TcCfg::kSmemBytes, stream>>>(p, maps, done);
-  KVB_CUDA(cudaGetLastError());
+  KVB_CUDA(launch_overlapped(kernel, dim3(p.num_splits, p.Hkv, p.B), dim3(kvb::TC_THREADS),
+                             kvb::Vs1TcCfg::kSmemBytes, stream, p, maps, done));
   if (p.num_splits > 1 && done == nullptr) {
     kvb::merge_kernel<128><<<p.B * p.Hq, 128, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits,
                                                           static_cast<int64_t>(p.B) * p.Hq, true, p.out, p.out_f32,
@@ -366,11 +387,16 @@ int kvskip_set_option(const char* name, int value) {
     g_decode_path.store(value, std::memory_order_relaxed);
     return KVSKIP_OK;
   }
+  if (!std::strcmp(name, "pdl")) {
+    g_use_pdl.store(value ? 1 : 0, std::memory_order_relaxed);
+    return KVSKIP_OK;
+  }
   return fail(KVSKIP_E_ARG, "unknown option %s", name);
 }
 
 int kvskip_get_option(const char* name) {
   if (name && !std::strcmp(name, "decode_path")) return g_decode_path.load(std::memory_order_relaxed);
+  if (name && !std::strcmp(name, "pdl")) return g_use_pdl.load(std::memory_order_relaxed);
   return fail(KVSKIP_E_ARG, "unknown option");
 }
 
@@ -408,8 +434,8 @@ int kvskip_launch_plan(const kvskip_plan_params* p, void* stream) {
   if (smem > 200 * 1024) return fail(KVSKIP_E_LIMIT, "plan: more than %d blocks", 200 * 1024);
   if (smem > 40 * 1024)
     if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::plan_kernel), 200 * 1024)) return rc;
-  kvb::plan_kernel<<<dim3(chunks, p->Hkv, p->B), kvb::PL_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(*p, done);
-  KVB_CUDA(cudaGetLastError());
+  KVB_CUDA(launch_overlapped(kvb::plan_kernel, dim3(chunks, p->Hkv, p->B), dim3(kvb::PL_THREADS), smem,
+                             static_cast<cudaStream_t>(stream), *p, done));
   return KVSKIP_OK;
 }
 
@@ -424,8 +450,8 @@ int kvskip_launch_update(const kvskip_update_params* p, void* stream) {
   if (smem > 220 * 1024) return fail(KVSKIP_E_LIMIT, "update: more than %d blocks", 220 * 1024 / 33);
   if (smem > 48 * 1024)
     if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::update_kernel), 220 * 1024)) return rc;
-  kvb::update_kernel<<<dim3(p->Hkv, p->B), kvb::PL_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(*p);
-  KVB_CUDA(cudaGetLastError());
+  KVB_CUDA(launch_overlapped(kvb::update_kernel, dim3(p->Hkv, p->B), dim3(kvb::PL_THREADS), smem,
+                             static_cast<cudaStream_t>(stream), *p));
   return KVSKIP_OK;
 }
 

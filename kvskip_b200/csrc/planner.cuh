@@ -86,6 +86,8 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
   __shared__ int scan[PL_THREADS];
   __shared__ float wM[PL_THREADS / 32][PL_G], wS[PL_THREADS / 32][PL_G];
   __shared__ int s_flag;
+  pdl_wait_prior();          // the state this kernel reads may come from the previous kernel on the stream
+  pdl_launch_dependents();
 
   const int fl = p.flags[h];
   if (fl & 2) {   // token-index head: index blocks + sink + newest, never refreshes; one CTA does it
@@ -253,6 +255,8 @@ __global__ void __launch_bounds__(PL_THREADS) update_kernel(const kvskip_update_
   uint8_t* skeep = reinterpret_cast<uint8_t*>(up_smem + 2 * PL_G * nb);   // [nb] union of the new sets
   uint8_t* sflag = skeep + nb;   // [nb] bit 0: stored or always read, bit 1: joined through the token index
   uint8_t* keep = p.keep + bh * p.NBC;
+  pdl_wait_prior();          // statistics and decisions come from the kernels before this one
+  pdl_launch_dependents();
   const bool tr = p.trig[bh];
   __shared__ float s_real[PL_G];
 

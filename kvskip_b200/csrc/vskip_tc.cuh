@@ -56,6 +56,8 @@ vskip1_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
     mbar_fence_init();
   }
   __syncthreads();
+  pdl_wait_prior();          // nothing written by the previous kernel on the stream is read above
+  pdl_launch_dependents();
 
   const int lrow = lane & 7, lmat = lane >> 3;
   const int64_t hq0 = static_cast<int64_t>(b) * p.Hq + h * G;
