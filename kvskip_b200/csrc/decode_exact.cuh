@@ -25,8 +25,11 @@ template <int D, bool LOAD_V>
 struct ExactCfg {
   static constexpr int kTileBytes = TILE * D * 2;
   static constexpr int kStageBytes = kTileBytes * (LOAD_V ? 2 : 1);
-  // ring depth: as many stages as fit beside the score buffers (about 190 KB of tiles)
-  static constexpr int kStages = (D == 128) ? (LOAD_V ? 6 : 10) : (LOAD_V ? 10 : 12);
+  // ring depth: two stages of K+V (64 KB), so three CTAs fit on an SM.  This path is bound by its
+  // own instruction stream (one warp per scheduler and CTA); more resident CTAs hide more latency
+  // than a deeper ring does (measured: 2.3 -> 4.1 TB/s at batch 1 / 64k with 54 splits, 2.9 -> 5.3
+  // TB/s at batch 16 / 32k), so the front end sizes the split count for three CTAs per SM.
+  static constexpr int kStages = (D == 128) ? (LOAD_V ? 2 : 4) : (LOAD_V ? 4 : 8);
   static constexpr int kAuxFloats = 4 * TILE /*scores*/ + TILE * 4 /*probs*/ + 4 /*alpha*/ + 8 /*m,l*/;
   static constexpr int kSmemBytes = kStages * kStageBytes + kAuxFloats * 4 + kStages * 8 + 128;
 };
@@ -37,7 +40,7 @@ struct TmaMaps {
 };
 
 template <int D, bool MASKED, bool STATS, bool LOAD_V>
-__global__ void __launch_bounds__(EX_THREADS, 1)
+__global__ void __launch_bounds__(EX_THREADS, 3)
 decode_exact_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps) {
   using Cfg = ExactCfg<D, LOAD_V>;
   constexpr int G = 4;

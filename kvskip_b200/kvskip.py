@@ -116,7 +116,9 @@ def decode(q, k, v, scale: float, *, plan: Plan | None = None, stats: bool = Fal
     B, Hkv, T = q.shape[0], k.shape[1], k.shape[2]
     if num_splits is None:
         n_items = math.ceil(T / TILE) if plan is None else plan.max_cnt
-        num_splits = num_splits_for(B * Hkv, n_items)
+        # the tensor-core kernel owns an SM; three CTAs of the exact-order kernel share one
+        per_sm = 1 if (q.shape[-1] == 128 and ext().get_option("decode_path") != 1) else 3
+        num_splits = num_splits_for(B * Hkv, n_items, sms=per_sm * num_sms())
     bi, bc = (None, None) if plan is None else (plan.block_idx, plan.block_cnt)
     out, lse, bmax, bsum, o32, pbuf = ext().decode(q, k, v, float(scale), bi, bc, stats, load_v,
                                                    int(num_splits), int(stages), out_f32, write_p)
