@@ -182,6 +182,13 @@ int kvskip_max_smem_bytes(int D, int stages, int load_v);
 int kvskip_launch_merge(const float* part_acc, const float* part_ml, int R, int64_t N, int D, uint16_t* out,
                         float* out_f32, float* lse, void* stream);
 
+/* Sequence shards without intermediate tensor ops: pack a rank's normalised result (out_f32 [N,D],
+ * lse [N]) into rows [acc(D) | m | l] = [out | lse/ln2 | 1] of `packed` [N,D+2] (the buffer handed
+ * to the all-gather), and merge R gathered buffers `parts` [R,N,D+2] in ascending r. */
+int kvskip_launch_pack_partial(const float* out_f32, const float* lse, float* packed, int64_t N, int D, void* stream);
+int kvskip_launch_merge_packed(const float* parts, int R, int64_t N, int D, uint16_t* out, float* out_f32, float* lse,
+                               void* stream);
+
 /* Token-index blocks of one decode step on the device (the reference builds them with torch ops,
  * src/lab.py:149-167): ids int64 [n, ids_stride], current token at T-1; out uint8 [n, NBC], a
  * block is marked if it holds an earlier copy of the current token or the position after one. */

@@ -314,4 +314,44 @@ __global__ void __launch_bounds__(D) merge_kernel(const float* __restrict__ part
   if (d == 0 && lse) lse[row] = l > 0.f ? (m + log2f(l)) * LN2 : -INFINITY;
 }
 
+// Sequence shards: a rank's normalised result as the triple the merge consumes, packed per row as
+// [acc(D) | m | l] with acc = out, m = lse / ln 2, l = 1 (l = 0, m = -inf for a rank that read nothing).
+template <int D>
+__global__ void __launch_bounds__(D) pack_partial_kernel(const float* __restrict__ out_f32,
+                                                         const float* __restrict__ lse, float* __restrict__ packed) {
+  const int64_t row = blockIdx.x;
+  const int d = threadIdx.x;
+  pdl_wait_prior();
+  packed[row * (D + 2) + d] = out_f32[row * D + d];
+  if (d == 0) {
+    const float x = lse[row];
+    const bool empty = x == -INFINITY;
+    packed[row * (D + 2) + D] = empty ? -INFINITY : x * LOG2E;
+    packed[row * (D + 2) + D + 1] = empty ? 0.f : 1.f;
+  }
+}
+
+// merge_kernel for R packed partials [R][N][D+2], ascending r.
+template <int D>
+__global__ void __launch_bounds__(D) merge_packed_kernel(const float* __restrict__ parts, int R, int64_t N,
+                                                         uint16_t* out, float* out_f32, float* lse) {
+  const int64_t row = blockIdx.x;
+  const int d = threadIdx.x;
+  constexpr int W = D + 2;
+  float m = -INFINITY;
+  for (int r = 0; r < R; ++r) m = fmaxf(m, parts[(static_cast<int64_t>(r) * N + row) * W + D]);
+  const float mu = (m == -INFINITY) ? 0.f : m;
+  float l = 0.f, acc = 0.f;
+  for (int r = 0; r < R; ++r) {
+    const float* pr = parts + (static_cast<int64_t>(r) * N + row) * W;
+    const float w = ex2(pr[D] - mu);
+    l += pr[D + 1] * w;
+    acc += pr[d] * w;
+  }
+  const float o32 = l > 0.f ? acc / l : 0.f;
+  if (out) reinterpret_cast<__nv_bfloat16*>(out)[row * D + d] = __float2bfloat16(o32);
+  if (out_f32) out_f32[row * D + d] = o32;
+  if (d == 0 && lse) lse[row] = l > 0.f ? (m + log2f(l)) * LN2 : -INFINITY;
+}
+
 }  // namespace kvb

@@ -478,6 +478,33 @@ int kvskip_launch_merge(const float* part_acc, const float* part_ml, int R, int6
   return KVSKIP_OK;
 }
 
+int kvskip_launch_pack_partial(const float* out_f32, const float* lse, float* packed, int64_t N, int D, void* stream) {
+  if (!out_f32 || !lse || !packed || N < 1 || N > 2147483647LL) return fail(KVSKIP_E_ARG, "pack_partial: bad arguments");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (D == 128)
+    kvb::pack_partial_kernel<128><<<static_cast<unsigned>(N), 128, 0, s>>>(out_f32, lse, packed);
+  else if (D == 64)
+    kvb::pack_partial_kernel<64><<<static_cast<unsigned>(N), 64, 0, s>>>(out_f32, lse, packed);
+  else
+    return fail(KVSKIP_E_ARG, "kvskip: unsupported head dim");
+  KVB_CUDA(cudaGetLastError());
+  return KVSKIP_OK;
+}
+
+int kvskip_launch_merge_packed(const float* parts, int R, int64_t N, int D, uint16_t* out, float* out_f32, float* lse,
+                               void* stream) {
+  if (!parts || R < 1 || N < 1 || N > 2147483647LL) return fail(KVSKIP_E_ARG, "merge_packed: bad arguments");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (D == 128)
+    kvb::merge_packed_kernel<128><<<static_cast<unsigned>(N), 128, 0, s>>>(parts, R, N, out, out_f32, lse);
+  else if (D == 64)
+    kvb::merge_packed_kernel<64><<<static_cast<unsigned>(N), 64, 0, s>>>(parts, R, N, out, out_f32, lse);
+  else
+    return fail(KVSKIP_E_ARG, "kvskip: unsupported head dim");
+  KVB_CUDA(cudaGetLastError());
+  return KVSKIP_OK;
+}
+
 int kvskip_launch_index_blocks(const int64_t* ids, int64_t ids_stride, int n, int T, uint8_t* out, int NBC,
                                void* stream) {
   if (!ids || !out || n < 1 || T < 1) return fail(KVSKIP_E_ARG, "index_blocks: bad arguments");

@@ -388,6 +388,32 @@ std::vector<at::Tensor> merge(const at::Tensor& part_acc, const at::Tensor& part
   return {out, out32, lse};
 }
 
+// out_f32 [.., D] fp32, lse [..] fp32 -> packed [N, D+2] fp32 (rows [out | lse/ln2 | 1])
+at::Tensor pack_partial(const at::Tensor& out_f32, const at::Tensor& lse) {
+  need_f32(out_f32, "out_f32"); need_f32(lse, "lse");
+  const int64_t D = out_f32.size(-1), N = out_f32.numel() / D;
+  TORCH_CHECK(lse.numel() == N, "lse: one value per row of out_f32");
+  const c10::cuda::CUDAGuard guard(out_f32.device());
+  at::Tensor packed = at::empty({N, D + 2}, out_f32.options());
+  raise_on(kvskip_launch_pack_partial(out_f32.data_ptr<float>(), lse.data_ptr<float>(), packed.data_ptr<float>(), N,
+                                      static_cast<int>(D), cur_stream()));
+  return packed;
+}
+
+// parts [R,N,D+2] fp32 -> [out bf16 [N,D], out_f32 [N,D], lse [N]]
+std::vector<at::Tensor> merge_packed(const at::Tensor& parts) {
+  need_f32(parts, "parts");
+  TORCH_CHECK(parts.dim() == 3 && parts.size(2) > 2, "parts [R,N,D+2]");
+  const c10::cuda::CUDAGuard guard(parts.device());
+  const int64_t R = parts.size(0), N = parts.size(1), D = parts.size(2) - 2;
+  at::Tensor out = at::empty({N, D}, parts.options().dtype(at::kBFloat16));
+  at::Tensor out32 = at::empty({N, D}, parts.options());
+  at::Tensor lse = at::empty({N}, parts.options());
+  raise_on(kvskip_launch_merge_packed(parts.data_ptr<float>(), static_cast<int>(R), N, static_cast<int>(D), u16m(out),
+                                      out32.data_ptr<float>(), lse.data_ptr<float>(), cur_stream()));
+  return {out, out32, lse};
+}
+
 void index_blocks(const at::Tensor& ids, int64_t T, at::Tensor& out) {
   TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.dim() == 2 && ids.stride(1) == 1, "ids: CUDA int64 [n, >= T]");
   TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kByte && out.dim() == 2 && out.is_contiguous() &&
@@ -448,6 +474,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("calib_kind") = 0, py::arg("calib_rate") = 0.0, py::arg("calib_free") = false,
         py::arg("aix") = py::none(), py::arg("aix_thr") = 0.0);
   m.def("merge", &merge, "merge of R partial (max, sum, acc) rows", py::arg("part_acc"), py::arg("part_ml"));
+  m.def("pack_partial", &pack_partial, "rank-local (out_f32, lse) -> packed (acc, m, l) rows", py::arg("out_f32"),
+        py::arg("lse"));
+  m.def("merge_packed", &merge_packed, "merge of R packed partial buffers [R,N,D+2]", py::arg("parts"));
   m.def("index_blocks", &index_blocks, "token-index blocks of one step", py::arg("ids"), py::arg("T"), py::arg("out"));
   m.def("set_option", &set_option, "process-wide option, e.g. (\"decode_path\", 1) for the exact-order kernels",
         py::arg("name"), py::arg("value"));

@@ -63,6 +63,12 @@ class CudaBackend:
     def merge(self, acc, ml):
         return K.ext().merge(acc, ml)
 
+    def pack(self, out_f32, lse):
+        return K.ext().pack_partial(out_f32, lse)
+
+    def merge_packed(self, parts):
+        return K.ext().merge_packed(parts)
+
 
 def local_partial(q, k_local, v_local, scale, plan=None, num_splits=None, backend=None):
     """Attention over this rank's part of the sequence as a packed (acc, m, l) triple:
@@ -70,6 +76,8 @@ def local_partial(q, k_local, v_local, scale, plan=None, num_splits=None, backen
     (l = 0 and m = -inf when the rank read nothing)."""
     backend = backend or CudaBackend()
     r = backend.decode(q, k_local, v_local, scale, plan=plan, num_splits=num_splits)
+    if hasattr(backend, "pack"):
+        return backend.pack(r["out_f32"], r["lse"])         # one small kernel instead of five tensor ops
     B, Hq, D = r["out_f32"].shape
     lse = r["lse"].reshape(B * Hq, 1)
     empty = torch.isinf(lse)
@@ -83,9 +91,13 @@ def merge_partials(parts: torch.Tensor, B: int, Hq: int, backend=None):
     merge, ranks in ascending order."""
     R, N, W = parts.shape
     D = W - 2
+    backend = backend or CudaBackend()
+    if hasattr(backend, "merge_packed"):
+        out, o32, lse = backend.merge_packed(parts.contiguous())
+        return {"out": out.view(B, Hq, D), "out_f32": o32.view(B, Hq, D), "lse": lse.view(B, Hq)}
     acc = parts[..., :D].contiguous()
     ml = parts[..., D:].contiguous()
-    out, o32, lse = (backend or CudaBackend()).merge(acc, ml)
+    out, o32, lse = backend.merge(acc, ml)
     return {"out": out.view(B, Hq, D), "out_f32": o32.view(B, Hq, D), "lse": lse.view(B, Hq)}
 
 
