@@ -293,6 +293,31 @@ def multi_gpu_cases(dev, rank, world, peak):
     cases.append({"case": f"sequence-sharded dense B=1 T={T} over {world} GPUs (all-gather of (m,l,acc) + merge)",
                   "us": round(us, 2), "GBps": round(gbs, 1), "frac_of_peak": round(gbs / (peak * world), 4),
                   "scaling": "strong", "note": "back-to-back steps, inputs larger than L2"})
+    # the same step with the exchange fused into one kernel over peer memory (no collective call)
+    try:
+        xchg = shard.PeerExchange(HQ, D)
+        fn2 = lambda: shard.decode_sequence_sharded(q, k, v, D ** -0.5, exchange=xchg)  # noqa: E731
+        a, b2 = fn(), fn2()
+        same = bool(torch.equal(a["out_f32"], b2["out_f32"]) and torch.equal(a["lse"], b2["lse"]))
+        for _ in range(5):
+            fn2()
+        dist.barrier()
+        torch.cuda.synchronize()
+        s.record()
+        for _ in range(iters):
+            fn2()
+        e.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([s.elapsed_time(e) * 1e3 / iters], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us2 = float(t)
+        gbs2 = kv_bytes(1, T) / (us2 * 1e-6) / 1e9
+        cases.append({"case": f"sequence-sharded dense B=1 T={T} over {world} GPUs, exchange + merge fused in one "
+                              "kernel over peer memory", "us": round(us2, 2), "GBps": round(gbs2, 1),
+                      "frac_of_peak": round(gbs2 / (peak * world), 4), "scaling": "strong",
+                      "bit_identical_to_all_gather_path": same, "status_word": int(K.ext().device_status())})
+    except Exception as ex:  # noqa: BLE001
+        cases.append({"case": "sequence-sharded, fused peer exchange", "error": str(ex)[:200]})
     del k, v
     # (a) batch 64 x 64k masked at 30 % stored blocks, 64/world sequences per GPU, no collective
     Bl = shard.batch_slice(64, rank, world)

@@ -189,6 +189,19 @@ int kvskip_launch_pack_partial(const float* out_f32, const float* lse, float* pa
 int kvskip_launch_merge_packed(const float* parts, int R, int64_t N, int D, uint16_t* out, float* out_f32, float* lse,
                                void* stream);
 
+/* Sequence shards, exchange and merge fused in one kernel over peer memory (no collective call).
+ * Every rank (one process per GPU, R <= 8) passes its normalised local result (out_f32 [N,D],
+ * lse [N]), the R peer-visible addresses of the ranks' exchange buffers (each 2*R*N*(D+2) floats)
+ * and flag arrays (each R*N uint32, zero before the first step), its rank, and a step number seq
+ * that is the same on every rank and grows by one per call (starting at 1).  Each row is stored
+ * into every rank's buffer with plain stores over NVLink, flagged, awaited and merged in ascending
+ * rank order; results equal kvskip_launch_merge_packed on the all-gathered buffers bit for bit.
+ * The wait is bounded (about a second); on expiry the device status word is set.  All ranks must
+ * call it for the same step: a rank that does not shows up as that timeout, not as a hang. */
+int kvskip_launch_exchange_merge(const float* out_f32, const float* lse, float* const* peer_bufs,
+                                 unsigned int* const* peer_flags, int rank, int R, int64_t N, int D, unsigned int seq,
+                                 uint16_t* out, float* res_f32, float* res_lse, void* stream);
+
 /* Token-index blocks of one decode step on the device (the reference builds them with torch ops,
  * src/lab.py:149-167): ids int64 [n, ids_stride], current token at T-1; out uint8 [n, NBC], a
  * block is marked if it holds an earlier copy of the current token or the position after one. */

@@ -354,4 +354,87 @@ __global__ void __launch_bounds__(D) merge_packed_kernel(const float* __restrict
   if (d == 0 && lse) lse[row] = l > 0.f ? (m + log2f(l)) * LN2 : -INFINITY;
 }
 
+// ---- sequence shards, exchange and merge in one kernel over peer memory ----------------------
+// One process per GPU.  Every rank owns a symmetric buffer [2][R][N][D+2] floats and a flag array
+// [R][N] (uint32), and knows the peers' addresses of both.  Row `row` of this rank's result is
+// packed and stored straight into slot [seq & 1][rank][row] of EVERY rank's buffer (plain stores
+// over NVLink), followed by a system-scope fence and the per-row flag flags[rank][row] = seq on
+// every rank; the same CTA then waits until all R flags of its row on ITS OWN array hold `seq` and
+// merges the R triples from its own buffer in ascending rank order (the arithmetic of
+// merge_packed_kernel, so the bits equal the all-gather path).  Two buffer sets alternate by the
+// parity of seq: a rank can be at most one step ahead of a peer, because finishing a step needs
+// the peer's flags of that step.  The wait is bounded; on expiry the status word is set and the
+// row is written from whatever arrived.
+constexpr int XCHG_MAX_RANKS = 8;
+struct XchgPeers {
+  float* buf[XCHG_MAX_RANKS];
+  unsigned int* flags[XCHG_MAX_RANKS];
+};
+
+template <int D>
+__global__ void __launch_bounds__(D) exchange_merge_kernel(const float* __restrict__ out_f32,
+                                                           const float* __restrict__ lse, const XchgPeers peers,
+                                                           int rank, int R, int64_t N, unsigned int seq,
+                                                           uint16_t* out, float* res_f32, float* res_lse) {
+  constexpr int W = D + 2;
+  const int64_t row = blockIdx.x;
+  const int d = threadIdx.x;
+  pdl_wait_prior();
+  const int64_t slot = ((static_cast<int64_t>(seq & 1u) * R + rank) * N + row) * W;
+  const float val = out_f32[row * D + d];
+  float mval = 0.f, lval = 0.f;
+  if (d == 0) {
+    const float x = lse[row];
+    mval = x == -INFINITY ? -INFINITY : x * LOG2E;
+    lval = x == -INFINITY ? 0.f : 1.f;
+  }
+  for (int r = 0; r < R; ++r) {
+    float* dst = peers.buf[r] + slot;
+    dst[d] = val;
+    if (d == 0) {
+      dst[D] = mval;
+      dst[D + 1] = lval;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (d < R) {
+    volatile unsigned int* f = peers.flags[d] + static_cast<int64_t>(rank) * N + row;
+    *f = seq;
+  }
+  // wait for the R flags of this row on this rank's own array
+  __shared__ int s_ok;
+  if (d == 0) s_ok = 1;
+  __syncthreads();
+  if (d < R) {
+    const volatile unsigned int* f = peers.flags[rank] + static_cast<int64_t>(d) * N + row;
+    bool got = false;
+    for (uint32_t it = 0; it < (1u << 21); ++it) {
+      if (*f == seq) { got = true; break; }
+      __nanosleep(100);
+    }
+    if (!got) {
+      s_ok = 0;
+      atomicCAS(&g_status, 0u, 0x500u + d);
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  const float* mine = peers.buf[rank] + (static_cast<int64_t>(seq & 1u) * R) * N * W;
+  float m = -INFINITY;
+  for (int r = 0; r < R; ++r) m = fmaxf(m, __ldcg(mine + (static_cast<int64_t>(r) * N + row) * W + D));
+  const float mu = (m == -INFINITY) ? 0.f : m;
+  float l = 0.f, acc = 0.f;
+  for (int r = 0; r < R; ++r) {
+    const float* pr = mine + (static_cast<int64_t>(r) * N + row) * W;
+    const float w = ex2(__ldcg(pr + D) - mu);
+    l += __ldcg(pr + D + 1) * w;
+    acc += __ldcg(pr + d) * w;
+  }
+  const float o32 = l > 0.f ? acc / l : 0.f;
+  if (out) reinterpret_cast<__nv_bfloat16*>(out)[row * D + d] = __float2bfloat16(o32);
+  if (res_f32) res_f32[row * D + d] = o32;
+  if (d == 0 && res_lse) res_lse[row] = l > 0.f ? (m + log2f(l)) * LN2 : -INFINITY;
+}
+
 }  // namespace kvb

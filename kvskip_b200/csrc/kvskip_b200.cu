@@ -505,6 +505,32 @@ int kvskip_launch_merge_packed(const float* parts, int R, int64_t N, int D, uint
   return KVSKIP_OK;
 }
 
+int kvskip_launch_exchange_merge(const float* out_f32, const float* lse, float* const* peer_bufs,
+                                 unsigned int* const* peer_flags, int rank, int R, int64_t N, int D, unsigned int seq,
+                                 uint16_t* out, float* res_f32, float* res_lse, void* stream) {
+  if (!out_f32 || !lse || !peer_bufs || !peer_flags) return fail(KVSKIP_E_ARG, "exchange_merge: null argument");
+  if (R < 1 || R > kvb::XCHG_MAX_RANKS || rank < 0 || rank >= R)
+    return fail(KVSKIP_E_LIMIT, "exchange_merge: 1..%d ranks", kvb::XCHG_MAX_RANKS);
+  if (N < 1 || N > 2147483647LL || seq == 0) return fail(KVSKIP_E_ARG, "exchange_merge: N >= 1, seq >= 1");
+  kvb::XchgPeers peers{};
+  for (int r = 0; r < R; ++r) {
+    if (!peer_bufs[r] || !peer_flags[r]) return fail(KVSKIP_E_ARG, "exchange_merge: null peer pointer");
+    peers.buf[r] = peer_bufs[r];
+    peers.flags[r] = peer_flags[r];
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (D == 128)
+    kvb::exchange_merge_kernel<128><<<static_cast<unsigned>(N), 128, 0, s>>>(out_f32, lse, peers, rank, R, N, seq, out,
+                                                                             res_f32, res_lse);
+  else if (D == 64)
+    kvb::exchange_merge_kernel<64><<<static_cast<unsigned>(N), 64, 0, s>>>(out_f32, lse, peers, rank, R, N, seq, out,
+                                                                           res_f32, res_lse);
+  else
+    return fail(KVSKIP_E_ARG, "kvskip: unsupported head dim");
+  KVB_CUDA(cudaGetLastError());
+  return KVSKIP_OK;
+}
+
 int kvskip_launch_index_blocks(const int64_t* ids, int64_t ids_stride, int n, int T, uint8_t* out, int NBC,
                                void* stream) {
   if (!ids || !out || n < 1 || T < 1) return fail(KVSKIP_E_ARG, "index_blocks: bad arguments");

@@ -414,6 +414,30 @@ std::vector<at::Tensor> merge_packed(const at::Tensor& parts) {
   return {out, out32, lse};
 }
 
+// Fused exchange + merge over peer memory; buf_ptrs / flag_ptrs are the peers' device addresses.
+std::vector<at::Tensor> exchange_merge(const at::Tensor& out_f32, const at::Tensor& lse,
+                                       const std::vector<int64_t>& buf_ptrs, const std::vector<int64_t>& flag_ptrs,
+                                       int64_t rank, int64_t seq) {
+  need_f32(out_f32, "out_f32"); need_f32(lse, "lse");
+  const int64_t D = out_f32.size(-1), N = out_f32.numel() / D, R = static_cast<int64_t>(buf_ptrs.size());
+  TORCH_CHECK(lse.numel() == N && flag_ptrs.size() == buf_ptrs.size() && R >= 1 && R <= 8, "exchange_merge arguments");
+  const c10::cuda::CUDAGuard guard(out_f32.device());
+  float* bufs[8];
+  unsigned int* flags[8];
+  for (int64_t r = 0; r < R; ++r) {
+    bufs[r] = reinterpret_cast<float*>(buf_ptrs[r]);
+    flags[r] = reinterpret_cast<unsigned int*>(flag_ptrs[r]);
+  }
+  at::Tensor out = at::empty({N, D}, out_f32.options().dtype(at::kBFloat16));
+  at::Tensor out32 = at::empty({N, D}, out_f32.options());
+  at::Tensor res_lse = at::empty({N}, out_f32.options());
+  raise_on(kvskip_launch_exchange_merge(out_f32.data_ptr<float>(), lse.data_ptr<float>(), bufs, flags,
+                                        static_cast<int>(rank), static_cast<int>(R), N, static_cast<int>(D),
+                                        static_cast<unsigned int>(seq), u16m(out), out32.data_ptr<float>(),
+                                        res_lse.data_ptr<float>(), cur_stream()));
+  return {out, out32, res_lse};
+}
+
 void index_blocks(const at::Tensor& ids, int64_t T, at::Tensor& out) {
   TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.dim() == 2 && ids.stride(1) == 1, "ids: CUDA int64 [n, >= T]");
   TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kByte && out.dim() == 2 && out.is_contiguous() &&
@@ -477,6 +501,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("pack_partial", &pack_partial, "rank-local (out_f32, lse) -> packed (acc, m, l) rows", py::arg("out_f32"),
         py::arg("lse"));
   m.def("merge_packed", &merge_packed, "merge of R packed partial buffers [R,N,D+2]", py::arg("parts"));
+  m.def("exchange_merge", &exchange_merge, "sequence shards: peer-memory exchange and merge in one kernel",
+        py::arg("out_f32"), py::arg("lse"), py::arg("buf_ptrs"), py::arg("flag_ptrs"), py::arg("rank"), py::arg("seq"));
   m.def("index_blocks", &index_blocks, "token-index blocks of one step", py::arg("ids"), py::arg("T"), py::arg("out"));
   m.def("set_option", &set_option, "process-wide option, e.g. (\"decode_path\", 1) for the exact-order kernels",
         py::arg("name"), py::arg("value"));

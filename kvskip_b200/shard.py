@@ -101,11 +101,49 @@ def merge_partials(parts: torch.Tensor, B: int, Hq: int, backend=None):
     return {"out": out.view(B, Hq, D), "out_f32": o32.view(B, Hq, D), "lse": lse.view(B, Hq)}
 
 
-def decode_sequence_sharded(q, k_local, v_local, scale, plan=None, group=None, num_splits=None, backend=None):
+class PeerExchange:
+    """Exchange + merge of the per-rank triples in ONE kernel over peer memory, instead of pack ->
+    NCCL all-gather -> merge: every rank stores its rows straight into every rank's buffer over
+    NVLink, flags them, waits for its peers' flags (bounded) and merges.  Buffers come from
+    torch's symmetric memory (one allocation per rank, rendezvous once); results equal the
+    all-gather path bit for bit.  All ranks must call it once per step, in the same order."""
+
+    def __init__(self, n_rows: int, D: int, group=None, device=None):
+        import torch.distributed._symmetric_memory as symm
+        group = group or dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks")
+        device = device or torch.device("cuda", torch.cuda.current_device())
+        n_float = 2 * self.world * n_rows * (D + 2)
+        self.mem = symm.empty(n_float + self.world * n_rows, dtype=torch.float32, device=device)
+        self.mem.zero_()
+        handle = symm.rendezvous(self.mem, group)
+        ptrs = [int(p) for p in handle.buffer_ptrs]
+        self.buf_ptrs = ptrs
+        self.flag_ptrs = [p + 4 * n_float for p in ptrs]
+        self.n_rows, self.D, self.seq = n_rows, D, 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group)                       # every rank's flags are zero before anyone writes
+
+    def __call__(self, out_f32: torch.Tensor, lse: torch.Tensor):
+        self.seq += 1
+        return K.ext().exchange_merge(out_f32.reshape(self.n_rows, self.D), lse.reshape(self.n_rows),
+                                      self.buf_ptrs, self.flag_ptrs, self.rank, self.seq)
+
+
+def decode_sequence_sharded(q, k_local, v_local, scale, plan=None, group=None, num_splits=None, backend=None,
+                            exchange: "PeerExchange | None" = None):
     """One decode step with the sequence split over the ranks of `group`.  k_local / v_local
     hold this rank's block range; `plan` (optional) lists local block indices.  Every rank
-    returns the full result."""
+    returns the full result.  With `exchange` (a PeerExchange built once for this shape) the
+    triples travel by peer stores inside one kernel instead of an all-gather."""
     B, Hq = q.shape[0], q.shape[1]
+    if exchange is not None:
+        r = K.decode(q, k_local, v_local, scale, plan=plan, num_splits=num_splits, out_f32=True)
+        out, o32, lse = exchange(r["out_f32"], r["lse"])
+        D = o32.shape[-1]
+        return {"out": out.view(B, Hq, D), "out_f32": o32.view(B, Hq, D), "lse": lse.view(B, Hq)}
     part = local_partial(q, k_local, v_local, scale, plan=plan, num_splits=num_splits, backend=backend)
     world = dist.get_world_size(group)
     parts = torch.empty(world * part.shape[0], part.shape[1], dtype=part.dtype, device=part.device)

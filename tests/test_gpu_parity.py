@@ -454,3 +454,65 @@ def test_sequence_shards_emulated_on_one_gpu(R):
     assert torch.allclose(gotm["lse"].double().cpu(), refm["lse"], rtol=0, atol=2e-4)
     one = K.decode(qc, kc, vc, scale, out_f32=True)
     assert rel_err(got["out_f32"], one["out_f32"].double().cpu()) < 2e-5
+
+
+def test_exchange_merge_single_rank():
+    """The fused exchange kernel with one rank (its own buffer is the only peer): the merge of one
+    triple is the identity, step numbers alternate the buffer set, nothing times out."""
+    torch.manual_seed(5)
+    N, D = 32, 128
+    buf = torch.zeros(2 * N * (D + 2) + N, dtype=torch.float32, device=DEV)
+    bp, fp = [buf.data_ptr()], [buf.data_ptr() + 4 * 2 * N * (D + 2)]
+    for seq in (1, 2, 3):
+        o = torch.randn(N, D, device=DEV)
+        lse = torch.randn(N, device=DEV) * 3
+        lse[3] = float("-inf")
+        o[3] = 0
+        out, o32, l2 = K.ext().exchange_merge(o, lse, bp, fp, 0, seq)
+        assert torch.allclose(o32, o, rtol=2e-6, atol=1e-7) and torch.equal(out, o32.to(torch.bfloat16))
+        assert torch.allclose(l2[torch.isfinite(lse)], lse[torch.isfinite(lse)], rtol=0, atol=1e-5)
+        assert torch.isinf(l2[3]) and (o32[3] == 0).all()
+    assert K.ext().device_status() == 0
+
+
+def _xchg_rank(rank, world, port, ret):
+    import os
+    import torch.distributed as dist
+    from kvskip_b200 import shard
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        q, k, v, scale, keep = synth.sink_body_case(31, T=16384 + 77, B=2)
+        nb = keep.shape[-1]
+        lo, hi = shard.block_range(nb, rank, world)
+        qc = q.cuda()
+        kl, vl = k[:, :, lo * 64:hi * 64].cuda(), v[:, :, lo * 64:hi * 64].cuda()
+        xchg = shard.PeerExchange(2 * 32, 128)
+        ok = True
+        for step in range(4):
+            a = shard.decode_sequence_sharded(qc, kl, vl, scale)
+            b = shard.decode_sequence_sharded(qc, kl, vl, scale, exchange=xchg)
+            ok = ok and torch.equal(a["out_f32"], b["out_f32"]) and torch.equal(a["lse"], b["lse"])
+        if rank == 0:
+            ref = oracle.decode_f64(q, k, v, scale)
+            ret["err"] = rel_err(b["out_f32"], ref["out"])
+        ret[f"ok{rank}"] = bool(ok)
+        ret[f"status{rank}"] = int(K.ext().device_status())
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_exchange_merge_two_gpus_matches_all_gather():
+    """Two ranks on two GPUs: the fused peer-memory exchange gives the same bits as pack ->
+    all-gather -> merge, step after step, and the whole-sequence result matches the CPU oracle."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import os
+    import torch.multiprocessing as mp
+    ret = mp.Manager().dict()
+    mp.spawn(_xchg_rank, args=(2, 29700 + os.getpid() % 200, ret), nprocs=2, join=True)
+    assert ret["ok0"] and ret["ok1"], dict(ret)
+    assert ret["status0"] == 0 and ret["status1"] == 0
+    assert ret["err"] < TOL_F32
