@@ -87,7 +87,8 @@ __device__ __forceinline__ float quadcol_sum(float v) {
 
 template <bool MASKED, bool STATS, bool LOAD_V>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* __restrict__ split_done) {
+decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* __restrict__ split_done,
+                 const int min_blocks) {
   using Cfg = TcCfg<LOAD_V>;
   constexpr int G = 4, D = 128;
   constexpr int S = Cfg::kStages;
@@ -127,7 +128,16 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
   } else {
     n_items = (p.T + TILE - 1) / TILE;
   }
-  const int per = (n_items + p.num_splits - 1) / p.num_splits;
+  // Splits actually used for this (batch, kv head).  A block list can be much shorter than the
+  // length the grid was sized for (a head that does not refresh reads a tenth of the blocks a
+  // refreshing one reads): with the merge inside the kernel the list is cut into at most
+  // ceil(n_items / min_blocks) pieces and the surplus CTAs leave at once, instead of every CTA
+  // paying its fixed cost for a handful of blocks.
+  int S_use = p.num_splits;
+  if (MASKED && LOAD_V && split_done != nullptr && min_blocks > 1)
+    S_use = max(1, min(p.num_splits, (n_items + min_blocks - 1) / min_blocks));
+  if (split >= S_use) return;
+  const int per = (n_items + S_use - 1) / S_use;
   const int i0 = min(n_items, split * per);
   const int n = min(n_items, i0 + per) - i0;
 
@@ -357,7 +367,7 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
         l += sL[w * 4 + g] * f;
       }
       const int64_t hq = static_cast<int64_t>(b) * p.Hq + h * G + g;
-      if (p.num_splits == 1) {
+      if (S_use == 1) {
         const float o32 = l > 0.f ? sum / l : 0.f;
         reinterpret_cast<__nv_bfloat16*>(p.out)[hq * D + d] = __float2bfloat16(o32);
         if (p.out_f32) p.out_f32[hq * D + d] = o32;
@@ -373,7 +383,7 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
     float l = 0.f;
     for (int w = 0; w < NC; ++w) l += sL[w * 4 + tid] * ex2(sM[w * 4 + tid] - mu);
     const int64_t hq = static_cast<int64_t>(b) * p.Hq + h * G + tid;
-    if (p.num_splits == 1) {
+    if (S_use == 1) {
       if (p.lse) p.lse[hq] = l > 0.f ? (M + log2f(l)) * LN2 : -INFINITY;
     } else {
       p.part_ml[(hq * p.num_splits + split) * 2] = M;
@@ -385,19 +395,19 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
   // same ascending-split order as merge_kernel, without a second launch.  split_done[] counts the
   // finished splits and is put back to zero by the CTA that merges.
   if constexpr (LOAD_V) {
-    if (p.num_splits > 1 && split_done != nullptr) {
+    if (S_use > 1 && split_done != nullptr) {
       __shared__ int s_last;
       __threadfence();            // this CTA's partials are visible device-wide before it is counted
       __syncthreads();
-      if (tid == 0) s_last = atomicAdd(&split_done[b * p.Hkv + h], 1) == p.num_splits - 1;
+      if (tid == 0) s_last = atomicAdd(&split_done[b * p.Hkv + h], 1) == S_use - 1;
       __syncthreads();
       if (s_last) {
         __threadfence();
-        const int S2 = p.num_splits;
+        const int S2 = S_use;             // partials used; their stride stays p.num_splits
         for (int o = tid; o < G * D; o += TC_THREADS) {
           const int g = o / D, d = o % D;
           const int64_t hq = static_cast<int64_t>(b) * p.Hq + h * G + g;
-          const float* ml = p.part_ml + hq * S2 * 2;
+          const float* ml = p.part_ml + hq * p.num_splits * 2;
           float m = -INFINITY;
           for (int s2 = 0; s2 < S2; ++s2) m = fmaxf(m, __ldcg(ml + 2 * s2));
           const float mu = (m == -INFINITY) ? 0.f : m;
@@ -405,7 +415,7 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
           for (int s2 = 0; s2 < S2; ++s2) {
             const float w = ex2(__ldcg(ml + 2 * s2) - mu);
             l += __ldcg(ml + 2 * s2 + 1) * w;
-            a += __ldcg(p.part_acc + (hq * S2 + s2) * D + d) * w;
+            a += __ldcg(p.part_acc + (hq * p.num_splits + s2) * D + d) * w;
           }
           const float o32 = l > 0.f ? a / l : 0.f;
           reinterpret_cast<__nv_bfloat16*>(p.out)[hq * D + d] = __float2bfloat16(o32);

@@ -201,8 +201,15 @@ int launch_tc(const kvskip_params& p, cudaStream_t stream) {
   int* done = nullptr;
   if (LOAD_V && p.num_splits > 1)
     if (int rc = split_done_region(p.B * p.Hkv, &done)) return rc;
+  // with more CTAs than SMs, a short block list is cut into pieces of at least this many blocks
+  int sms = 148;
+  {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int min_blocks = (static_cast<int64_t>(p.num_splits) * p.Hkv * p.B > sms) ? 24 : 1;
   KVB_CUDA(launch_overlapped(kernel, dim3(p.num_splits, p.Hkv, p.B), dim3(kvb::TC_THREADS), Cfg::kSmemBytes, stream, p,
-                             maps, done));
+                             maps, done, min_blocks));
   if (LOAD_V && p.num_splits > 1 && done == nullptr) {
     kvb::merge_kernel<128><<<p.B * p.Hq, 128, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits,
                                                           static_cast<int64_t>(p.B) * p.Hq, true, p.out, p.out_f32,

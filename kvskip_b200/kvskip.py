@@ -104,6 +104,17 @@ def make_plan(keep: torch.Tensor, sync: bool = True) -> Plan:
     return Plan(order, cnt, int(cnt.max()) if sync else nb, nb)
 
 
+def splits_for_unsynced_plan(bh: int, nb: int) -> int:
+    """Split count for a block list whose true lengths are not known on the host (sized for nb).
+    The tensor-core kernel cuts every list into pieces of >= 24 blocks and lets surplus CTAs leave
+    at once, so at small batch it pays to provision enough splits for a head that reads every block
+    to spread over many SMs; at larger batch the grid is several waves anyway."""
+    base = num_splits_for(bh, nb)
+    if bh * base <= 2 * num_sms():
+        return min(64, max(base, -(-nb // 24)))
+    return base
+
+
 def _q3(q):
     return q.squeeze(2) if q.dim() == 4 else q
 
@@ -118,7 +129,10 @@ def decode(q, k, v, scale: float, *, plan: Plan | None = None, stats: bool = Fal
         n_items = math.ceil(T / TILE) if plan is None else plan.max_cnt
         # the tensor-core kernel owns an SM; three CTAs of the exact-order kernel share one
         per_sm = 1 if (q.shape[-1] == 128 and ext().get_option("decode_path") != 1) else 3
-        num_splits = num_splits_for(B * Hkv, n_items, sms=per_sm * num_sms())
+        if plan is not None and per_sm == 1 and plan.max_cnt == plan.nb and load_v:
+            num_splits = splits_for_unsynced_plan(B * Hkv, n_items)
+        else:
+            num_splits = num_splits_for(B * Hkv, n_items, sms=per_sm * num_sms())
     bi, bc = (None, None) if plan is None else (plan.block_idx, plan.block_cnt)
     out, lse, bmax, bsum, o32, pbuf = ext().decode(q, k, v, float(scale), bi, bc, stats, load_v,
                                                    int(num_splits), int(stages), out_f32, write_p)

@@ -185,7 +185,7 @@ class RefreshLayer:
         kind = CALIB_KINDS[cfg.calib_kind]
         auto = cfg.calib_auto_ix is not None
         if hasattr(self.ops, "fused_step"):
-            ns = K.num_splits_for(B * k.shape[1], nb)        # sized for every block: no host sync
+            ns = K.splits_for_unsynced_plan(B * k.shape[1], nb)   # sized for every block: no host sync
             out, lse, bmax, bsum = self.ops.fused_step(
                 q, k, v, s["csum"], s["lse_ref"], s["cs_ref"], s["keep"], s["lse_att"], s["age"], s["flags"],
                 s["cs_now"], s["trig"], s["block_idx"], s["block_cnt"], float(scale), float(cfg.delta),
