@@ -255,6 +255,7 @@ def single_gpu_cases(dev, peak):
                                        "peak calibration, auto index")
     planner_case(8, 8, 32768, 64, 8, "planner loop: 8 layers x 64 steps, batch 8, 32k context")
     planner_case(4, 8, 65536, 48, 8, "planner loop: 4 layers x 48 steps, batch 8, 64k context")
+    planner_case(3, 16, 65536, 40, 8, "planner loop: 3 layers x 40 steps, batch 16, 64k context")
     return cases
 
 

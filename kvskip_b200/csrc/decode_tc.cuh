@@ -38,13 +38,20 @@ constexpr int TC_CONSUMERS = 6;
 constexpr int TC_THREADS = (TC_CONSUMERS + 1) * 32;
 constexpr int TC_HALF_BYTES = TILE * 64 * 2;        // one TMA box: 64 tokens x 64 dims bf16 = 8 KB
 
-template <bool LOAD_V>
+// NC consumer warps and NC (K+V) or 2*NC (K only) stages.  NC = 6 fills an SM with one CTA (198 KB):
+// used when the grid is a single wave.  NC = 3 is half of that, two CTAs per SM: used when the grid
+// has more CTAs than SMs, so that while one CTA of an SM sets up, drains or merges, the other one
+// streams -- the fixed cost of a CTA (about 6 us: launch, first TMA round trip, merge, fence and
+// counter) is as long as streaming 9 blocks, and block lists of a refresh step are short.
+template <int NC, bool LOAD_V>
 struct TcCfg {
+  static constexpr int kThreads = (NC + 1) * 32;
   static constexpr int kStageBytes = TC_HALF_BYTES * (LOAD_V ? 4 : 2);
-  static constexpr int kStages = LOAD_V ? 6 : 12;
-  static constexpr int kRedBytes = TC_CONSUMERS * 4 * 128 * 4;     // epilogue staging, aliases the ring
-  static constexpr int kAuxBytes = TC_CONSUMERS * 8 * 4 + 2 * kStages * 8;
-  static_assert(kStages % TC_CONSUMERS == 0, "a stage must always be consumed by the same warp");
+  static constexpr int kStages = LOAD_V ? NC : 2 * NC;
+  static constexpr int kRedBytes = NC * 4 * 128 * 4;               // epilogue staging, aliases the ring
+  static constexpr int kAuxBytes = NC * 8 * 4 + 2 * kStages * 8;
+  static_assert(kStages % NC == 0, "a stage must always be consumed by the same warp");
+  static_assert(kRedBytes <= kStages * kStageBytes, "epilogue staging fits in the ring");
   static constexpr int kSmemBytes = kStages * kStageBytes + kAuxBytes + 1024 /* alignment slack */;
 };
 
@@ -85,14 +92,165 @@ __device__ __forceinline__ float quadcol_sum(float v) {
   return v + __shfl_xor_sync(0xffffffffu, v, 16);
 }
 
-template <bool MASKED, bool STATS, bool LOAD_V>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+// ---- one 64-token block for one consumer warp: scores, online softmax (+ statistics), output.
+// kbase: shared-memory address of the stage (K halves, then V halves); state in m_run / l_run / acc.
+template <bool STATS, bool LOAD_V>
+__device__ __forceinline__ void tc_block(const kvskip_params& p, const uint32_t kbase, const uint32_t (&bq)[8][2],
+                                         const int blk, const int64_t hq0, const int lane, float (&m_run)[2],
+                                         float (&l_run)[2], float (&acc)[8][4]) {
+  const int lrow = lane & 7, lmat = lane >> 3;
+  const bool col_ok = (lane & 3) < 2;          // this thread's two columns are real heads
+  const int head0 = 2 * (lane & 3);
+  const int t0 = blk * TILE;
+  // ---- S^T = K Q^T: 4 tiles of 16 tokens x 8 heads
+  float sc[4][4];
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) sc[mt][c] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    const uint32_t hbase = kbase + (ks >> 2) * TC_HALF_BYTES;
+    const int chunk = (ks & 3) * 2 + (lmat >> 1);
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt) {
+      const int row = mt * 16 + (lmat & 1) * 8 + lrow;
+      uint32_t a[4];
+      ldsm_x4(a, hbase + row * 128 + ((chunk ^ lrow) << 4));
+      mma_bf16(sc[mt], a, bq[ks][0], bq[ks][1]);
+    }
+  }
+  // scale to log2 units, mask the tokens past T (last block only)
+  const bool ragged = t0 + TILE > p.T;
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      float v = sc[mt][c] * p.scale_log2;
+      if (ragged && t0 + mt * 16 + (lane >> 2) + (c >> 1) * 8 >= p.T) v = -INFINITY;
+      sc[mt][c] = v;
+    }
+  // ---- online softmax, two heads per thread
+  float mb[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    float v = fmaxf(sc[0][e], sc[0][e + 2]);
+#pragma unroll
+    for (int mt = 1; mt < 4; ++mt) v = fmaxf(v, fmaxf(sc[mt][e], sc[mt][e + 2]));
+    mb[e] = quadcol_max(v);
+  }
+  float alpha[2], mu[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const float m_new = fmaxf(m_run[e], mb[e]);
+    mu[e] = (m_new == -INFINITY) ? 0.f : m_new;
+    alpha[e] = ex2(m_run[e] - mu[e]);
+    m_run[e] = m_new;
+  }
+  if constexpr (STATS) {
+    float es[2] = {0.f, 0.f};
+    const float mtu[2] = {mb[0] == -INFINITY ? 0.f : mb[0], mb[1] == -INFINITY ? 0.f : mb[1]};
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float ev = ex2(sc[mt][c] - mtu[c & 1]);
+        es[c & 1] += ev;
+        if (p.p_out && col_ok) {
+          __half* po = reinterpret_cast<__half*>(p.p_out) + (hq0 + head0 + (c & 1)) * p.t_pad + t0;
+          po[mt * 16 + (lane >> 2) + (c >> 1) * 8] = __float2half_rn(ev);
+        }
+      }
+    es[0] = quadcol_sum(es[0]);
+    es[1] = quadcol_sum(es[1]);
+    if (lane < 2) {   // lanes 0 and 1 hold heads (0,1) and (2,3)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        p.blk_max[(hq0 + head0 + e) * p.nb + blk] = mb[e] * LN2;
+        p.blk_sum[(hq0 + head0 + e) * p.nb + blk] = es[e];
+      }
+    }
+  }
+  float ls[2] = {0.f, 0.f};
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const float pv = ex2(sc[mt][c] - mu[c & 1]);
+      sc[mt][c] = pv;
+      ls[c & 1] += pv;
+    }
+  l_run[0] = l_run[0] * alpha[0] + ls[0];
+  l_run[1] = l_run[1] * alpha[1] + ls[1];
+
+  if constexpr (LOAD_V) {
+    // ---- O^T = alpha * O^T + V^T P^T
+    if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt) {
+        acc[mt][0] *= alpha[0]; acc[mt][1] *= alpha[1];
+        acc[mt][2] *= alpha[0]; acc[mt][3] *= alpha[1];
+      }
+    }
+    const uint32_t vbase = kbase + 2 * TC_HALF_BYTES;
+#pragma unroll
+    for (int kt = 0; kt < 4; ++kt) {
+      // P of tokens kt*16..+15 as high + low bf16 parts, transposed into the B layout
+      const uint32_t h0 = pack_bf16(sc[kt][0], sc[kt][1]);
+      const uint32_t h1 = pack_bf16(sc[kt][2], sc[kt][3]);
+      const uint32_t l0 = pack_bf16(sc[kt][0] - bf_lo(h0), sc[kt][1] - bf_hi(h0));
+      const uint32_t l1 = pack_bf16(sc[kt][2] - bf_lo(h1), sc[kt][3] - bf_hi(h1));
+      const uint32_t bh0 = movm_t(h0), bh1 = movm_t(h1), bl0 = movm_t(l0), bl1 = movm_t(l1);
+      const int tok = kt * 16 + (lmat >> 1) * 8 + lrow;
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt) {
+        const int dchunk = mt * 2 + (lmat & 1);
+        uint32_t a[4];
+        ldsm_x4_t(a, vbase + (dchunk >> 3) * TC_HALF_BYTES + tok * 128 + (((dchunk & 7) ^ lrow) << 4));
+        mma_bf16(acc[mt], a, bh0, bh1);
+        mma_bf16(acc[mt], a, bl0, bl1);
+      }
+    }
+  }
+}
+
+// Q^T as the B operand of the score MMA: column n = lane/4 is a head (4..7 are zero padding),
+// rows k = 2*(lane%4)+{0,1} (+8) of each 16-dim step
+__device__ __forceinline__ void tc_load_q(const kvskip_params& p, const int b, const int h, const int lane,
+                                          uint32_t (&bq)[8][2]) {
+  const int head = lane >> 2;
+  const uint16_t* qp = p.q + b * p.q_sb + (h * 4 + (head & 3)) * p.q_sh + 2 * (lane & 3);
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    bq[ks][0] = head < 4 ? *reinterpret_cast<const uint32_t*>(qp + ks * 16) : 0u;
+    bq[ks][1] = head < 4 ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8) : 0u;
+  }
+}
+
+// Statistics of the blocks a list skips: -inf / 0 between the previous listed block and this one
+// (the last item also covers the tail), so the caller need not pre-fill the arrays.
+__device__ __forceinline__ void tc_fill_gap(const kvskip_params& p, const int32_t* list, const int pos,
+                                            const int n_items, const int blk, const int64_t hq0, const int lane) {
+  const int prev = pos > 0 ? list[pos - 1] : -1;
+  const int next = (pos + 1 == n_items) ? p.nb : blk;
+  for (int gblk = prev + 1 + lane; gblk < next; gblk += 32) {
+    if (gblk == blk) continue;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      p.blk_max[(hq0 + g) * p.nb + gblk] = -INFINITY;
+      p.blk_sum[(hq0 + g) * p.nb + gblk] = 0.f;
+    }
+  }
+}
+
+template <int NC, bool MASKED, bool STATS, bool LOAD_V>
+__global__ void __launch_bounds__((NC + 1) * 32, NC <= 3 ? 2 : 1)
 decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* __restrict__ split_done,
                  const int min_blocks) {
-  using Cfg = TcCfg<LOAD_V>;
+  using Cfg = TcCfg<NC, LOAD_V>;
   constexpr int G = 4, D = 128;
   constexpr int S = Cfg::kStages;
-  constexpr int NC = TC_CONSUMERS;
+  constexpr int TC_THREADS = Cfg::kThreads;   // shadows the 6-consumer constant inside this kernel
 
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -170,154 +328,19 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
     }
   } else {
     // ------------------------------------------------------------------ consumers
-    // Q^T as the B operand of the score MMA: column n = lane/4 is a head (4..7 are zero padding),
-    // rows k = 2*(lane%4)+{0,1} (+8) of each 16-dim step
     uint32_t bq[8][2];
-    {
-      const int head = lane >> 2;
-      const uint16_t* qp = p.q + b * p.q_sb + (h * G + (head & 3)) * p.q_sh + 2 * (lane & 3);
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        bq[ks][0] = head < G ? *reinterpret_cast<const uint32_t*>(qp + ks * 16) : 0u;
-        bq[ks][1] = head < G ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8) : 0u;
-      }
-    }
-    const int lrow = lane & 7, lmat = lane >> 3;
+    tc_load_q(p, b, h, lane, bq);
     const int64_t hq0 = static_cast<int64_t>(b) * p.Hq + h * G;
-    const bool col_ok = (lane & 3) < 2;          // this thread's two columns are real heads
     const int head0 = 2 * (lane & 3);
 
     for (int i = warp; i < n; i += NC) {
       const int s = i % S;
       const int blk = MASKED ? list[i0 + i] : i0 + i;
-      const int t0 = blk * TILE;
-      if constexpr (MASKED && STATS) {
-        // statistics of the blocks this list skips: -inf / 0 between the previous listed block and
-        // this one (and after the last listed block), so the caller need not pre-fill the arrays
-        const int prev = (i0 + i) > 0 ? list[i0 + i - 1] : -1;
-        const int next = (i0 + i + 1 == n_items) ? p.nb : blk;   // last item also covers the tail
-        for (int gblk = prev + 1 + lane; gblk < next; gblk += 32) {
-          if (gblk == blk) continue;
-#pragma unroll
-          for (int g = 0; g < G; ++g) {
-            p.blk_max[(hq0 + g) * p.nb + gblk] = -INFINITY;
-            p.blk_sum[(hq0 + g) * p.nb + gblk] = 0.f;
-          }
-        }
-      }
+      if constexpr (MASKED && STATS) tc_fill_gap(p, list, i0 + i, n_items, blk, hq0, lane);
       if (!mbar_wait(&full[s], (i / S) & 1, 0x210u + s)) break;
       const uint32_t kbase = smem_u32(ring + s * Cfg::kStageBytes);
 
-      // ---- S^T = K Q^T: 4 tiles of 16 tokens x 8 heads
-      float sc[4][4];
-#pragma unroll
-      for (int mt = 0; mt < 4; ++mt)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) sc[mt][c] = 0.f;
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint32_t hbase = kbase + (ks >> 2) * TC_HALF_BYTES;
-        const int chunk = (ks & 3) * 2 + (lmat >> 1);
-#pragma unroll
-        for (int mt = 0; mt < 4; ++mt) {
-          const int row = mt * 16 + (lmat & 1) * 8 + lrow;
-          uint32_t a[4];
-          ldsm_x4(a, hbase + row * 128 + ((chunk ^ lrow) << 4));
-          mma_bf16(sc[mt], a, bq[ks][0], bq[ks][1]);
-        }
-      }
-      // scale to log2 units, mask the tokens past T (last block only)
-      const bool ragged = t0 + TILE > p.T;
-#pragma unroll
-      for (int mt = 0; mt < 4; ++mt)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          float v = sc[mt][c] * p.scale_log2;
-          if (ragged && t0 + mt * 16 + (lane >> 2) + (c >> 1) * 8 >= p.T) v = -INFINITY;
-          sc[mt][c] = v;
-        }
-      // ---- online softmax, two heads per thread
-      float mb[2];
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        float v = fmaxf(sc[0][e], sc[0][e + 2]);
-#pragma unroll
-        for (int mt = 1; mt < 4; ++mt) v = fmaxf(v, fmaxf(sc[mt][e], sc[mt][e + 2]));
-        mb[e] = quadcol_max(v);
-      }
-      float alpha[2], mu[2];
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const float m_new = fmaxf(m_run[e], mb[e]);
-        mu[e] = (m_new == -INFINITY) ? 0.f : m_new;
-        alpha[e] = ex2(m_run[e] - mu[e]);
-        m_run[e] = m_new;
-      }
-      if constexpr (STATS) {
-        float es[2] = {0.f, 0.f};
-        const float mtu[2] = {mb[0] == -INFINITY ? 0.f : mb[0], mb[1] == -INFINITY ? 0.f : mb[1]};
-#pragma unroll
-        for (int mt = 0; mt < 4; ++mt)
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const float ev = ex2(sc[mt][c] - mtu[c & 1]);
-            es[c & 1] += ev;
-            if (p.p_out && col_ok) {
-              __half* po = reinterpret_cast<__half*>(p.p_out) + (hq0 + head0 + (c & 1)) * p.t_pad + t0;
-              po[mt * 16 + (lane >> 2) + (c >> 1) * 8] = __float2half_rn(ev);
-            }
-          }
-        es[0] = quadcol_sum(es[0]);
-        es[1] = quadcol_sum(es[1]);
-        if (lane < 2) {   // lanes 0 and 1 hold heads (0,1) and (2,3)
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            p.blk_max[(hq0 + head0 + e) * p.nb + blk] = mb[e] * LN2;
-            p.blk_sum[(hq0 + head0 + e) * p.nb + blk] = es[e];
-          }
-        }
-      }
-      float ls[2] = {0.f, 0.f};
-#pragma unroll
-      for (int mt = 0; mt < 4; ++mt)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const float pv = ex2(sc[mt][c] - mu[c & 1]);
-          sc[mt][c] = pv;
-          ls[c & 1] += pv;
-        }
-      l_run[0] = l_run[0] * alpha[0] + ls[0];
-      l_run[1] = l_run[1] * alpha[1] + ls[1];
-
-      if constexpr (LOAD_V) {
-        // ---- O^T = alpha * O^T + V^T P^T
-        if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
-#pragma unroll
-          for (int mt = 0; mt < 8; ++mt) {
-            acc[mt][0] *= alpha[0]; acc[mt][1] *= alpha[1];
-            acc[mt][2] *= alpha[0]; acc[mt][3] *= alpha[1];
-          }
-        }
-        const uint32_t vbase = kbase + 2 * TC_HALF_BYTES;
-#pragma unroll
-        for (int kt = 0; kt < 4; ++kt) {
-          // P of tokens kt*16..+15 as high + low bf16 parts, transposed into the B layout
-          const uint32_t h0 = pack_bf16(sc[kt][0], sc[kt][1]);
-          const uint32_t h1 = pack_bf16(sc[kt][2], sc[kt][3]);
-          const uint32_t l0 = pack_bf16(sc[kt][0] - bf_lo(h0), sc[kt][1] - bf_hi(h0));
-          const uint32_t l1 = pack_bf16(sc[kt][2] - bf_lo(h1), sc[kt][3] - bf_hi(h1));
-          const uint32_t bh0 = movm_t(h0), bh1 = movm_t(h1), bl0 = movm_t(l0), bl1 = movm_t(l1);
-          const int tok = kt * 16 + (lmat >> 1) * 8 + lrow;
-#pragma unroll
-          for (int mt = 0; mt < 8; ++mt) {
-            const int dchunk = mt * 2 + (lmat & 1);
-            uint32_t a[4];
-            ldsm_x4_t(a, vbase + (dchunk >> 3) * TC_HALF_BYTES + tok * 128 + (((dchunk & 7) ^ lrow) << 4));
-            mma_bf16(acc[mt], a, bh0, bh1);
-            mma_bf16(acc[mt], a, bl0, bl1);
-          }
-        }
-      }
+      tc_block<STATS, LOAD_V>(p, kbase, bq, blk, hq0, lane, m_run, l_run, acc);
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);
     }

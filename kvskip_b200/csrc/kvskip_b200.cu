@@ -163,6 +163,7 @@ constexpr int kMergeRegion = 4096;
 constexpr int kMergeRegions = 16;
 __device__ int g_split_done[kMergeRegion * kMergeRegions];
 std::atomic<unsigned> g_merge_seq{0};
+std::atomic<int> g_half_cta{1};
 
 int split_done_region(int units, int** out) {
   static std::mutex mu;
@@ -184,11 +185,18 @@ int split_done_region(int units, int** out) {
   return KVSKIP_OK;
 }
 
+template <int NC, bool MASKED, bool STATS, bool LOAD_V>
+int launch_tc_nc(const kvskip_params& p, const kvb::TmaMaps& maps, int* done, int min_blocks, cudaStream_t stream) {
+  using Cfg = kvb::TcCfg<NC, LOAD_V>;
+  auto kernel = kvb::decode_tc_kernel<NC, MASKED, STATS, LOAD_V>;
+  if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes)) return rc;
+  KVB_CUDA(launch_overlapped(kernel, dim3(p.num_splits, p.Hkv, p.B), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, p,
+                             maps, done, min_blocks));
+  return KVSKIP_OK;
+}
+
 template <bool MASKED, bool STATS, bool LOAD_V>
 int launch_tc(const kvskip_params& p, cudaStream_t stream) {
-  using Cfg = kvb::TcCfg<LOAD_V>;
-  auto kernel = kvb::decode_tc_kernel<MASKED, STATS, LOAD_V>;
-  if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes)) return rc;
   kvb::TmaMaps maps;
   if (int rc = make_kv_map(&maps.k, p.k, p.k_sb, p.k_sh, p.k_st, p.B, p.Hkv, p.T, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
@@ -198,18 +206,22 @@ int launch_tc(const kvskip_params& p, cudaStream_t stream) {
   } else {
     maps.v = maps.k;
   }
-  int* done = nullptr;
-  if (LOAD_V && p.num_splits > 1)
-    if (int rc = split_done_region(p.B * p.Hkv, &done)) return rc;
-  // with more CTAs than SMs, a short block list is cut into pieces of at least this many blocks
   int sms = 148;
   {
     int dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  const int min_blocks = (static_cast<int64_t>(p.num_splits) * p.Hkv * p.B > sms) ? 24 : 1;
-  KVB_CUDA(launch_overlapped(kernel, dim3(p.num_splits, p.Hkv, p.B), dim3(kvb::TC_THREADS), Cfg::kSmemBytes, stream, p,
-                             maps, done, min_blocks));
+  const int64_t total = static_cast<int64_t>(p.num_splits) * p.Hkv * p.B;
+  int* done = nullptr;
+  if (LOAD_V && p.num_splits > 1)
+    if (int rc = split_done_region(p.B * p.Hkv, &done)) return rc;
+  // with more CTAs than SMs: a short block list is cut into pieces of at least 24 blocks, and the
+  // half-size CTA (two per SM) is used so that set-up and merge of one overlap the other's streaming
+  const bool multi_wave = total > sms && g_half_cta.load(std::memory_order_relaxed);
+  const int min_blocks = (total > sms) ? 24 : 1;
+  if (int rc = multi_wave ? launch_tc_nc<3, MASKED, STATS, LOAD_V>(p, maps, done, min_blocks, stream)
+                          : launch_tc_nc<6, MASKED, STATS, LOAD_V>(p, maps, done, min_blocks, stream))
+    return rc;
   if (LOAD_V && p.num_splits > 1 && done == nullptr) {
     kvb::merge_kernel<128><<<p.B * p.Hq, 128, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits,
                                                           static_cast<int64_t>(p.B) * p.Hq, true, p.out, p.out_f32,
@@ -394,6 +406,10 @@ int kvskip_set_option(const char* name, int value) {
     g_decode_path.store(value, std::memory_order_relaxed);
     return KVSKIP_OK;
   }
+  if (!std::strcmp(name, "half_cta")) {
+    g_half_cta.store(value ? 1 : 0, std::memory_order_relaxed);
+    return KVSKIP_OK;
+  }
   if (!std::strcmp(name, "pdl")) {
     g_use_pdl.store(value ? 1 : 0, std::memory_order_relaxed);
     return KVSKIP_OK;
@@ -404,6 +420,7 @@ int kvskip_set_option(const char* name, int value) {
 int kvskip_get_option(const char* name) {
   if (name && !std::strcmp(name, "decode_path")) return g_decode_path.load(std::memory_order_relaxed);
   if (name && !std::strcmp(name, "pdl")) return g_use_pdl.load(std::memory_order_relaxed);
+  if (name && !std::strcmp(name, "half_cta")) return g_half_cta.load(std::memory_order_relaxed);
   return fail(KVSKIP_E_ARG, "unknown option");
 }
 
@@ -433,16 +450,14 @@ int kvskip_launch_plan(const kvskip_plan_params* p, void* stream) {
   if (((p->flags == nullptr)) || !p->csum || !p->keep || !p->block_idx || !p->block_cnt || !p->trig || !p->cs_now)
     return fail(KVSKIP_E_ARG, "plan: missing state tensor");
   if (p->B > 65535 || p->Hkv > 65535) return fail(KVSKIP_E_LIMIT, "B and Hkv are grid dims: at most 65535");
-  int* done = nullptr;
-  if (int rc = split_done_region(p->B * p->Hkv, &done)) return rc;
-  if (!done) return fail(KVSKIP_E_LIMIT, "plan: more than %d (batch, kv head) pairs per call", kMergeRegion);
   const int chunks = (nb + kvb::PL_CHUNK - 1) / kvb::PL_CHUNK;
   const int smem = (nb + 15) & ~15;   // attended flags of one head
   if (smem > 200 * 1024) return fail(KVSKIP_E_LIMIT, "plan: more than %d blocks", 200 * 1024);
   if (smem > 40 * 1024)
-    if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::plan_kernel), 200 * 1024)) return rc;
-  KVB_CUDA(launch_overlapped(kvb::plan_kernel, dim3(chunks, p->Hkv, p->B), dim3(kvb::PL_THREADS), smem,
-                             static_cast<cudaStream_t>(stream), *p, done));
+    if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::plan_decide_kernel), 200 * 1024)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  KVB_CUDA(launch_overlapped(kvb::plan_scores_kernel, dim3(chunks, p->Hkv, p->B), dim3(kvb::PL_THREADS), 0, s, *p));
+  KVB_CUDA(launch_overlapped(kvb::plan_decide_kernel, dim3(p->Hkv, p->B), dim3(kvb::PL_THREADS), smem, s, *p));
   return KVSKIP_OK;
 }
 
