@@ -154,7 +154,7 @@ def time_cuda(fn, iters, flush=None, warmup=3):
     return {"us": statistics.median(t), "us_p10": t[int(0.1 * len(t))], "us_p90": t[min(len(t) - 1, int(0.9 * len(t)))]}
 
 
-def single_gpu_cases(dev, peak):
+def single_gpu_cases(dev, peak, planner_only=False):
     """Other configurations of the path on one GPU (parity of each is covered by tests/)."""
     import torch
     from kvskip_b200 import kvskip as K
@@ -174,6 +174,14 @@ def single_gpu_cases(dev, peak):
                       **kw})
 
     g = torch.Generator(device=dev).manual_seed(2)
+    if not planner_only:
+        _attention_cases(dev, K, synth, g, add, flush)
+    _planner_cases(dev, peak, K, synth, RefreshConfig, RefreshLayer, cases)
+    return cases
+
+
+def _attention_cases(dev, K, synth, g, add, flush):
+    import torch
     # read ceiling of this GPU with the library's own streaming-read kernel
     x = torch.ones(2 * 2**30 // 2, dtype=torch.bfloat16, device=dev)
     o = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -209,6 +217,10 @@ def single_gpu_cases(dev, peak):
         time_cuda(lambda: K.vskip_one_pass(q, k, v, scale, tau=1e-4, lse_prev=lse), 30, flush),
         kv_bytes(1, T_HEAD, 0.5 * (1 + vk)), v_kept=round(vk, 4), bytes="all K + V of voted blocks")
     del q, k, v
+
+
+def _planner_cases(dev, peak, K, synth, RefreshConfig, RefreshLayer, cases):
+    import torch
     # planner loops: plan -> masked+stats attention -> update per layer and step, no host sync
     cfg = RefreshConfig(calib=0.05, calib_warm=(32, 8), calib_kind="peak", calib_auto_ix=0.1)
 
@@ -256,7 +268,6 @@ def single_gpu_cases(dev, peak):
     planner_case(8, 8, 32768, 64, 8, "planner loop: 8 layers x 64 steps, batch 8, 32k context")
     planner_case(4, 8, 65536, 48, 8, "planner loop: 4 layers x 48 steps, batch 8, 64k context")
     planner_case(3, 16, 65536, 40, 8, "planner loop: 3 layers x 40 steps, batch 16, 64k context")
-    return cases
 
 
 def multi_gpu_cases(dev, rank, world, peak):
@@ -360,6 +371,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cases", action="store_true", help="skip the additional configurations")
+    ap.add_argument("--planner-cases-only", action="store_true", help="of the additional configurations, run only "
+                    "the planner loops (development aid)")
     ap.add_argument("--batch", type=int, default=B_PER_GPU, help="sequences per GPU of the headline workload")
     ap.add_argument("--context", type=int, default=0, help="context length of a --profile --mode planner run")
     ap.add_argument("--profile", action="store_true",
@@ -522,7 +535,7 @@ def main():
         del k, v
         torch.cuda.empty_cache()
         if world == 1:
-            cases = single_gpu_cases(dev, peak)
+            cases = single_gpu_cases(dev, peak, args.planner_cases_only)
         else:
             cases = multi_gpu_cases(dev, rank, world, peak)
 

@@ -79,14 +79,12 @@ constexpr int PL_CHUNK = 32;   // blocks whose centroid scores one CTA computes 
 //                       list.  It is resident early and waits for the first kernel to finish.
 // The arithmetic of a score and of the fold is unchanged, only spread over more SMs: one CTA per
 // head reading nb * 512 bytes of key sums is latency-bound at long contexts.
-__global__ void __launch_bounds__(PL_THREADS) plan_scores_kernel(const kvskip_plan_params p) {
-  const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+// Centroid scores of one chunk of 32 blocks of (b, h) -> cs_now (and the new token into its key sum).
+__device__ __forceinline__ void pl_scores(const kvskip_plan_params& p, const int chunk, const int h, const int b) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nb = (p.T + TILE - 1) / TILE;
   const int64_t bh = static_cast<int64_t>(b) * p.Hkv + h;
   float* csum = p.csum + bh * p.NBC * PL_D;
-  pdl_wait_prior();          // the state this kernel reads may come from the previous kernel on the stream
-  pdl_launch_dependents();
   if (p.flags[h] & 2) return;   // token-index head: no scores, no key-sum update (plan_decide lists its blocks)
 
   const int blk0 = chunk * PL_CHUNK;
@@ -145,8 +143,8 @@ __global__ void __launch_bounds__(PL_THREADS) plan_scores_kernel(const kvskip_pl
   }
 }
 
-__global__ void __launch_bounds__(PL_THREADS) plan_decide_kernel(const kvskip_plan_params p) {
-  const int h = blockIdx.x, b = blockIdx.y;
+// Estimate fold, refresh decision and block list of (b, h), from the centroid scores in cs_now.
+__device__ __forceinline__ void pl_decide(const kvskip_plan_params& p, const int h, const int b) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nb = (p.T + TILE - 1) / TILE;
   const int64_t bh = static_cast<int64_t>(b) * p.Hkv + h;
@@ -156,8 +154,6 @@ __global__ void __launch_bounds__(PL_THREADS) plan_decide_kernel(const kvskip_pl
   __shared__ int scan[PL_THREADS];
   __shared__ float wM[PL_THREADS / 32][PL_G], wS[PL_THREADS / 32][PL_G];
   __shared__ int s_flag;
-  pdl_wait_prior();          // the centroid scores of plan_scores_kernel are complete and visible
-  pdl_launch_dependents();
 
   const int fl = p.flags[h];
   if (fl & 2) {   // token-index head: index blocks + sink + newest, never refreshes
@@ -270,6 +266,43 @@ __global__ void __launch_bounds__(PL_THREADS) plan_decide_kernel(const kvskip_pl
   }
   pl_compact(nb, bi, p.block_cnt + bh, scan, [&](int i) { return pl_att[i] != 0; });
 }
+
+__global__ void __launch_bounds__(PL_THREADS) plan_scores_kernel(const kvskip_plan_params p) {
+  pdl_wait_prior();          // the state this kernel reads may come from the previous kernel on the stream
+  pdl_launch_dependents();
+  pl_scores(p, blockIdx.x, blockIdx.y, blockIdx.z);
+}
+
+__global__ void __launch_bounds__(PL_THREADS) plan_decide_kernel(const kvskip_plan_params p) {
+  pdl_wait_prior();          // the centroid scores of plan_scores_kernel are complete and visible
+  pdl_launch_dependents();
+  pl_decide(p, blockIdx.x, blockIdx.y);
+}
+
+// The same in one launch: grid as plan_scores_kernel; the last CTA of a (batch, kv head) to finish
+// its scores (counted in done[], which it puts back to zero) goes on to decide.  One launch less,
+// at the price of a fence and an atomic in every CTA.
+__global__ void __launch_bounds__(PL_THREADS) plan_fused_kernel(const kvskip_plan_params p, int* __restrict__ done) {
+  const int h = blockIdx.y, b = blockIdx.z;
+  __shared__ int s_go;
+  pdl_wait_prior();
+  pdl_launch_dependents();
+  if (p.flags[h] & 2) {              // token-index head: one CTA lists its blocks, nothing to score
+    if (blockIdx.x == 0) pl_decide(p, h, b);
+    return;
+  }
+  pl_scores(p, blockIdx.x, h, b);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0)
+    s_go = atomicAdd(&done[b * p.Hkv + h], 1) == static_cast<int>(gridDim.x) - 1;
+  __syncthreads();
+  if (!s_go) return;
+  __threadfence();
+  if (threadIdx.x == 0) done[b * p.Hkv + h] = 0;
+  pl_decide(p, h, b);
+}
+
 
 __global__ void __launch_bounds__(PL_THREADS) update_kernel(const kvskip_update_params p) {
   const int h = blockIdx.x, b = blockIdx.y;
