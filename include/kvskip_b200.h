@@ -213,16 +213,13 @@ int kvskip_launch_index_blocks(const int64_t* ids, int64_t ids_stride, int n, in
  *                  1: exact-order kernel everywhere -- scores, block statistics and outputs are
  *                     bit-identical to the reference's kernels on the same GPU;
  *                  2: tensor-core kernel, error where it does not exist.
- *   "half_cta"     1 (default): when a tensor-core decode launch has at least four CTAs per SM of the
- *                  GPU it uses CTAs of half the size (3 consumer warps, 3 stages), two per SM, so the
+ *   "half_cta"     1 (default): when a dense (no block list) tensor-core decode launch has at least
+ *                  four CTAs per SM of the GPU it uses CTAs of half the size (3 consumer warps, 3 stages), two per SM, so the
  *                  set-up and merge of one overlap the streaming of the other; 0: always one
  *                  full-size CTA per SM.
  *   "pdl"          1 (default): the attention and planner kernels are launched with programmatic
  *                  stream serialisation, so their set-up overlaps the tail of the previous kernel
- *                  on the stream (they wait for it before reading memory); 0: plain launches.
- *   "plan_fused"   0 (default): kvskip_launch_plan is two launches, a streaming pass over the block
- *                  centroids and one CTA per head for the decision and the block list; 1: one launch,
- *                  the last CTA of a head to finish its centroids makes the decision.  Same results. */
+ *                  on the stream (they wait for it before reading memory); 0: plain launches. */
 int kvskip_set_option(const char* name, int value);
 int kvskip_get_option(const char* name);
 

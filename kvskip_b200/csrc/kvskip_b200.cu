@@ -164,7 +164,6 @@ constexpr int kMergeRegions = 16;
 __device__ int g_split_done[kMergeRegion * kMergeRegions];
 std::atomic<unsigned> g_merge_seq{0};
 std::atomic<int> g_half_cta{1};
-std::atomic<int> g_plan_fused{0};
 
 int split_done_region(int units, int** out) {
   static std::mutex mu;
@@ -216,10 +215,12 @@ int launch_tc(const kvskip_params& p, cudaStream_t stream) {
   int* done = nullptr;
   if (LOAD_V && p.num_splits > 1)
     if (int rc = split_done_region(p.B * p.Hkv, &done)) return rc;
-  // with more CTAs than SMs: a short block list is cut into pieces of at least 24 blocks, and the
-  // half-size CTA (two per SM) is used so that set-up and merge of one overlap the other's streaming
-  // (several waves of CTAs that really work: with a block list most of a small grid leaves at once)
-  const bool multi_wave = total >= 4 * static_cast<int64_t>(sms) && g_half_cta.load(std::memory_order_relaxed);
+  // With more CTAs than SMs a short block list is cut into pieces of at least 24 blocks.  A dense
+  // launch of four or more waves uses the half-size CTA (two per SM), so that set-up and merge of
+  // one overlap the other's streaming; with a block list, where many CTAs leave at once and the
+  // rest differ in length, the full-size CTA measured faster.
+  const bool multi_wave =
+      !MASKED && total >= 4 * static_cast<int64_t>(sms) && g_half_cta.load(std::memory_order_relaxed);
   const int min_blocks = (total > sms) ? 24 : 1;
   if (int rc = multi_wave ? launch_tc_nc<3, MASKED, STATS, LOAD_V>(p, maps, done, min_blocks, stream)
                           : launch_tc_nc<6, MASKED, STATS, LOAD_V>(p, maps, done, min_blocks, stream))
@@ -408,10 +409,6 @@ int kvskip_set_option(const char* name, int value) {
     g_decode_path.store(value, std::memory_order_relaxed);
     return KVSKIP_OK;
   }
-  if (!std::strcmp(name, "plan_fused")) {
-    g_plan_fused.store(value ? 1 : 0, std::memory_order_relaxed);
-    return KVSKIP_OK;
-  }
   if (!std::strcmp(name, "half_cta")) {
     g_half_cta.store(value ? 1 : 0, std::memory_order_relaxed);
     return KVSKIP_OK;
@@ -427,7 +424,6 @@ int kvskip_get_option(const char* name) {
   if (name && !std::strcmp(name, "decode_path")) return g_decode_path.load(std::memory_order_relaxed);
   if (name && !std::strcmp(name, "pdl")) return g_use_pdl.load(std::memory_order_relaxed);
   if (name && !std::strcmp(name, "half_cta")) return g_half_cta.load(std::memory_order_relaxed);
-  if (name && !std::strcmp(name, "plan_fused")) return g_plan_fused.load(std::memory_order_relaxed);
   return fail(KVSKIP_E_ARG, "unknown option");
 }
 
@@ -457,24 +453,16 @@ int kvskip_launch_plan(const kvskip_plan_params* p, void* stream) {
   if (((p->flags == nullptr)) || !p->csum || !p->keep || !p->block_idx || !p->block_cnt || !p->trig || !p->cs_now)
     return fail(KVSKIP_E_ARG, "plan: missing state tensor");
   if (p->B > 65535 || p->Hkv > 65535) return fail(KVSKIP_E_LIMIT, "B and Hkv are grid dims: at most 65535");
+  int* done = nullptr;
+  if (int rc = split_done_region(p->B * p->Hkv, &done)) return rc;
+  if (!done) return fail(KVSKIP_E_LIMIT, "plan: more than %d (batch, kv head) pairs per call", kMergeRegion);
   const int chunks = (nb + kvb::PL_CHUNK - 1) / kvb::PL_CHUNK;
   const int smem = (nb + 15) & ~15;   // attended flags of one head
   if (smem > 200 * 1024) return fail(KVSKIP_E_LIMIT, "plan: more than %d blocks", 200 * 1024);
   if (smem > 40 * 1024)
-    if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::plan_decide_kernel), 200 * 1024)) return rc;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  int* done = nullptr;
-  if (g_plan_fused.load(std::memory_order_relaxed))
-    if (int rc = split_done_region(p->B * p->Hkv, &done)) return rc;
-  if (done != nullptr) {
-    if (smem > 40 * 1024)
-      if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::plan_fused_kernel), 200 * 1024)) return rc;
-    KVB_CUDA(launch_overlapped(kvb::plan_fused_kernel, dim3(chunks, p->Hkv, p->B), dim3(kvb::PL_THREADS), smem, s, *p,
-                               done));
-    return KVSKIP_OK;
-  }
-  KVB_CUDA(launch_overlapped(kvb::plan_scores_kernel, dim3(chunks, p->Hkv, p->B), dim3(kvb::PL_THREADS), 0, s, *p));
-  KVB_CUDA(launch_overlapped(kvb::plan_decide_kernel, dim3(p->Hkv, p->B), dim3(kvb::PL_THREADS), smem, s, *p));
+    if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::plan_kernel), 200 * 1024)) return rc;
+  KVB_CUDA(launch_overlapped(kvb::plan_kernel, dim3(chunks, p->Hkv, p->B), dim3(kvb::PL_THREADS), smem,
+                             static_cast<cudaStream_t>(stream), *p, done));
   return KVSKIP_OK;
 }
 

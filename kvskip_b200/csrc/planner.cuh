@@ -70,22 +70,36 @@ __device__ __forceinline__ void pl_compact(int nb, int* bi, int* cnt, int* scan,
 
 constexpr int PL_CHUNK = 32;   // blocks whose centroid scores one CTA computes (4 warps x 8 in flight)
 
-// `plan` is two launches chained by programmatic dependent launch:
-//   plan_scores_kernel  grid (ceil(nb / PL_CHUNK), Hkv, B): every CTA adds the new token's key to its
-//                       block sum if that block is in its chunk, computes the centroid scores of
-//                       its 32 blocks and stores them to cs_now.  Pure streaming: no fence, no
-//                       counter, so a CTA lives for one memory round trip.
-//   plan_decide_kernel  grid (Hkv, B): folds the estimate from cs_now, decides, writes the block
-//                       list.  It is resident early and waits for the first kernel to finish.
+// grid (ceil(nb / PL_CHUNK), Hkv, B).  Every CTA computes the centroid scores of its chunk of
+// blocks and stores them to cs_now; the last CTA of a (batch, kv head) to finish (counted in
+// done[], which it puts back to zero) folds the estimate, decides and writes the block list.
 // The arithmetic of a score and of the fold is unchanged, only spread over more SMs: one CTA per
 // head reading nb * 512 bytes of key sums is latency-bound at long contexts.
-// Centroid scores of one chunk of 32 blocks of (b, h) -> cs_now (and the new token into its key sum).
-__device__ __forceinline__ void pl_scores(const kvskip_plan_params& p, const int chunk, const int h, const int b) {
+__global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_params p, int* __restrict__ done) {
+  const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nb = (p.T + TILE - 1) / TILE;
   const int64_t bh = static_cast<int64_t>(b) * p.Hkv + h;
   float* csum = p.csum + bh * p.NBC * PL_D;
-  if (p.flags[h] & 2) return;   // token-index head: no scores, no key-sum update (plan_decide lists its blocks)
+  const uint8_t* keep = p.keep + bh * p.NBC;
+  int* bi = p.block_idx + bh * p.NBC;
+  __shared__ int scan[PL_THREADS];
+  __shared__ float wM[PL_THREADS / 32][PL_G], wS[PL_THREADS / 32][PL_G];
+  __shared__ int s_flag;
+  pdl_wait_prior();          // the state this kernel reads may come from the previous kernel on the stream
+  pdl_launch_dependents();
+
+  const int fl = p.flags[h];
+  if (fl & 2) {   // token-index head: index blocks + sink + newest, never refreshes; one CTA does it
+    if (chunk != 0) return;
+    const uint8_t* ix = p.idx + static_cast<int64_t>(b) * p.NBC;
+    pl_compact(nb, bi, p.block_cnt + bh, scan, [&](int i) { return ix[i] || pl_always(i, nb, p.local); });
+    if (tid == 0) p.trig[bh] = 0;
+    return;
+  }
+  const bool uni = (fl & 4) || (p.aix && p.aix[bh]);
+  const uint8_t* ix = uni ? p.idx + static_cast<int64_t>(b) * p.NBC : nullptr;
+  auto attended = [&](int blk) { return keep[blk] || pl_always(blk, nb, p.local) || (uni && ix[blk]); };
 
   const int blk0 = chunk * PL_CHUNK;
   const int tok_blk = (p.T - 1) / TILE;
@@ -141,71 +155,33 @@ __device__ __forceinline__ void pl_scores(const kvskip_plan_params& p, const int
       p.cs_now[row0 + g * p.NBC + blk] = a[0] * inv_n;
     }
   }
-}
+  // count this chunk; only the last one of the head goes on
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_flag = atomicAdd(&done[bh], 1) == static_cast<int>(gridDim.x) - 1;
+  __syncthreads();
+  if (!s_flag) return;
+  __threadfence();
+  if (tid == 0) done[bh] = 0;
 
-// Estimate fold, refresh decision and block list of (b, h), from the centroid scores in cs_now.
-__device__ __forceinline__ void pl_decide(const kvskip_plan_params& p, const int h, const int b) {
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int nb = (p.T + TILE - 1) / TILE;
-  const int64_t bh = static_cast<int64_t>(b) * p.Hkv + h;
-  const uint8_t* keep = p.keep + bh * p.NBC;
-  int* bi = p.block_idx + bh * p.NBC;
-  const int64_t row0 = (static_cast<int64_t>(b) * p.Hq + h * PL_G) * p.NBC;
-  __shared__ int scan[PL_THREADS];
-  __shared__ float wM[PL_THREADS / 32][PL_G], wS[PL_THREADS / 32][PL_G];
-  __shared__ int s_flag;
-
-  const int fl = p.flags[h];
-  if (fl & 2) {   // token-index head: index blocks + sink + newest, never refreshes
-    const uint8_t* ix = p.idx + static_cast<int64_t>(b) * p.NBC;
-    pl_compact(nb, bi, p.block_cnt + bh, scan, [&](int i) { return ix[i] || pl_always(i, nb, p.local); });
-    if (tid == 0) p.trig[bh] = 0;
-    return;
-  }
-  const bool uni = (fl & 4) || (p.aix && p.aix[bh]);
-  const uint8_t* ix = uni ? p.idx + static_cast<int64_t>(b) * p.NBC : nullptr;
-
-  // Everything this CTA needs from global memory is requested in three batches of independent
-  // loads (scalars, membership bytes, fold operands): the kernel is a chain of memory round trips,
-  // so the number of dependent trips is what its time is made of.
-  extern __shared__ unsigned char pl_att[];   // [nb] attended flags
-  __shared__ float s_lse_att[PL_G];
-  __shared__ float s_calib;
-  __shared__ int s_age;
-  if (tid < PL_G) s_lse_att[tid] = p.lse_att[static_cast<int64_t>(b) * p.Hq + h * PL_G + tid];
-  if (tid == PL_G) s_calib = (p.calib && p.calib_on) ? p.calib[bh] : 0.f;
-  if (tid == PL_G + 1) s_age = p.age[bh];
-  constexpr int AU = 8;
-  for (int base = tid; base < nb; base += AU * PL_THREADS) {
-    uint8_t kv[AU], xv[AU];
-#pragma unroll
-    for (int j = 0; j < AU; ++j) {
-      const int i = base + j * PL_THREADS;
-      kv[j] = i < nb ? keep[i] : 0;
-      xv[j] = (uni && i < nb) ? ix[i] : 0;
-    }
-#pragma unroll
-    for (int j = 0; j < AU; ++j) {
-      const int i = base + j * PL_THREADS;
-      if (i < nb) pl_att[i] = (kv[j] || xv[j] || pl_always(i, nb, p.local)) ? 1 : 0;
-    }
-  }
+  // attended flags of every block into shared memory: independent, coalesced loads
+  extern __shared__ unsigned char pl_att[];   // [nb]
+  for (int i = tid; i < nb; i += PL_THREADS) pl_att[i] = attended(i) ? 1 : 0;
   __syncthreads();
 
   // 2. estimate of the mass outside the attended set: fold slot t takes blocks t, t+128, ...
-  // (operands of eight blocks are loaded before the dependent exp chain of the fold starts)
+  // (operands of four blocks are loaded before the dependent exp chain of the fold starts)
   float m[PL_G], s[PL_G];
 #pragma unroll
   for (int g = 0; g < PL_G; ++g) {
     m[g] = -INFINITY;
     s[g] = 0.f;
   }
-  constexpr int FU = 8;
-  for (int base = tid; base < nb; base += FU * PL_THREADS) {
-    float e[FU][PL_G];
-    bool use[FU];
+  for (int base = tid; base < nb; base += 4 * PL_THREADS) {
+    float e[4][PL_G];
+    bool use[4];
 #pragma unroll
-    for (int j = 0; j < FU; ++j) {
+    for (int j = 0; j < 4; ++j) {
       const int blk = base + j * PL_THREADS;
       use[j] = blk < nb && !pl_att[blk];
       if (use[j]) {
@@ -216,7 +192,7 @@ __device__ __forceinline__ void pl_decide(const kvskip_plan_params& p, const int
       }
     }
 #pragma unroll
-    for (int j = 0; j < FU; ++j)
+    for (int j = 0; j < 4; ++j)
       if (use[j]) {
 #pragma unroll
         for (int g = 0; g < PL_G; ++g) pl_fold(m[g], s[g], e[j][g]);
@@ -243,14 +219,14 @@ __device__ __forceinline__ void pl_decide(const kvskip_plan_params& p, const int
         if (wS[w][g] > 0.f) S += wS[w][g] * __expf(wM[w][g] - M);
       if (S > 0.f) {
         const float est = M + __logf(S);
-        miss = fmaxf(miss, 1.f / (1.f + __expf(s_lse_att[g] - est)));
+        miss = fmaxf(miss, 1.f / (1.f + __expf(p.lse_att[static_cast<int64_t>(b) * p.Hq + h * PL_G + g] - est)));
       }
     }
     if (p.est) p.est[bh] = miss;
     float dec = miss;
     if (p.calib && p.calib_on)
-      dec = p.calib_kind ? miss + s_calib : 1.f / (1.f + __expf(-(pl_logit(miss) + s_calib)));
-    const int a = s_age + 1;
+      dec = p.calib_kind ? miss + p.calib[bh] : 1.f / (1.f + __expf(-(pl_logit(miss) + p.calib[bh])));
+    const int a = p.age[bh] + 1;
     const bool tr = dec > p.delta || a >= p.max_age || (fl & 1);
     p.age[bh] = tr ? 0 : a;
     p.trig[bh] = tr ? 1 : 0;
@@ -266,43 +242,6 @@ __device__ __forceinline__ void pl_decide(const kvskip_plan_params& p, const int
   }
   pl_compact(nb, bi, p.block_cnt + bh, scan, [&](int i) { return pl_att[i] != 0; });
 }
-
-__global__ void __launch_bounds__(PL_THREADS) plan_scores_kernel(const kvskip_plan_params p) {
-  pdl_wait_prior();          // the state this kernel reads may come from the previous kernel on the stream
-  pdl_launch_dependents();
-  pl_scores(p, blockIdx.x, blockIdx.y, blockIdx.z);
-}
-
-__global__ void __launch_bounds__(PL_THREADS) plan_decide_kernel(const kvskip_plan_params p) {
-  pdl_wait_prior();          // the centroid scores of plan_scores_kernel are complete and visible
-  pdl_launch_dependents();
-  pl_decide(p, blockIdx.x, blockIdx.y);
-}
-
-// The same in one launch: grid as plan_scores_kernel; the last CTA of a (batch, kv head) to finish
-// its scores (counted in done[], which it puts back to zero) goes on to decide.  One launch less,
-// at the price of a fence and an atomic in every CTA.
-__global__ void __launch_bounds__(PL_THREADS) plan_fused_kernel(const kvskip_plan_params p, int* __restrict__ done) {
-  const int h = blockIdx.y, b = blockIdx.z;
-  __shared__ int s_go;
-  pdl_wait_prior();
-  pdl_launch_dependents();
-  if (p.flags[h] & 2) {              // token-index head: one CTA lists its blocks, nothing to score
-    if (blockIdx.x == 0) pl_decide(p, h, b);
-    return;
-  }
-  pl_scores(p, blockIdx.x, h, b);
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0)
-    s_go = atomicAdd(&done[b * p.Hkv + h], 1) == static_cast<int>(gridDim.x) - 1;
-  __syncthreads();
-  if (!s_go) return;
-  __threadfence();
-  if (threadIdx.x == 0) done[b * p.Hkv + h] = 0;
-  pl_decide(p, h, b);
-}
-
 
 __global__ void __launch_bounds__(PL_THREADS) update_kernel(const kvskip_update_params p) {
   const int h = blockIdx.x, b = blockIdx.y;
@@ -331,23 +270,10 @@ __global__ void __launch_bounds__(PL_THREADS) update_kernel(const kvskip_update_
   {  // set membership flags once, with independent coalesced loads, instead of a global load per fold step
     const bool uni = tr && p.calib && ((p.flags[h] & 4) || (p.aix && p.aix[bh]));
     const uint8_t* ix = uni ? p.idx + static_cast<int64_t>(b) * p.NBC : nullptr;
-    constexpr int AU = 8;
-    for (int base = tid; base < nb; base += AU * PL_THREADS) {
-      uint8_t kv[AU], xv[AU];
-#pragma unroll
-      for (int j = 0; j < AU; ++j) {
-        const int i = base + j * PL_THREADS;
-        kv[j] = i < nb ? keep[i] : 0;
-        xv[j] = (uni && i < nb) ? ix[i] : 0;
-      }
-#pragma unroll
-      for (int j = 0; j < AU; ++j) {
-        const int i = base + j * PL_THREADS;
-        if (i < nb) {
-          skeep[i] = 0;
-          sflag[i] = ((kv[j] || pl_always(i, nb, p.local)) ? 1 : 0) | (xv[j] ? 2 : 0);
-        }
-      }
+#pragma unroll 4
+    for (int i = tid; i < nb; i += PL_THREADS) {
+      skeep[i] = 0;
+      sflag[i] = ((keep[i] || pl_always(i, nb, p.local)) ? 1 : 0) | ((uni && ix[i]) ? 2 : 0);
     }
   }
   mx = warp_max(mx);
@@ -393,7 +319,6 @@ __global__ void __launch_bounds__(PL_THREADS) update_kernel(const kvskip_update_
     }
     for (int i = lane; i < nb; i += 32)
       if (x[i] - lse >= lo) skeep[i] = 1;
-#pragma unroll 4
     for (int i = lane; i < p.NBC; i += 32) {
       p.lse_ref[hrow * p.NBC + i] = i < nb ? x[i] : -INFINITY;
       p.cs_ref[hrow * p.NBC + i] = i < nb ? p.cs_now[hrow * p.NBC + i] : 0.f;

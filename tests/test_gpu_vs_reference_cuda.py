@@ -106,16 +106,8 @@ VARIANTS = {
 }
 
 
-@pytest.fixture(params=[0, 1], ids=["plan_split", "plan_fused"])
-def plan_variant(request):
-    """Both forms of the plan launch: two kernels, or one whose last CTA per head decides."""
-    K.ext().set_option("plan_fused", request.param)
-    yield request.param
-    K.ext().set_option("plan_fused", 0)
-
-
 @pytest.mark.parametrize("name", list(VARIANTS))
-def test_planner_loop_bits(libs, name, plan_variant):
+def test_planner_loop_bits(libs, name):
     """64 decode steps of plan -> masked+stats attention -> update, our library and the reference's
     kernels side by side from the same first-step state: every state tensor identical after every
     step (block lists, decisions, stored sets, ages, references, corrections, latches)."""
