@@ -208,6 +208,24 @@ int kvskip_launch_exchange_merge(const float* out_f32, const float* lse, float* 
 int kvskip_launch_index_blocks(const int64_t* ids, int64_t ids_stride, int n, int T, uint8_t* out, int NBC,
                                void* stream);
 
+/* Device-resident sequence length (no counterpart in the reference, whose launches take T by value;
+ * its README lists a captured decode step as an open item).  The same kernels as the entry points
+ * above, but the length they work on is read from *t_dev on the device after the preceding work
+ * of the stream has finished, so one captured sequence of launches can be replayed while the
+ * cache grows.  The T of the parameter block (T_bound for the index) is then an upper bound: it
+ * sizes the grid, the tensor maps (the K/V views must be valid for T rows) and the layout -- the
+ * statistics rows keep the stride ceil(T/64), and blocks between the current and the bounded
+ * length are reported as unread (-inf / 0).  A value outside [1, T] is clamped.  K/V rows beyond
+ * the current length are never used, whatever they hold.  Tensor-core path only (D = 128).
+ * kvskip_launch_advance adds delta to *t_dev in stream order (one thread). */
+int kvskip_launch_decode_dyn(const kvskip_params* p, int D, int G, int stages, int masked, int stats, int load_v,
+                             const int* t_dev, void* stream);
+int kvskip_launch_plan_dyn(const kvskip_plan_params* p, const int* t_dev, void* stream);
+int kvskip_launch_update_dyn(const kvskip_update_params* p, const int* t_dev, void* stream);
+int kvskip_launch_index_blocks_dyn(const int64_t* ids, int64_t ids_stride, int n, int T_bound, const int* t_dev,
+                                   uint8_t* out, int NBC, void* stream);
+int kvskip_launch_advance(int* t_dev, int delta, void* stream);
+
 /* Process-wide options (no counterpart in the reference).
  *   "decode_path"  0 (default): tensor-core kernel for D = 128, exact-order kernel otherwise;
  *                  1: exact-order kernel everywhere -- scores, block statistics and outputs are

@@ -96,8 +96,8 @@ __device__ __forceinline__ float quadcol_sum(float v) {
 // kbase: shared-memory address of the stage (K halves, then V halves); state in m_run / l_run / acc.
 template <bool STATS, bool LOAD_V>
 __device__ __forceinline__ void tc_block(const kvskip_params& p, const uint32_t kbase, const uint32_t (&bq)[8][2],
-                                         const int blk, const int64_t hq0, const int lane, float (&m_run)[2],
-                                         float (&l_run)[2], float (&acc)[8][4]) {
+                                         const int blk, const int64_t hq0, const int lane, const int T,
+                                         float (&m_run)[2], float (&l_run)[2], float (&acc)[8][4]) {
   const int lrow = lane & 7, lmat = lane >> 3;
   const bool col_ok = (lane & 3) < 2;          // this thread's two columns are real heads
   const int head0 = 2 * (lane & 3);
@@ -121,13 +121,13 @@ __device__ __forceinline__ void tc_block(const kvskip_params& p, const uint32_t 
     }
   }
   // scale to log2 units, mask the tokens past T (last block only)
-  const bool ragged = t0 + TILE > p.T;
+  const bool ragged = t0 + TILE > T;
 #pragma unroll
   for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       float v = sc[mt][c] * p.scale_log2;
-      if (ragged && t0 + mt * 16 + (lane >> 2) + (c >> 1) * 8 >= p.T) v = -INFINITY;
+      if (ragged && t0 + mt * 16 + (lane >> 2) + (c >> 1) * 8 >= T) v = -INFINITY;
       sc[mt][c] = v;
     }
   // ---- online softmax, two heads per thread
@@ -246,7 +246,7 @@ __device__ __forceinline__ void tc_fill_gap(const kvskip_params& p, const int32_
 template <int NC, bool MASKED, bool STATS, bool LOAD_V>
 __global__ void __launch_bounds__((NC + 1) * 32, NC <= 3 ? 2 : 1)
 decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* __restrict__ split_done,
-                 const int min_blocks) {
+                 const int min_blocks, const int* __restrict__ t_dev) {
   using Cfg = TcCfg<NC, LOAD_V>;
   constexpr int G = 4, D = 128;
   constexpr int S = Cfg::kStages;
@@ -278,13 +278,16 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
   pdl_wait_prior();
   pdl_launch_dependents();
 
+  // Length of the sequences: p.T, or, with a device-resident length, the value at t_dev (p.T is
+  // then the bound the grid, the tensor maps and the statistics stride p.nb were sized for).
+  const int T = t_dev ? max(1, min(*t_dev, p.T)) : p.T;
   int n_items;
   const int32_t* list = nullptr;
   if constexpr (MASKED) {
     n_items = p.block_cnt[b * p.Hkv + h];
     list = p.block_idx + static_cast<int64_t>(b * p.Hkv + h) * p.max_blocks;
   } else {
-    n_items = (p.T + TILE - 1) / TILE;
+    n_items = (T + TILE - 1) / TILE;
   }
   // Splits actually used for this (batch, kv head).  A block list can be much shorter than the
   // length the grid was sized for (a head that does not refresh reads a tenth of the blocks a
@@ -339,8 +342,23 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
       if constexpr (MASKED && STATS) tc_fill_gap(p, list, i0 + i, n_items, blk, hq0, lane);
       if (!mbar_wait(&full[s], (i / S) & 1, 0x210u + s)) break;
       const uint32_t kbase = smem_u32(ring + s * Cfg::kStageBytes);
+      if constexpr (LOAD_V) {
+        // Device-resident length: the tensor map reaches past T, so the rows of the last block
+        // beyond T hold whatever the cache holds there.  Their weights are zero, but 0 x NaN is
+        // not: clear those V rows (whole 128-byte rows of both halves, so the swizzle is moot).
+        if (t_dev != nullptr && blk * TILE + TILE > T) {
+          const int r0 = T - blk * TILE;
+          unsigned char* vst = ring + s * Cfg::kStageBytes + 2 * TC_HALF_BYTES;
+          for (int o = r0 * 128 + lane * 16; o < TILE * 128; o += 32 * 16) {
+            *reinterpret_cast<uint4*>(vst + o) = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(vst + TC_HALF_BYTES + o) = make_uint4(0u, 0u, 0u, 0u);
+          }
+          fence_proxy_async_smem();   // ordered before the next bulk load into this stage
+          __syncwarp();
+        }
+      }
 
-      tc_block<STATS, LOAD_V>(p, kbase, bq, blk, hq0, lane, m_run, l_run, acc);
+      tc_block<STATS, LOAD_V>(p, kbase, bq, blk, hq0, lane, T, m_run, l_run, acc);
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);
     }
@@ -348,6 +366,16 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
       // an empty list: the first split clears every block of this KV head
       if (n_items == 0 && split == 0 && warp == 0)
         for (int gblk = lane; gblk < p.nb; gblk += 32)
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            p.blk_max[(hq0 + g) * p.nb + gblk] = -INFINITY;
+            p.blk_sum[(hq0 + g) * p.nb + gblk] = 0.f;
+          }
+    }
+    if constexpr (!MASKED && STATS) {
+      // device-resident length: blocks between the current and the provisioned length are unread
+      if (t_dev != nullptr && split == 0 && warp == 0)
+        for (int gblk = n_items + lane; gblk < p.nb; gblk += 32)
 #pragma unroll
           for (int g = 0; g < G; ++g) {
             p.blk_max[(hq0 + g) * p.nb + gblk] = -INFINITY;

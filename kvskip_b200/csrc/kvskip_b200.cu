@@ -186,17 +186,18 @@ int split_done_region(int units, int** out) {
 }
 
 template <int NC, bool MASKED, bool STATS, bool LOAD_V>
-int launch_tc_nc(const kvskip_params& p, const kvb::TmaMaps& maps, int* done, int min_blocks, cudaStream_t stream) {
+int launch_tc_nc(const kvskip_params& p, const kvb::TmaMaps& maps, int* done, int min_blocks, const int* t_dev,
+                 cudaStream_t stream) {
   using Cfg = kvb::TcCfg<NC, LOAD_V>;
   auto kernel = kvb::decode_tc_kernel<NC, MASKED, STATS, LOAD_V>;
   if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes)) return rc;
   KVB_CUDA(launch_overlapped(kernel, dim3(p.num_splits, p.Hkv, p.B), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, p,
-                             maps, done, min_blocks));
+                             maps, done, min_blocks, t_dev));
   return KVSKIP_OK;
 }
 
 template <bool MASKED, bool STATS, bool LOAD_V>
-int launch_tc(const kvskip_params& p, cudaStream_t stream) {
+int launch_tc(const kvskip_params& p, const int* t_dev, cudaStream_t stream) {
   kvb::TmaMaps maps;
   if (int rc = make_kv_map(&maps.k, p.k, p.k_sb, p.k_sh, p.k_st, p.B, p.Hkv, p.T, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
@@ -222,8 +223,8 @@ int launch_tc(const kvskip_params& p, cudaStream_t stream) {
   const bool multi_wave =
       !MASKED && total >= 4 * static_cast<int64_t>(sms) && g_half_cta.load(std::memory_order_relaxed);
   const int min_blocks = (total > sms) ? 24 : 1;
-  if (int rc = multi_wave ? launch_tc_nc<3, MASKED, STATS, LOAD_V>(p, maps, done, min_blocks, stream)
-                          : launch_tc_nc<6, MASKED, STATS, LOAD_V>(p, maps, done, min_blocks, stream))
+  if (int rc = multi_wave ? launch_tc_nc<3, MASKED, STATS, LOAD_V>(p, maps, done, min_blocks, t_dev, stream)
+                          : launch_tc_nc<6, MASKED, STATS, LOAD_V>(p, maps, done, min_blocks, t_dev, stream))
     return rc;
   if (LOAD_V && p.num_splits > 1 && done == nullptr) {
     kvb::merge_kernel<128><<<p.B * p.Hq, 128, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits,
@@ -234,13 +235,13 @@ int launch_tc(const kvskip_params& p, cudaStream_t stream) {
   return KVSKIP_OK;
 }
 
-int dispatch_tc(const kvskip_params& p, bool masked, bool stats, bool load_v, cudaStream_t s) {
-  if (!masked && !stats && load_v) return launch_tc<false, false, true>(p, s);
-  if (!masked && stats && load_v) return launch_tc<false, true, true>(p, s);
-  if (!masked && stats && !load_v) return launch_tc<false, true, false>(p, s);
-  if (masked && !stats && load_v) return launch_tc<true, false, true>(p, s);
-  if (masked && stats && load_v) return launch_tc<true, true, true>(p, s);
-  if (masked && stats && !load_v) return launch_tc<true, true, false>(p, s);
+int dispatch_tc(const kvskip_params& p, bool masked, bool stats, bool load_v, const int* t_dev, cudaStream_t s) {
+  if (!masked && !stats && load_v) return launch_tc<false, false, true>(p, t_dev, s);
+  if (!masked && stats && load_v) return launch_tc<false, true, true>(p, t_dev, s);
+  if (!masked && stats && !load_v) return launch_tc<false, true, false>(p, t_dev, s);
+  if (masked && !stats && load_v) return launch_tc<true, false, true>(p, t_dev, s);
+  if (masked && stats && load_v) return launch_tc<true, true, true>(p, t_dev, s);
+  if (masked && stats && !load_v) return launch_tc<true, true, false>(p, t_dev, s);
   return fail(KVSKIP_E_ARG, "kvskip: unsupported flag combination (load_v=false needs stats=true)");
 }
 
@@ -333,8 +334,9 @@ int kvskip_max_smem_bytes(int D, int stages, int load_v) {
   return 0;
 }
 
-int kvskip_launch_decode(const kvskip_params* p, int D, int G, int stages, int masked, int stats, int load_v,
-                         void* stream) {
+namespace {
+int decode_impl(const kvskip_params* p, int D, int G, int stages, int masked, int stats, int load_v, const int* t_dev,
+                void* stream) {
   if (int rc = check_common(p, D, G)) return rc;
   if (stages != 2 && stages != 3) return fail(KVSKIP_E_ARG, "kvskip: unsupported head dim / stages");
   if (!load_v && !stats) return fail(KVSKIP_E_ARG, "kvskip: unsupported flag combination (load_v=false needs stats=true)");
@@ -345,9 +347,22 @@ int kvskip_launch_decode(const kvskip_params* p, int D, int G, int stages, int m
     return fail(KVSKIP_E_ARG, "num_splits > 1 needs part_acc / part_ml scratch");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int path = g_decode_path.load(std::memory_order_relaxed);
-  if (D == 128 && path != 1) return dispatch_tc(*p, masked, stats, load_v, s);
+  if (D == 128 && path != 1) return dispatch_tc(*p, masked, stats, load_v, t_dev, s);
+  if (t_dev) return fail(KVSKIP_E_ARG, "a device-resident length needs the tensor-core path (D = 128, decode_path != 1)");
   if (path == 2) return fail(KVSKIP_E_ARG, "the tensor-core path exists for D = 128 only");
   return D == 128 ? dispatch_exact<128>(*p, masked, stats, load_v, s) : dispatch_exact<64>(*p, masked, stats, load_v, s);
+}
+}  // namespace
+
+int kvskip_launch_decode(const kvskip_params* p, int D, int G, int stages, int masked, int stats, int load_v,
+                         void* stream) {
+  return decode_impl(p, D, G, stages, masked, stats, load_v, nullptr, stream);
+}
+
+int kvskip_launch_decode_dyn(const kvskip_params* p, int D, int G, int stages, int masked, int stats, int load_v,
+                             const int* t_dev, void* stream) {
+  if (!t_dev) return fail(KVSKIP_E_ARG, "t_dev is null");
+  return decode_impl(p, D, G, stages, masked, stats, load_v, t_dev, stream);
 }
 
 // ---- split-K decode for callers that cannot allocate device memory -------------------------
@@ -445,7 +460,8 @@ int kvskip_launch_pv(const kvskip_params* p, int D, int G, void* stream) {
   return D == 128 ? launch_pv_t<128>(*p, s) : launch_pv_t<64>(*p, s);
 }
 
-int kvskip_launch_plan(const kvskip_plan_params* p, void* stream) {
+namespace {
+int plan_impl(const kvskip_plan_params* p, const int* t_dev, void* stream) {
   if (!p) return fail(KVSKIP_E_ARG, "null parameter block");
   if (p->Hq != 4 * p->Hkv) return fail(KVSKIP_E_ARG, "planner kernels: D = 128, G = 4");
   const int nb = (p->T + KVSKIP_TILE - 1) / KVSKIP_TILE;
@@ -462,11 +478,20 @@ int kvskip_launch_plan(const kvskip_plan_params* p, void* stream) {
   if (smem > 40 * 1024)
     if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::plan_kernel), 200 * 1024)) return rc;
   KVB_CUDA(launch_overlapped(kvb::plan_kernel, dim3(chunks, p->Hkv, p->B), dim3(kvb::PL_THREADS), smem,
-                             static_cast<cudaStream_t>(stream), *p, done));
+                             static_cast<cudaStream_t>(stream), *p, done, t_dev));
   return KVSKIP_OK;
 }
+}  // namespace
 
-int kvskip_launch_update(const kvskip_update_params* p, void* stream) {
+int kvskip_launch_plan(const kvskip_plan_params* p, void* stream) { return plan_impl(p, nullptr, stream); }
+
+int kvskip_launch_plan_dyn(const kvskip_plan_params* p, const int* t_dev, void* stream) {
+  if (!t_dev) return fail(KVSKIP_E_ARG, "t_dev is null");
+  return plan_impl(p, t_dev, stream);
+}
+
+namespace {
+int update_impl(const kvskip_update_params* p, const int* t_dev, void* stream) {
   if (!p) return fail(KVSKIP_E_ARG, "null parameter block");
   if (p->Hq != 4 * p->Hkv) return fail(KVSKIP_E_ARG, "planner kernels: D = 128, G = 4");
   const int nb = (p->T + KVSKIP_TILE - 1) / KVSKIP_TILE;
@@ -478,8 +503,16 @@ int kvskip_launch_update(const kvskip_update_params* p, void* stream) {
   if (smem > 48 * 1024)
     if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::update_kernel), 220 * 1024)) return rc;
   KVB_CUDA(launch_overlapped(kvb::update_kernel, dim3(p->Hkv, p->B), dim3(kvb::PL_THREADS), smem,
-                             static_cast<cudaStream_t>(stream), *p));
+                             static_cast<cudaStream_t>(stream), *p, t_dev));
   return KVSKIP_OK;
+}
+}  // namespace
+
+int kvskip_launch_update(const kvskip_update_params* p, void* stream) { return update_impl(p, nullptr, stream); }
+
+int kvskip_launch_update_dyn(const kvskip_update_params* p, const int* t_dev, void* stream) {
+  if (!t_dev) return fail(KVSKIP_E_ARG, "t_dev is null");
+  return update_impl(p, t_dev, stream);
 }
 
 int kvskip_launch_read(const void* x, int64_t bytes, uint32_t* out, int blocks, void* stream) {
@@ -558,13 +591,33 @@ int kvskip_launch_exchange_merge(const float* out_f32, const float* lse, float* 
   return KVSKIP_OK;
 }
 
-int kvskip_launch_index_blocks(const int64_t* ids, int64_t ids_stride, int n, int T, uint8_t* out, int NBC,
-                               void* stream) {
+namespace {
+int index_blocks_impl(const int64_t* ids, int64_t ids_stride, int n, int T, const int* t_dev, uint8_t* out, int NBC,
+                      void* stream) {
   if (!ids || !out || n < 1 || T < 1) return fail(KVSKIP_E_ARG, "index_blocks: bad arguments");
   if ((T + KVSKIP_TILE - 1) / KVSKIP_TILE > NBC) return fail(KVSKIP_E_ARG, "block capacity exceeded");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   KVB_CUDA(cudaMemsetAsync(out, 0, static_cast<size_t>(n) * NBC, s));
-  kvb::index_blocks_kernel<<<dim3((T + 255) / 256, n), 256, 0, s>>>(ids, ids_stride, T, out, NBC);
+  kvb::index_blocks_kernel<<<dim3((T + 255) / 256, n), 256, 0, s>>>(ids, ids_stride, T, out, NBC, t_dev);
+  KVB_CUDA(cudaGetLastError());
+  return KVSKIP_OK;
+}
+}  // namespace
+
+int kvskip_launch_index_blocks(const int64_t* ids, int64_t ids_stride, int n, int T, uint8_t* out, int NBC,
+                               void* stream) {
+  return index_blocks_impl(ids, ids_stride, n, T, nullptr, out, NBC, stream);
+}
+
+int kvskip_launch_index_blocks_dyn(const int64_t* ids, int64_t ids_stride, int n, int T_bound, const int* t_dev,
+                                   uint8_t* out, int NBC, void* stream) {
+  if (!t_dev) return fail(KVSKIP_E_ARG, "t_dev is null");
+  return index_blocks_impl(ids, ids_stride, n, T_bound, t_dev, out, NBC, stream);
+}
+
+int kvskip_launch_advance(int* t_dev, int delta, void* stream) {
+  if (!t_dev) return fail(KVSKIP_E_ARG, "t_dev is null");
+  kvb::advance_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(t_dev, delta);
   KVB_CUDA(cudaGetLastError());
   return KVSKIP_OK;
 }

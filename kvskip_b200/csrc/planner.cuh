@@ -75,10 +75,12 @@ constexpr int PL_CHUNK = 32;   // blocks whose centroid scores one CTA computes 
 // done[], which it puts back to zero) folds the estimate, decides and writes the block list.
 // The arithmetic of a score and of the fold is unchanged, only spread over more SMs: one CTA per
 // head reading nb * 512 bytes of key sums is latency-bound at long contexts.
-__global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_params p, int* __restrict__ done) {
+// With a device-resident length (t_dev != nullptr) p.T is the bound the grid was sized for; CTAs
+// whose chunk lies beyond the current length leave without being counted.
+__global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_params p, int* __restrict__ done,
+                                                          const int* __restrict__ t_dev) {
   const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int nb = (p.T + TILE - 1) / TILE;
   const int64_t bh = static_cast<int64_t>(b) * p.Hkv + h;
   float* csum = p.csum + bh * p.NBC * PL_D;
   const uint8_t* keep = p.keep + bh * p.NBC;
@@ -88,6 +90,10 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
   __shared__ int s_flag;
   pdl_wait_prior();          // the state this kernel reads may come from the previous kernel on the stream
   pdl_launch_dependents();
+  const int T = t_dev ? max(1, min(*t_dev, p.T)) : p.T;
+  const int nb = (T + TILE - 1) / TILE;
+  const int chunks = (nb + PL_CHUNK - 1) / PL_CHUNK;
+  if (chunk >= chunks) return;
 
   const int fl = p.flags[h];
   if (fl & 2) {   // token-index head: index blocks + sink + newest, never refreshes; one CTA does it
@@ -102,10 +108,10 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
   auto attended = [&](int blk) { return keep[blk] || pl_always(blk, nb, p.local) || (uni && ix[blk]); };
 
   const int blk0 = chunk * PL_CHUNK;
-  const int tok_blk = (p.T - 1) / TILE;
+  const int tok_blk = (T - 1) / TILE;
   if (p.add_token && tok_blk >= blk0 && tok_blk < blk0 + PL_CHUNK) {   // D == 128 == PL_THREADS
     const __nv_bfloat16* kr = reinterpret_cast<const __nv_bfloat16*>(p.k) + b * p.k_sb + h * p.k_sh +
-                              static_cast<int64_t>(p.T - 1) * p.k_st;
+                              static_cast<int64_t>(T - 1) * p.k_st;
     csum[static_cast<int64_t>(tok_blk) * PL_D + tid] += __bfloat162float(kr[tid]);
   }
   __syncthreads();
@@ -151,14 +157,14 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
     }
     const int blk = wb + (lane >> 2), g = lane & 3;
     if (blk < nb) {
-      const float inv_n = 1.f / static_cast<float>(blk == nb - 1 ? p.T - blk * TILE : TILE);
+      const float inv_n = 1.f / static_cast<float>(blk == nb - 1 ? T - blk * TILE : TILE);
       p.cs_now[row0 + g * p.NBC + blk] = a[0] * inv_n;
     }
   }
   // count this chunk; only the last one of the head goes on
   __threadfence();
   __syncthreads();
-  if (tid == 0) s_flag = atomicAdd(&done[bh], 1) == static_cast<int>(gridDim.x) - 1;
+  if (tid == 0) s_flag = atomicAdd(&done[bh], 1) == chunks - 1;
   __syncthreads();
   if (!s_flag) return;
   __threadfence();
@@ -243,27 +249,30 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
   pl_compact(nb, bi, p.block_cnt + bh, scan, [&](int i) { return pl_att[i] != 0; });
 }
 
-__global__ void __launch_bounds__(PL_THREADS) update_kernel(const kvskip_update_params p) {
+// With a device-resident length p.T bounds it and gives the row stride of the statistics.
+__global__ void __launch_bounds__(PL_THREADS) update_kernel(const kvskip_update_params p,
+                                                            const int* __restrict__ t_dev) {
   const int h = blockIdx.x, b = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int nb = (p.T + TILE - 1) / TILE;
+  const int nbs = (p.T + TILE - 1) / TILE;   // row stride of blk_max / blk_sum
   const int64_t bh = static_cast<int64_t>(b) * p.Hkv + h;
   const int64_t hrow = static_cast<int64_t>(b) * p.Hq + h * PL_G + warp;   // this warp's query head
   extern __shared__ float up_smem[];
+  uint8_t* keep = p.keep + bh * p.NBC;
+  pdl_wait_prior();          // statistics and decisions come from the kernels before this one
+  pdl_launch_dependents();
+  const int nb = (t_dev ? max(1, min(*t_dev, p.T)) + TILE - 1 : p.T + TILE - 1) / TILE;
   float* x = up_smem + warp * nb;                                          // block log-weights of the head
   float* ey = up_smem + (PL_G + warp) * nb;                                // exp(x - lse) of the head
   uint8_t* skeep = reinterpret_cast<uint8_t*>(up_smem + 2 * PL_G * nb);   // [nb] union of the new sets
   uint8_t* sflag = skeep + nb;   // [nb] bit 0: stored or always read, bit 1: joined through the token index
-  uint8_t* keep = p.keep + bh * p.NBC;
-  pdl_wait_prior();          // statistics and decisions come from the kernels before this one
-  pdl_launch_dependents();
   const bool tr = p.trig[bh];
   __shared__ float s_real[PL_G];
 
   float mx = -INFINITY;
 #pragma unroll 8
   for (int i = lane; i < nb; i += 32) {
-    const float val = p.blk_max[hrow * nb + i] + __logf(p.blk_sum[hrow * nb + i]);   // -inf where not read
+    const float val = p.blk_max[hrow * nbs + i] + __logf(p.blk_sum[hrow * nbs + i]);   // -inf where not read
     x[i] = val;
     mx = fmaxf(mx, val);
   }
@@ -354,7 +363,9 @@ __global__ void __launch_bounds__(PL_THREADS) update_kernel(const kvskip_update_
 // Token-index blocks of one step: grid (ceil(T/256), n).  A position t < T-1 holding the current
 // token marks its own block and the block of t+1.
 __global__ void __launch_bounds__(256) index_blocks_kernel(const int64_t* __restrict__ ids, int64_t stride,
-                                                           int T, uint8_t* out, int NBC) {
+                                                           int T, uint8_t* out, int NBC,
+                                                           const int* __restrict__ t_dev) {
+  if (t_dev) T = max(1, min(*t_dev, T));   // device-resident length, bounded by the launch's T
   const int r = blockIdx.y;
   const int64_t* x = ids + r * stride;
   const int64_t cur = x[T - 1];
@@ -364,5 +375,8 @@ __global__ void __launch_bounds__(256) index_blocks_kernel(const int64_t* __rest
     out[static_cast<int64_t>(r) * NBC + (t + 1) / TILE] = 1;
   }
 }
+
+// The device-resident sequence length of a captured decode step: one thread adds delta.
+__global__ void advance_kernel(int* t, int delta) { *t += delta; }
 
 }  // namespace kvb

@@ -59,6 +59,14 @@ void fill_qkv(kvskip_params& p, const at::Tensor& q, const at::Tensor& k, const 
   p.T = static_cast<int32_t>(k.size(2));
 }
 
+// Device-resident sequence length: a one-element int32 CUDA tensor, or nothing.
+const int* tdev_ptr(const c10::optional<at::Tensor>& t_dev) {
+  if (!t_dev.has_value()) return nullptr;
+  TORCH_CHECK(t_dev->is_cuda() && t_dev->scalar_type() == at::kInt && t_dev->numel() == 1,
+              "t_dev: one-element int32 CUDA tensor");
+  return t_dev->data_ptr<int32_t>();
+}
+
 }  // namespace
 
 // [out bf16 [B,Hq,D] (undefined without load_v), lse [B,Hq], blk_max, blk_sum ([B,Hq,nb] or
@@ -66,7 +74,8 @@ void fill_qkv(kvskip_params& p, const at::Tensor& q, const at::Tensor& k, const 
 std::vector<at::Tensor> decode(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double scale,
                                const c10::optional<at::Tensor>& block_idx,
                                const c10::optional<at::Tensor>& block_cnt, bool stats, bool load_v,
-                               int64_t num_splits, int64_t stages, bool want_f32, bool write_p) {
+                               int64_t num_splits, int64_t stages, bool want_f32, bool write_p,
+                               const c10::optional<at::Tensor>& t_dev) {
   need_q(q);
   need_kv(k, "k");
   need_kv(v, "v");
@@ -127,8 +136,12 @@ std::vector<at::Tensor> decode(const at::Tensor& q, const at::Tensor& k, const a
   p.nb = static_cast<int32_t>(nb);
   p.t_pad = nb * KVSKIP_TILE;
   if (write_p) p.p_out = u16m(pbuf);
-  raise_on(kvskip_launch_decode(&p, static_cast<int>(D), static_cast<int>(Hq / Hkv), static_cast<int>(stages),
-                                masked, stats, load_v, cur_stream()));
+  if (const int* td = tdev_ptr(t_dev))
+    raise_on(kvskip_launch_decode_dyn(&p, static_cast<int>(D), static_cast<int>(Hq / Hkv), static_cast<int>(stages),
+                                      masked, stats, load_v, td, cur_stream()));
+  else
+    raise_on(kvskip_launch_decode(&p, static_cast<int>(D), static_cast<int>(Hq / Hkv), static_cast<int>(stages),
+                                  masked, stats, load_v, cur_stream()));
   return {out, lse, bmax, bsum, out32, pbuf};
 }
 
@@ -230,7 +243,7 @@ void plan(const at::Tensor& q, const at::Tensor& k, at::Tensor& csum, const at::
           at::Tensor& block_cnt, double scale, double delta, int64_t max_age, int64_t local, bool add_token,
           const c10::optional<at::Tensor>& idx, const c10::optional<at::Tensor>& calib,
           const c10::optional<at::Tensor>& est, bool calib_on, int64_t calib_kind,
-          const c10::optional<at::Tensor>& aix) {
+          const c10::optional<at::Tensor>& aix, const c10::optional<at::Tensor>& t_dev) {
   TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && q.dim() == 3 && q.stride(2) == 1, "q: CUDA bf16 [B, Hq, D]");
   need_kv(k, "k");
   const int64_t B = q.size(0), Hq = q.size(1), D = q.size(2), Hkv = k.size(1), T = k.size(2);
@@ -291,7 +304,10 @@ void plan(const at::Tensor& q, const at::Tensor& k, at::Tensor& csum, const at::
   p.T = static_cast<int32_t>(T); p.NBC = static_cast<int32_t>(NBC);
   p.local = static_cast<int32_t>(local); p.max_age = static_cast<int32_t>(max_age); p.add_token = add_token;
   p.scale = static_cast<float>(scale); p.delta = static_cast<float>(delta);
-  raise_on(kvskip_launch_plan(&p, cur_stream()));
+  if (const int* td = tdev_ptr(t_dev))
+    raise_on(kvskip_launch_plan_dyn(&p, td, cur_stream()));
+  else
+    raise_on(kvskip_launch_plan(&p, cur_stream()));
 }
 
 void update(const at::Tensor& blk_max, const at::Tensor& blk_sum, const at::Tensor& trig, const at::Tensor& cs_now,
@@ -299,7 +315,7 @@ void update(const at::Tensor& blk_max, const at::Tensor& blk_sum, const at::Tens
             double level, int64_t local, const c10::optional<at::Tensor>& flags,
             const c10::optional<at::Tensor>& idx, const c10::optional<at::Tensor>& est,
             const c10::optional<at::Tensor>& calib, double calib_rate, bool calib_free, int64_t calib_kind,
-            const c10::optional<at::Tensor>& aix, double aix_thr) {
+            const c10::optional<at::Tensor>& aix, double aix_thr, const c10::optional<at::Tensor>& t_dev) {
   need_f32(blk_max, "blk_max"); need_f32(blk_sum, "blk_sum");
   const int64_t B = keep.size(0), Hkv = keep.size(1), NBC = keep.size(2), Hq = lse_att.size(1);
   TORCH_CHECK(blk_max.size(2) == (T + KVSKIP_TILE - 1) / KVSKIP_TILE, "stats length mismatch");
@@ -341,7 +357,10 @@ void update(const at::Tensor& blk_max, const at::Tensor& blk_sum, const at::Tens
       p.idx = idx->data_ptr<uint8_t>();
     }
   }
-  raise_on(kvskip_launch_update(&p, cur_stream()));
+  if (const int* td = tdev_ptr(t_dev))
+    raise_on(kvskip_launch_update_dyn(&p, td, cur_stream()));
+  else
+    raise_on(kvskip_launch_update(&p, cur_stream()));
 }
 
 // One layer's refresh-policy step in a single call: plan -> masked attention with block
@@ -356,12 +375,12 @@ std::vector<at::Tensor> refresh_step(const at::Tensor& q, const at::Tensor& k, c
                                      const c10::optional<at::Tensor>& idx, const c10::optional<at::Tensor>& calib,
                                      const c10::optional<at::Tensor>& est, bool calib_on, int64_t calib_kind,
                                      double calib_rate, bool calib_free, const c10::optional<at::Tensor>& aix,
-                                     double aix_thr) {
+                                     double aix_thr, const c10::optional<at::Tensor>& t_dev) {
   plan(q, k, csum, lse_ref, cs_ref, keep, lse_att, age, flags, cs_now, trig, block_idx, block_cnt, scale, delta, max_age,
-       local, true, idx, calib, est, calib_on, calib_kind, aix);
-  auto r = decode(q, k, v, scale, block_idx, block_cnt, true, true, num_splits, 2, false, false);
+       local, true, idx, calib, est, calib_on, calib_kind, aix, t_dev);
+  auto r = decode(q, k, v, scale, block_idx, block_cnt, true, true, num_splits, 2, false, false, t_dev);
   update(r[2], r[3], trig, cs_now, keep, lse_ref, cs_ref, lse_att, k.size(2), level, local, flags, idx, est, calib,
-         calib_rate, calib_free, calib_kind, aix, aix_thr);
+         calib_rate, calib_free, calib_kind, aix, aix_thr, t_dev);
   return {r[0], r[1], r[2], r[3]};
 }
 
@@ -438,15 +457,28 @@ std::vector<at::Tensor> exchange_merge(const at::Tensor& out_f32, const at::Tens
   return {out, out32, res_lse};
 }
 
-void index_blocks(const at::Tensor& ids, int64_t T, at::Tensor& out) {
+void index_blocks(const at::Tensor& ids, int64_t T, at::Tensor& out, const c10::optional<at::Tensor>& t_dev) {
   TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.dim() == 2 && ids.stride(1) == 1, "ids: CUDA int64 [n, >= T]");
   TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kByte && out.dim() == 2 && out.is_contiguous() &&
                   out.size(0) == ids.size(0), "out: contiguous uint8 [n, NBC]");
   TORCH_CHECK(T >= 1 && T <= ids.size(1), "T within ids");
   const c10::cuda::CUDAGuard guard(ids.device());
-  raise_on(kvskip_launch_index_blocks(ids.data_ptr<int64_t>(), ids.stride(0), static_cast<int>(ids.size(0)),
-                                      static_cast<int>(T), out.data_ptr<uint8_t>(), static_cast<int>(out.size(1)),
-                                      cur_stream()));
+  if (const int* td = tdev_ptr(t_dev))
+    raise_on(kvskip_launch_index_blocks_dyn(ids.data_ptr<int64_t>(), ids.stride(0), static_cast<int>(ids.size(0)),
+                                            static_cast<int>(T), td, out.data_ptr<uint8_t>(),
+                                            static_cast<int>(out.size(1)), cur_stream()));
+  else
+    raise_on(kvskip_launch_index_blocks(ids.data_ptr<int64_t>(), ids.stride(0), static_cast<int>(ids.size(0)),
+                                        static_cast<int>(T), out.data_ptr<uint8_t>(), static_cast<int>(out.size(1)),
+                                        cur_stream()));
+}
+
+// *t_dev += delta in stream order
+void advance(at::Tensor& t_dev, int64_t delta) {
+  TORCH_CHECK(t_dev.is_cuda() && t_dev.scalar_type() == at::kInt && t_dev.numel() == 1,
+              "t_dev: one-element int32 CUDA tensor");
+  const c10::cuda::CUDAGuard guard(t_dev.device());
+  raise_on(kvskip_launch_advance(t_dev.data_ptr<int32_t>(), static_cast<int>(delta), cur_stream()));
 }
 
 void set_option(const std::string& name, int64_t value) {
@@ -473,20 +505,21 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("block_idx"), py::arg("block_cnt"), py::arg("scale"), py::arg("delta"), py::arg("max_age"),
         py::arg("local"), py::arg("add_token"), py::arg("idx") = py::none(), py::arg("calib") = py::none(),
         py::arg("est") = py::none(), py::arg("calib_on") = false, py::arg("calib_kind") = 0,
-        py::arg("aix") = py::none());
+        py::arg("aix") = py::none(), py::arg("t_dev") = py::none());
   m.def("update", &update, "refresh planner: stored set and references (after the pass)",
         py::arg("blk_max"), py::arg("blk_sum"), py::arg("trig"), py::arg("cs_now"), py::arg("keep"),
         py::arg("lse_ref"), py::arg("cs_ref"), py::arg("lse_att"), py::arg("T"), py::arg("level"), py::arg("local"),
         py::arg("flags") = py::none(), py::arg("idx") = py::none(), py::arg("est") = py::none(),
         py::arg("calib") = py::none(), py::arg("calib_rate") = 0.0, py::arg("calib_free") = false,
-        py::arg("calib_kind") = 0, py::arg("aix") = py::none(), py::arg("aix_thr") = 0.0);
+        py::arg("calib_kind") = 0, py::arg("aix") = py::none(), py::arg("aix_thr") = 0.0,
+        py::arg("t_dev") = py::none());
   m.def("vskip1", &vskip1, "single-pass V-skip", py::arg("q"), py::arg("k"), py::arg("v"), py::arg("scale"),
         py::arg("tau"), py::arg("local") = 2, py::arg("num_splits") = 1, py::arg("want_f32") = false,
         py::arg("count") = false, py::arg("lse_prev") = py::none());
   m.def("decode", &decode, "split-K decode attention", py::arg("q"), py::arg("k"), py::arg("v"), py::arg("scale"),
         py::arg("block_idx") = py::none(), py::arg("block_cnt") = py::none(), py::arg("stats") = false,
         py::arg("load_v") = true, py::arg("num_splits") = 1, py::arg("stages") = 2, py::arg("want_f32") = false,
-        py::arg("write_p") = false);
+        py::arg("write_p") = false, py::arg("t_dev") = py::none());
   m.def("pv", &pv, "two-pass V-skip, pass 2", py::arg("P"), py::arg("v"), py::arg("blk_scale"), py::arg("block_idx"),
         py::arg("block_cnt"), py::arg("num_splits") = 1, py::arg("want_f32") = false);
   m.def("refresh_step", &refresh_step, "plan -> masked+stats attention -> update for one layer, one call",
@@ -496,14 +529,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("local"), py::arg("level"), py::arg("num_splits"), py::arg("idx") = py::none(),
         py::arg("calib") = py::none(), py::arg("est") = py::none(), py::arg("calib_on") = false,
         py::arg("calib_kind") = 0, py::arg("calib_rate") = 0.0, py::arg("calib_free") = false,
-        py::arg("aix") = py::none(), py::arg("aix_thr") = 0.0);
+        py::arg("aix") = py::none(), py::arg("aix_thr") = 0.0, py::arg("t_dev") = py::none());
   m.def("merge", &merge, "merge of R partial (max, sum, acc) rows", py::arg("part_acc"), py::arg("part_ml"));
   m.def("pack_partial", &pack_partial, "rank-local (out_f32, lse) -> packed (acc, m, l) rows", py::arg("out_f32"),
         py::arg("lse"));
   m.def("merge_packed", &merge_packed, "merge of R packed partial buffers [R,N,D+2]", py::arg("parts"));
   m.def("exchange_merge", &exchange_merge, "sequence shards: peer-memory exchange and merge in one kernel",
         py::arg("out_f32"), py::arg("lse"), py::arg("buf_ptrs"), py::arg("flag_ptrs"), py::arg("rank"), py::arg("seq"));
-  m.def("index_blocks", &index_blocks, "token-index blocks of one step", py::arg("ids"), py::arg("T"), py::arg("out"));
+  m.def("index_blocks", &index_blocks, "token-index blocks of one step", py::arg("ids"), py::arg("T"), py::arg("out"),
+        py::arg("t_dev") = py::none());
+  m.def("advance", &advance, "device-resident sequence length += delta, in stream order", py::arg("t_dev"),
+        py::arg("delta") = 1);
   m.def("set_option", &set_option, "process-wide option, e.g. (\"decode_path\", 1) for the exact-order kernels",
         py::arg("name"), py::arg("value"));
   m.def("get_option", &get_option, py::arg("name"));

@@ -154,17 +154,34 @@ class RefreshLayer:
             return min(cfg.max_age, cfg.calib_warm[1])
         return cfg.max_age
 
+    def graph_scalars(self) -> tuple:
+        """The host-decided scalars the next step passes to the kernels; a captured step is valid
+        while they stay the same (`kvskip_b200.graph.StepGraph`)."""
+        cfg, t = self.cfg, self.t + 1
+        max_age = min(cfg.max_age, cfg.calib_warm[1]) if cfg.calib_warm and t < cfg.calib_warm[0] else cfg.max_age
+        return (max_age, cfg.calib is not None and t >= cfg.calib_hold)
+
+    def note_replayed(self) -> None:
+        """A captured step of this layer was replayed: keep the step counter in step."""
+        self.t += 1
+
     def uses_index(self) -> bool:
         return bool(self.cfg.index_heads) or self.cfg.calib_auto_ix is not None
 
     # ---- one decode step ------------------------------------------------------------------
-    def step(self, q, k, v, scale, idx_blocks=None):
+    def step(self, q, k, v, scale, idx_blocks=None, t_dev=None):
         """q [B,Hq,D]; k, v [B,Hkv,T,D] views that already hold the token of this step at T-1.
         idx_blocks: bool/uint8 [B, >= nb] token-index blocks of this step (index heads / auto latch).
+        t_dev: one-element int32 CUDA tensor holding the sequence length; k and v are then views of
+        the whole provisioned cache (their length is a bound) and the three launches can be captured
+        in a CUDA graph and replayed while the length grows (see `kvskip_b200.graph`).
         Returns out bf16 [B,Hq,D]."""
         if q.dim() == 4:
             q = q.squeeze(2)
         if self.state is None:
+            if t_dev is not None:
+                raise ValueError("the first step of a layer builds the state on the host: run it with views of "
+                                 "the current length and without t_dev")
             return self._init(q, k, v, scale)
         cfg, s = self.cfg, self.state
         B, T = k.shape[0], k.shape[2]
@@ -191,9 +208,11 @@ class RefreshLayer:
                 s["cs_now"], s["trig"], s["block_idx"], s["block_cnt"], float(scale), float(cfg.delta),
                 int(self.max_age_now()), int(cfg.local), float(cfg.level), int(ns), idx, s["calib"] if cal else None,
                 s["est"], bool(cal and self.t >= cfg.calib_hold), kind, float(cfg.calib or 0.0),
-                bool(cfg.calib_free), s["aix"] if auto else None, float(cfg.calib_auto_ix or 0.0))
+                bool(cfg.calib_free), s["aix"] if auto else None, float(cfg.calib_auto_ix or 0.0), t_dev)
             self.last = {"blk_max": bmax, "blk_sum": bsum, "lse": lse, "first": False}
             return out
+        if t_dev is not None:
+            raise ValueError("a device-resident length needs a backend with fused_step")
         self.ops.plan(q, k, s["csum"], s["lse_ref"], s["cs_ref"], s["keep"], s["lse_att"], s["age"], s["flags"],
                       s["cs_now"], s["trig"], s["block_idx"], s["block_cnt"], float(scale), float(cfg.delta),
                       int(self.max_age_now()), int(cfg.local), True, idx, s["calib"] if cal else None, s["est"],

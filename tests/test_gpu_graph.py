@@ -1,0 +1,155 @@
+"""Device-resident sequence length and captured decode steps.
+
+The kernels that read the length from device memory must give bit for bit what the by-value
+launches give on views of that length, whatever the cache holds beyond it; a planner loop replayed
+from one CUDA graph must leave every state tensor identical to the same loop issued launch by
+launch."""
+import math
+
+import pytest
+import torch
+
+from kvskip_b200 import kvskip as K
+from kvskip_b200 import synth
+from kvskip_b200.graph import StepGraph
+from kvskip_b200.refresh import RefreshConfig, RefreshLayer
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _poison_tail(x, T):
+    """NaN in every row past T: nothing there may reach a result."""
+    x[:, :, T:] = float("nan")
+    return x
+
+
+@pytest.mark.parametrize("T", [1, 63, 64, 65, 1000, 1024, 1500])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_dense_with_device_length_matches_by_value(T, splits):
+    cap = 1536
+    q, k, v, scale = synth.dense_case(700 + T, 2, cap)
+    q, k, v = q.to(DEV), _poison_tail(k.to(DEV), T), _poison_tail(v.to(DEV), T)
+    t_dev = torch.tensor([T], dtype=torch.int32, device=DEV)
+    a = K.decode(q, k[:, :, :T], v[:, :, :T], scale, stats=True, out_f32=True, num_splits=splits)
+    b = K.decode(q, k, v, scale, stats=True, out_f32=True, num_splits=splits, t_dev=t_dev)
+    nb = math.ceil(T / 64)
+    assert torch.equal(a["out_f32"], b["out_f32"]) and torch.equal(a["out"], b["out"]) and torch.equal(a["lse"], b["lse"])
+    assert torch.equal(a["blk_max"], b["blk_max"][..., :nb]) and torch.equal(a["blk_sum"], b["blk_sum"][..., :nb])
+    assert (b["blk_max"][..., nb:] == float("-inf")).all() and (b["blk_sum"][..., nb:] == 0).all()
+    assert torch.isfinite(b["out_f32"]).all()
+    # the plain dense kernel (no statistics) too
+    c = K.decode(q, k, v, scale, out_f32=True, num_splits=splits, t_dev=t_dev)
+    d = K.decode(q, k[:, :, :T], v[:, :, :T], scale, out_f32=True, num_splits=splits)
+    assert torch.equal(c["out_f32"], d["out_f32"]) and torch.equal(c["lse"], d["lse"])
+
+
+@pytest.mark.parametrize("T", [130, 1000, 1471])
+def test_masked_with_device_length_matches_by_value(T):
+    cap, B, Hkv = 1536, 2, 8
+    q, k, v, scale = synth.dense_case(800 + T, B, cap)
+    q, k, v = q.to(DEV), _poison_tail(k.to(DEV), T), _poison_tail(v.to(DEV), T)
+    nb, nbc = math.ceil(T / 64), cap // 64
+    keep = torch.rand(B, Hkv, nb, generator=torch.Generator().manual_seed(T)) < 0.4
+    keep[..., 0] = True
+    keep[..., -1] = True                                   # the ragged newest block is read
+    keep[1, 3] = False                                     # one empty list
+    plan = K.make_plan(keep.to(DEV))
+    wide = torch.zeros(B, Hkv, nbc, dtype=torch.int32, device=DEV)
+    wide[..., :nb] = plan.block_idx
+    t_dev = torch.tensor([T], dtype=torch.int32, device=DEV)
+    for splits in (1, 3):
+        a = K.decode(q, k[:, :, :T], v[:, :, :T], scale, plan=plan, stats=True, out_f32=True, num_splits=splits)
+        b = K.decode(q, k, v, scale, plan=K.Plan(wide, plan.block_cnt, plan.max_cnt, nbc), stats=True, out_f32=True,
+                     num_splits=splits, t_dev=t_dev)
+        assert torch.equal(a["out_f32"], b["out_f32"]) and torch.equal(a["lse"], b["lse"])
+        assert torch.equal(a["blk_max"], b["blk_max"][..., :nb]) and torch.equal(a["blk_sum"], b["blk_sum"][..., :nb])
+        assert (b["blk_max"][..., nb:] == float("-inf")).all() and (b["blk_sum"][..., nb:] == 0).all()
+
+
+def test_exact_path_refuses_device_length():
+    q, k, v, scale = synth.dense_case(1, 1, 256)
+    t_dev = torch.tensor([200], dtype=torch.int32, device=DEV)
+    K.ext().set_option("decode_path", 1)
+    try:
+        with pytest.raises(RuntimeError, match="tensor-core path"):
+            K.decode(q.to(DEV), k.to(DEV), v.to(DEV), scale, t_dev=t_dev)
+    finally:
+        K.ext().set_option("decode_path", 0)
+
+
+def test_advance_and_index_blocks_with_device_length():
+    B, T, cap = 3, 700, 1024
+    ids = synth.token_ids_with_repeats(5, B, cap).to(DEV)
+    nbc = cap // 64 + 4
+    t_dev = torch.tensor([T - 2], dtype=torch.int32, device=DEV)
+    K.ext().advance(t_dev, 2)
+    assert int(t_dev) == T
+    a = torch.zeros(B, nbc, dtype=torch.uint8, device=DEV)
+    b = torch.ones(B, nbc, dtype=torch.uint8, device=DEV)      # the launch clears it
+    K.ext().index_blocks(ids, T, a)
+    K.ext().index_blocks(ids, cap, b, t_dev)
+    assert torch.equal(a, b) and int(a.sum()) > 0
+
+
+VARIANTS = {
+    "plain": dict(dense_heads=(6,)),
+    "peak_auto_warm": dict(calib=0.05, calib_warm=(12, 8), calib_kind="peak", calib_auto_ix=0.001),
+    "logit_union": dict(calib=0.3, calib_hold=6, calib_kind="logit", index_heads=(2,), index_union=True),
+}
+
+
+@pytest.mark.parametrize("name", list(VARIANTS))
+def test_planner_loop_replayed_from_a_graph_matches_launches(name):
+    """40 steps of two layers: launch by launch on views of the current length, and as one captured
+    step replayed with the length on the device.  Outputs and every planner state tensor are equal
+    after every step; the host-decided scalars change during the loop, so the step is captured
+    more than once in the variants that have a warm-up or a hold period."""
+    T0, steps, B, L = 4096 - 20, 40, 2, 2
+    walks = [synth.planner_walk(20 + l, T0, steps, B=B) for l in range(L)]
+    ids = synth.token_ids_with_repeats(11, B, T0 + steps).to(DEV)
+    ks = [_poison_tail(w.k.to(DEV).clone(), T0 + 1) for w in walks]     # rows of later steps filled in as we go
+    vs = [_poison_tail(w.v.to(DEV).clone(), T0 + 1) for w in walks]
+    qs = [w.q.to(DEV) for w in walks]
+    cap = T0 + steps
+    cfg = RefreshConfig(**VARIANTS[name])
+    eager = [RefreshLayer(cfg) for _ in range(L)]
+    graphed = [RefreshLayer(cfg) for _ in range(L)]
+    nbc = math.ceil((T0 + 1) / 64) + cfg.margin
+    idx_a = torch.zeros(B, nbc, dtype=torch.uint8, device=DEV)
+    idx_b = torch.zeros(B, nbc, dtype=torch.uint8, device=DEV)
+    q_buf = torch.zeros(L, *qs[0][0].shape, dtype=qs[0].dtype, device=DEV)
+    t_dev = torch.tensor([T0], dtype=torch.int32, device=DEV)
+
+    def launch():
+        K.ext().advance(t_dev, 1)
+        K.ext().index_blocks(ids, cap, idx_b, t_dev)
+        return [graphed[l].step(q_buf[l], ks[l], vs[l], walks[l].scale, idx_b, t_dev=t_dev) for l in range(L)]
+
+    g = StepGraph(launch, graphed, eager=1)
+    for t in range(steps):
+        T = T0 + t + 1
+        for l in range(L):                                   # the token of this step enters the cache
+            ks[l][:, :, T - 1] = walks[l].k[:, :, T - 1].to(DEV)
+            vs[l][:, :, T - 1] = walks[l].v[:, :, T - 1].to(DEV)
+            q_buf[l].copy_(qs[l][t])
+        K.ext().index_blocks(ids, T, idx_a)
+        out_a = [eager[l].step(qs[l][t], ks[l][:, :, :T], vs[l][:, :, :T], walks[l].scale, idx_a) for l in range(L)]
+        if t == 0:      # the first step builds the state on the host, from views of the current length
+            out_b = [graphed[l].step(qs[l][t], ks[l][:, :, :T], vs[l][:, :, :T], walks[l].scale, idx_a) for l in range(L)]
+            K.ext().advance(t_dev, 1)
+        else:
+            out_b = g.step()
+        assert int(t_dev) == T
+        for l in range(L):
+            assert torch.equal(out_a[l], out_b[l]), f"output of layer {l} differs at step {t}"
+            assert torch.isfinite(out_b[l].float()).all()
+            for key in ("trig", "block_cnt", "age", "keep", "aix", "calib", "est", "lse_att", "cs_now", "lse_ref",
+                        "cs_ref", "csum"):
+                assert torch.equal(eager[l].state[key], graphed[l].state[key]), f"{key} of layer {l} differs at step {t}"
+            nb = math.ceil(T / 64)
+            assert torch.equal(eager[l].read_mask(nb), graphed[l].read_mask(nb))
+            assert eager[l].t == graphed[l].t
+    assert g.replays == steps - 2                        # first step on the host, one eager step
+    assert g.captures == (1 if name == "plain" else 2)
+    assert K.ext().device_status() == 0
