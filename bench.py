@@ -252,16 +252,61 @@ def _planner_cases(dev, peak, K, synth, RefreshConfig, RefreshLayer, cases):
             torch.cuda.synchronize()
             return ev[0].elapsed_time(ev[1]) * 1e3 / ((steps - skip) * L), (int(read), total)
 
+        def run_graph():
+            """The same loop with every launch of a step (all layers) in one CUDA graph: the length
+            lives on the device, K/V are views of the whole cache, q of the step is copied into a
+            fixed buffer by one launch outside the graph; captured again when a host-decided
+            scalar of the policy changes (end of the warm-up period)."""
+            from kvskip_b200.graph import StepGraph
+            layers = [RefreshLayer(cfg) for _ in range(L)]
+            cap = T0 + steps
+            idx = torch.zeros(B, math.ceil((T0 + 1) / 64) + cfg.margin, dtype=torch.uint8, device=dev)
+            q_all = torch.stack([w.q for w in walks], dim=1)             # [steps, L, B, Hq, D]
+            q_buf = torch.empty_like(q_all[0])
+            t_dev = torch.tensor([T0], dtype=torch.int32, device=dev)
+
+            def launch():
+                K.ext().advance(t_dev, 1)
+                K.ext().index_blocks(ids, cap, idx, t_dev)
+                outs = [K.decode(q_buf[0], walks[0].k, walks[0].v, walks[0].scale, t_dev=t_dev)["out"]]
+                for l in range(1, L):
+                    outs.append(layers[l].step(q_buf[l], walks[l].k, walks[l].v, walks[l].scale, idx, t_dev=t_dev))
+                return outs
+
+            g = StepGraph(launch, layers[1:], eager=1)
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            for t in range(steps):
+                if t == skip:
+                    ev[0].record()
+                if t == 0:      # first step: state built on the host from views of the current length
+                    T = T0 + 1
+                    K.ext().index_blocks(ids, T, idx)
+                    for l in range(1, L):
+                        w = walks[l]
+                        layers[l].step(w.q[0], w.k[:, :, :T], w.v[:, :, :T], w.scale, idx)
+                    K.ext().advance(t_dev, 1)
+                    continue
+                q_buf.copy_(q_all[t])
+                g.step()
+            ev[1].record()
+            torch.cuda.synchronize()
+            return ev[0].elapsed_time(ev[1]) * 1e3 / ((steps - skip) * L), g.captures
+
         us, _ = run(False)
         _, (read, total) = run(True)
+        us_g, captures = run_graph()
         frac = read / max(1, total)
         # bytes actually read per layer-step, averaged over the L layers (layer 0 reads everything)
         nbytes = kv_bytes(B, T0 + steps // 2, (frac * (L - 1) + 1.0) / L)
         cases.append({"case": label, "us": round(us, 2), "blocks_read_planner_layers": round(frac, 4),
                       "GBps": round(nbytes / (us * 1e-6) / 1e9, 1),
                       "frac_of_peak": round(nbytes / (us * 1e-6) / 1e9 / peak, 4),
+                      "us_graph": round(us_g, 2), "GBps_graph": round(nbytes / (us_g * 1e-6) / 1e9, 1),
+                      "frac_of_peak_graph": round(nbytes / (us_g * 1e-6) / 1e9 / peak, 4), "graph_captures": captures,
                       "note": f"mean per layer-step over steps {skip}..{steps - 1}; one extension call per layer-step "
-                              "(3 launches), issued from Python, no host sync; bytes = K+V of the blocks read"})
+                              "(3 launches), issued from Python, no host sync; bytes = K+V of the blocks read; "
+                              "*_graph: the same steps replayed from one CUDA graph per step (device-resident "
+                              "length), captures inside the timed region included"})
 
     planner_case(32, 1, 32768, 128, 8, "planner loop: 32 layers x 128 steps, batch 1, 32k context, layer 0 dense, "
                                        "peak calibration, auto index")

@@ -249,6 +249,75 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
   pl_compact(nb, bi, p.block_cnt + bh, scan, [&](int i) { return pl_att[i] != 0; });
 }
 
+// The top-p cut of one query head by one warp: 32 bisection steps on the threshold lo in
+// [-80, 0] such that mass{y >= lo} >= level > mass{y >= hi}, y = x - lse.  Lane l owns blocks
+// l, l+32, ... and sums exp(y) over its members in ascending order, then the butterfly: the order
+// of the reference.  exp(y) is the same in every step, so it is evaluated once.  Once no block
+// lies between lo and hi every further step sees the same set, so the kept set {y >= lo} can no
+// longer change and the loop stops (the 32-step set is identical; lo itself is not an output).
+// Register form: R values of y and exp(y) per lane, nb <= 32 R.
+template <int R>
+__device__ __forceinline__ float pl_bisect_regs(const float* x, const int nb, const int lane, const float lse,
+                                                const float level) {
+  float y[R], e[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int i = lane + 32 * r;
+    y[r] = i < nb ? x[i] - lse : -INFINITY;
+    e[r] = i < nb ? __expf(x[i] - lse) : 0.f;
+  }
+  float lo = -80.f, hi = 0.f;
+  int n_lo = 0, n_hi = 0;       // blocks with y >= lo, y >= hi
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    n_lo += (y[r] >= lo) ? 1 : 0;
+    n_hi += (y[r] >= hi) ? 1 : 0;
+  }
+  n_lo = __reduce_add_sync(0xffffffffu, n_lo);
+  n_hi = __reduce_add_sync(0xffffffffu, n_hi);
+  for (int it = 0; it < 32 && n_lo != n_hi; ++it) {
+    const float mid = 0.5f * (lo + hi);
+    float a = 0.f;
+    int n_mid = 0;
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      if (y[r] >= mid) {
+        a += e[r];
+        ++n_mid;
+      }
+    n_mid = __reduce_add_sync(0xffffffffu, n_mid);
+    if (warp_sum(a) >= level) { lo = mid; n_lo = n_mid; } else { hi = mid; n_hi = n_mid; }
+  }
+  return lo;
+}
+
+// Shared-memory form for longer rows: ey[] receives exp(y).
+__device__ __forceinline__ float pl_bisect_smem(const float* x, float* ey, const int nb, const int lane,
+                                                const float lse, const float level) {
+  for (int i = lane; i < nb; i += 32) ey[i] = __expf(x[i] - lse);
+  float lo = -80.f, hi = 0.f;
+  int n_lo = 0, n_hi = 0;
+  for (int i = lane; i < nb; i += 32) {
+    n_lo += (x[i] - lse >= lo) ? 1 : 0;
+    n_hi += (x[i] - lse >= hi) ? 1 : 0;
+  }
+  n_lo = __reduce_add_sync(0xffffffffu, n_lo);
+  n_hi = __reduce_add_sync(0xffffffffu, n_hi);
+  for (int it = 0; it < 32 && n_lo != n_hi; ++it) {
+    const float mid = 0.5f * (lo + hi);
+    float a = 0.f;
+    int n_mid = 0;
+    for (int i = lane; i < nb; i += 32)
+      if (x[i] - lse >= mid) {
+        a += ey[i];
+        ++n_mid;
+      }
+    n_mid = __reduce_add_sync(0xffffffffu, n_mid);
+    if (warp_sum(a) >= level) { lo = mid; n_lo = n_mid; } else { hi = mid; n_hi = n_mid; }
+  }
+  return lo;
+}
+
 // With a device-resident length p.T bounds it and gives the row stride of the statistics.
 __global__ void __launch_bounds__(PL_THREADS) update_kernel(const kvskip_update_params p,
                                                             const int* __restrict__ t_dev) {
@@ -302,30 +371,17 @@ __global__ void __launch_bounds__(PL_THREADS) update_kernel(const kvskip_update_
     float se = 0.f;
     for (int i = lane; i < nb; i += 32) se += __expf(x[i] - mx);
     const float lse = mx + __logf(warp_sum(se));
-    // exp(y) is the same in all 32 bisection steps: evaluate it once, keep the summation order
-    for (int i = lane; i < nb; i += 32) ey[i] = __expf(x[i] - lse);
-    float lo = -80.f, hi = 0.f;   // mass{y >= lo} >= level > mass{y >= hi}, y = x - lse
-    int n_lo = 0, n_hi = 0;       // blocks with y >= lo, y >= hi
-    for (int i = lane; i < nb; i += 32) {
-      n_lo += (x[i] - lse >= lo) ? 1 : 0;
-      n_hi += (x[i] - lse >= hi) ? 1 : 0;
-    }
-    n_lo = __reduce_add_sync(0xffffffffu, n_lo);
-    n_hi = __reduce_add_sync(0xffffffffu, n_hi);
-    // Once no block lies between lo and hi every further step sees the same set, so the kept set
-    // {y >= lo} can no longer change: stop (the 32-step result is identical, lo itself is not output).
-    for (int it = 0; it < 32 && n_lo != n_hi; ++it) {
-      const float mid = 0.5f * (lo + hi);
-      float a = 0.f;
-      int n_mid = 0;
-      for (int i = lane; i < nb; i += 32)
-        if (x[i] - lse >= mid) {
-          a += ey[i];
-          ++n_mid;
-        }
-      n_mid = __reduce_add_sync(0xffffffffu, n_mid);
-      if (warp_sum(a) >= p.level) { lo = mid; n_lo = n_mid; } else { hi = mid; n_hi = n_mid; }
-    }
+    // Top-p cut: lo such that mass{y >= lo} >= level, y = x - lse.  With up to 2048 blocks a lane's
+    // values of y and exp(y) stay in registers for all 32 steps; longer rows use shared memory.
+    float lo;
+    if (nb <= 8 * 32) lo = pl_bisect_regs<8>(x, nb, lane, lse, p.level);
+    else if (nb <= 16 * 32) lo = pl_bisect_regs<16>(x, nb, lane, lse, p.level);
+    else if (nb <= 24 * 32) lo = pl_bisect_regs<24>(x, nb, lane, lse, p.level);
+    else if (nb <= 32 * 32) lo = pl_bisect_regs<32>(x, nb, lane, lse, p.level);
+    else if (nb <= 40 * 32) lo = pl_bisect_regs<40>(x, nb, lane, lse, p.level);
+    else if (nb <= 48 * 32) lo = pl_bisect_regs<48>(x, nb, lane, lse, p.level);
+    else if (nb <= 64 * 32) lo = pl_bisect_regs<64>(x, nb, lane, lse, p.level);
+    else lo = pl_bisect_smem(x, ey, nb, lane, lse, p.level);
     for (int i = lane; i < nb; i += 32)
       if (x[i] - lse >= lo) skeep[i] = 1;
     for (int i = lane; i < p.NBC; i += 32) {
