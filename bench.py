@@ -237,6 +237,7 @@ def _planner_cases(dev, peak, K, synth, RefreshConfig, RefreshLayer, cases):
             for t in range(steps):
                 if t == skip:
                     ev[0].record()
+                    host0 = time.perf_counter()
                 T = T0 + t + 1
                 K.ext().index_blocks(ids, T, idx)
                 for l in range(L):
@@ -249,10 +250,11 @@ def _planner_cases(dev, peak, K, synth, RefreshConfig, RefreshLayer, cases):
                         read += layers[l].state["block_cnt"].sum()
                         total += B * HKV * math.ceil(T / 64)
             ev[1].record()
+            host_us = (time.perf_counter() - host0) * 1e6 / ((steps - skip) * L)
             torch.cuda.synchronize()
-            return ev[0].elapsed_time(ev[1]) * 1e3 / ((steps - skip) * L), (int(read), total)
+            return ev[0].elapsed_time(ev[1]) * 1e3 / ((steps - skip) * L), (int(read), total), host_us
 
-        def run_graph():
+        def run_graph(overlap=False):
             """The same loop with every launch of a step (all layers) in one CUDA graph: the length
             lives on the device, K/V are views of the whole cache, q of the step is copied into a
             fixed buffer by one launch outside the graph; captured again when a host-decided
@@ -264,20 +266,38 @@ def _planner_cases(dev, peak, K, synth, RefreshConfig, RefreshLayer, cases):
             q_all = torch.stack([w.q for w in walks], dim=1)             # [steps, L, B, Hq, D]
             q_buf = torch.empty_like(q_all[0])
             t_dev = torch.tensor([T0], dtype=torch.int32, device=dev)
+            side = torch.cuda.Stream(device=dev) if overlap else None
 
             def launch():
                 K.ext().advance(t_dev, 1)
                 K.ext().index_blocks(ids, cap, idx, t_dev)
                 outs = [K.decode(q_buf[0], walks[0].k, walks[0].v, walks[0].scale, t_dev=t_dev)["out"]]
                 for l in range(1, L):
-                    outs.append(layers[l].step(q_buf[l], walks[l].k, walks[l].v, walks[l].scale, idx, t_dev=t_dev))
+                    outs.append(layers[l].step(q_buf[l], walks[l].k, walks[l].v, walks[l].scale, idx, t_dev=t_dev,
+                                               update_stream=side))
+                if side is not None:
+                    torch.cuda.current_stream().wait_stream(side)
                 return outs
 
             g = StepGraph(launch, layers[1:], eager=1)
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            seg, seg_steps, seg_open, host_replay = [], 0, None, 0.0    # replay-only segments of the timed region
             for t in range(steps):
                 if t == skip:
                     ev[0].record()
+                if t >= skip:
+                    if g.will_capture():        # a capturing step is left out of the replay-only figure
+                        if seg_open is not None:
+                            e = torch.cuda.Event(enable_timing=True)
+                            e.record()
+                            seg.append((seg_open, e))
+                            seg_open = None
+                    elif seg_open is None:
+                        seg_open = torch.cuda.Event(enable_timing=True)
+                        seg_open.record()
+                    if seg_open is not None:
+                        seg_steps += 1
+                        h0 = time.perf_counter()
                 if t == 0:      # first step: state built on the host from views of the current length
                     T = T0 + 1
                     K.ext().index_blocks(ids, T, idx)
@@ -288,25 +308,40 @@ def _planner_cases(dev, peak, K, synth, RefreshConfig, RefreshLayer, cases):
                     continue
                 q_buf.copy_(q_all[t])
                 g.step()
+                if t >= skip and seg_open is not None:
+                    host_replay += time.perf_counter() - h0
             ev[1].record()
+            if seg_open is not None:
+                seg.append((seg_open, ev[1]))
             torch.cuda.synchronize()
-            return ev[0].elapsed_time(ev[1]) * 1e3 / ((steps - skip) * L), g.captures
+            replay_us = sum(a.elapsed_time(b) for a, b in seg) * 1e3 / max(1, seg_steps * L)
+            return (ev[0].elapsed_time(ev[1]) * 1e3 / ((steps - skip) * L), g.captures, replay_us,
+                    host_replay * 1e6 / max(1, seg_steps * L))
 
-        us, _ = run(False)
-        _, (read, total) = run(True)
-        us_g, captures = run_graph()
+        us, _, host_us = run(False)
+        _, (read, total), _ = run(True)
+        us_g, captures, us_replay, host_us_g = run_graph()
+        _, _, us_overlap, _ = run_graph(overlap=True)
         frac = read / max(1, total)
         # bytes actually read per layer-step, averaged over the L layers (layer 0 reads everything)
         nbytes = kv_bytes(B, T0 + steps // 2, (frac * (L - 1) + 1.0) / L)
         cases.append({"case": label, "us": round(us, 2), "blocks_read_planner_layers": round(frac, 4),
                       "GBps": round(nbytes / (us * 1e-6) / 1e9, 1),
                       "frac_of_peak": round(nbytes / (us * 1e-6) / 1e9 / peak, 4),
-                      "us_graph": round(us_g, 2), "GBps_graph": round(nbytes / (us_g * 1e-6) / 1e9, 1),
-                      "frac_of_peak_graph": round(nbytes / (us_g * 1e-6) / 1e9 / peak, 4), "graph_captures": captures,
+                      "host_us": round(host_us, 2),
+                      "us_graph": round(us_g, 2), "us_graph_replay": round(us_replay, 2),
+                      "host_us_graph_replay": round(host_us_g, 2),
+                      "GBps_graph_replay": round(nbytes / (us_replay * 1e-6) / 1e9, 1),
+                      "frac_of_peak_graph_replay": round(nbytes / (us_replay * 1e-6) / 1e9 / peak, 4),
+                      "us_graph_replay_update_overlapped": round(us_overlap, 2),
+                      "graph_captures": captures,
                       "note": f"mean per layer-step over steps {skip}..{steps - 1}; one extension call per layer-step "
                               "(3 launches), issued from Python, no host sync; bytes = K+V of the blocks read; "
-                              "*_graph: the same steps replayed from one CUDA graph per step (device-resident "
-                              "length), captures inside the timed region included"})
+                              "host_us: host time to issue a layer-step; us_graph: the same steps replayed from one "
+                              "CUDA graph per step (device-resident length), the capture at the end of the warm-up "
+                              "period included; *_graph_replay: steps that only replay; *_update_overlapped: `update` of a "
+                              "layer on a second stream inside the graph (its results are needed only by the "
+                              "same layer's next step), joined at the end of the step"})
 
     planner_case(32, 1, 32768, 128, 8, "planner loop: 32 layers x 128 steps, batch 1, 32k context, layer 0 dense, "
                                        "peak calibration, auto index")

@@ -59,6 +59,10 @@ class StepGraph:
         self.graph = None
         self.result = None
 
+    def will_capture(self) -> bool:
+        """True if the next `step()` records a new capture before replaying it."""
+        return self.eager <= 0 and (self.graph is None or self._scalars() != self.signature)
+
     def step(self):
         if self.eager > 0:
             self.eager -= 1

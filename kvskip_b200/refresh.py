@@ -169,12 +169,16 @@ class RefreshLayer:
         return bool(self.cfg.index_heads) or self.cfg.calib_auto_ix is not None
 
     # ---- one decode step ------------------------------------------------------------------
-    def step(self, q, k, v, scale, idx_blocks=None, t_dev=None):
+    def step(self, q, k, v, scale, idx_blocks=None, t_dev=None, update_stream=None):
         """q [B,Hq,D]; k, v [B,Hkv,T,D] views that already hold the token of this step at T-1.
         idx_blocks: bool/uint8 [B, >= nb] token-index blocks of this step (index heads / auto latch).
         t_dev: one-element int32 CUDA tensor holding the sequence length; k and v are then views of
         the whole provisioned cache (their length is a bound) and the three launches can be captured
         in a CUDA graph and replayed while the length grows (see `kvskip_b200.graph`).
+        update_stream: a second CUDA stream for `update`.  The attention output does not depend on
+        it (it prepares this layer's next step), so it can overlap whatever follows on the current
+        stream; the caller makes the current stream wait for update_stream before this layer's
+        next step (e.g. once at the end of a decode step).
         Returns out bf16 [B,Hq,D]."""
         if q.dim() == 4:
             q = q.squeeze(2)
@@ -201,6 +205,24 @@ class RefreshLayer:
         cal = cfg.calib is not None
         kind = CALIB_KINDS[cfg.calib_kind]
         auto = cfg.calib_auto_ix is not None
+        if hasattr(self.ops, "fused_step") and update_stream is not None:
+            ns = K.splits_for_unsynced_plan(B * k.shape[1], nb)
+            ext = K.ext()
+            ext.plan(q, k, s["csum"], s["lse_ref"], s["cs_ref"], s["keep"], s["lse_att"], s["age"], s["flags"],
+                     s["cs_now"], s["trig"], s["block_idx"], s["block_cnt"], float(scale), float(cfg.delta),
+                     int(self.max_age_now()), int(cfg.local), True, idx, s["calib"] if cal else None, s["est"],
+                     bool(cal and self.t >= cfg.calib_hold), kind, s["aix"] if auto else None, t_dev)
+            out, lse, bmax, bsum, _, _ = ext.decode(q, k, v, float(scale), s["block_idx"], s["block_cnt"], True, True,
+                                                    int(ns), 2, False, False, t_dev)
+            update_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(update_stream):
+                ext.update(bmax, bsum, s["trig"], s["cs_now"], s["keep"], s["lse_ref"], s["cs_ref"], s["lse_att"], T,
+                           float(cfg.level), int(cfg.local), s["flags"], idx, s["est"], s["calib"] if cal else None,
+                           float(cfg.calib or 0.0), bool(cfg.calib_free), kind, s["aix"] if auto else None,
+                           float(cfg.calib_auto_ix or 0.0), t_dev)
+            # the statistics stay referenced here until this layer's next step, past the join
+            self.last = {"blk_max": bmax, "blk_sum": bsum, "lse": lse, "first": False}
+            return out
         if hasattr(self.ops, "fused_step"):
             ns = K.splits_for_unsynced_plan(B * k.shape[1], nb)   # sized for every block: no host sync
             out, lse, bmax, bsum = self.ops.fused_step(

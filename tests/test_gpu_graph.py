@@ -99,12 +99,14 @@ VARIANTS = {
 }
 
 
+@pytest.mark.parametrize("overlap", [False, True], ids=["serial", "update_on_side_stream"])
 @pytest.mark.parametrize("name", list(VARIANTS))
-def test_planner_loop_replayed_from_a_graph_matches_launches(name):
+def test_planner_loop_replayed_from_a_graph_matches_launches(name, overlap):
     """40 steps of two layers: launch by launch on views of the current length, and as one captured
     step replayed with the length on the device.  Outputs and every planner state tensor are equal
     after every step; the host-decided scalars change during the loop, so the step is captured
-    more than once in the variants that have a warm-up or a hold period."""
+    more than once in the variants that have a warm-up or a hold period.  With `overlap` the
+    update kernels run on a second stream inside the graph, joined at the end of the step."""
     T0, steps, B, L = 4096 - 20, 40, 2, 2
     walks = [synth.planner_walk(20 + l, T0, steps, B=B) for l in range(L)]
     ids = synth.token_ids_with_repeats(11, B, T0 + steps).to(DEV)
@@ -121,10 +123,16 @@ def test_planner_loop_replayed_from_a_graph_matches_launches(name):
     q_buf = torch.zeros(L, *qs[0][0].shape, dtype=qs[0].dtype, device=DEV)
     t_dev = torch.tensor([T0], dtype=torch.int32, device=DEV)
 
+    side = torch.cuda.Stream() if overlap else None
+
     def launch():
         K.ext().advance(t_dev, 1)
         K.ext().index_blocks(ids, cap, idx_b, t_dev)
-        return [graphed[l].step(q_buf[l], ks[l], vs[l], walks[l].scale, idx_b, t_dev=t_dev) for l in range(L)]
+        outs = [graphed[l].step(q_buf[l], ks[l], vs[l], walks[l].scale, idx_b, t_dev=t_dev, update_stream=side)
+                for l in range(L)]
+        if side is not None:
+            torch.cuda.current_stream().wait_stream(side)
+        return outs
 
     g = StepGraph(launch, graphed, eager=1)
     for t in range(steps):

@@ -35,3 +35,68 @@ def test_reference_import_path_resolves_here():
     for name in ("ext", "num_sms", "num_splits_for", "make_plan", "block_weights", "always_keep", "select_blocks",
                  "pv", "vskip_two_pass", "vskip_one_pass"):
         assert hasattr(alias, name)
+
+
+def test_graph_scalars_follow_the_step_counter():
+    """The scalars a captured step freezes are those the next step would pass to the kernels: the
+    maximum age of the warm-up period and whether the correction is applied yet."""
+    from kvskip_b200.refresh import RefreshConfig, RefreshLayer
+    layer = RefreshLayer(RefreshConfig(calib=0.05, calib_warm=(4, 8), calib_hold=6, max_age=32), ops=object())
+    seen = []
+    for _ in range(8):
+        seen.append(layer.graph_scalars())
+        layer.note_replayed()
+        assert layer.max_age_now() == seen[-1][0]
+        assert (layer.t >= 6) == seen[-1][1]
+    assert seen[0] == (8, False) and seen[2] == (8, False) and seen[3] == (32, False) and seen[5] == (32, True)
+    assert RefreshLayer(RefreshConfig(), ops=object()).graph_scalars() == (32, False)
+
+
+def test_step_graph_runs_eager_steps_before_capturing(monkeypatch):
+    """StepGraph's bookkeeping with the CUDA graph replaced by a recorder: eager steps first, one
+    capture per distinct set of host-decided scalars, the layers' counters advanced on replays."""
+    import torch
+    from kvskip_b200 import graph as G
+
+    class FakeGraph:
+        def __init__(self):
+            self.fn = None
+
+        def replay(self):
+            calls.append("replay")
+
+    class FakeCapture:
+        def __init__(self, g):
+            pass
+
+        def __enter__(self):
+            calls.append("capture")
+
+        def __exit__(self, *a):
+            return False
+
+    class Layer:
+        t = 0
+
+        def graph_scalars(self):
+            return (8 if self.t + 1 < 4 else 32,)
+
+        def note_replayed(self):
+            self.t += 1
+
+    calls, layer = [], Layer()
+
+    def launch():
+        layer.t += 1
+        calls.append("launch")
+        return layer.t
+
+    monkeypatch.setattr(torch.cuda, "CUDAGraph", FakeGraph)
+    monkeypatch.setattr(torch.cuda, "graph", FakeCapture)
+    g = G.StepGraph(launch, [layer], eager=2)
+    assert not g.will_capture()
+    for _ in range(7):
+        g.step()
+    assert layer.t == 7 and g.captures == 2 and g.replays == 5
+    assert calls == ["launch", "launch", "capture", "launch", "replay", "capture", "launch", "replay", "replay", "replay",
+                     "replay"]
