@@ -226,6 +226,27 @@ int kvskip_launch_index_blocks_dyn(const int64_t* ids, int64_t ids_stride, int n
                                    uint8_t* out, int NBC, void* stream);
 int kvskip_launch_advance(int* t_dev, int delta, void* stream);
 
+/* Paged cache (no counterpart in the reference, which reads [B,Hkv,T,D] views; its notes name a
+ * cache in which a 64-token block is a page as the natural layout next to the block lists).
+ * k and v of the parameter block are page pools [num_pages, Hkv, 64, D] (k_sb = page stride, k_sh,
+ * k_st as usual, D contiguous); page_table int32 [B, max_pages] names the page of every 64-token
+ * block of every sequence, max_pages >= ceil(T/64).  Block lists, statistics and planner state keep
+ * their per-sequence block numbering.  An entry outside the pool reads as zeros in the attention
+ * kernel and is skipped (status word 0x300 / 0x301) where a single row is addressed.  t_dev may be
+ * null (length by value) or a device-resident length as above.  Tensor-core path only (D = 128);
+ * write_p is not supported.  `update` and the token index do not touch K/V and need no variant.
+ * kvskip_launch_append writes the K and V rows of the newest token (row T-1, T the length after
+ * the append) from k_new, v_new [B,Hkv,D] into a contiguous cache (page_table null; sb, sh, st its
+ * element strides) or into the pool. */
+int kvskip_launch_decode_paged(const kvskip_params* p, int D, int G, int stages, int masked, int stats, int load_v,
+                               const int32_t* page_table, int max_pages, int num_pages, const int* t_dev,
+                               void* stream);
+int kvskip_launch_plan_paged(const kvskip_plan_params* p, const int32_t* page_table, int max_pages, int num_pages,
+                             const int* t_dev, void* stream);
+int kvskip_launch_append(uint16_t* k, uint16_t* v, int64_t sb, int64_t sh, int64_t st, const uint16_t* k_new,
+                         const uint16_t* v_new, int B, int Hkv, int D, int T, const int* t_dev,
+                         const int32_t* page_table, int max_pages, int num_pages, void* stream);
+
 /* Process-wide options (no counterpart in the reference).
  *   "decode_path"  0 (default): tensor-core kernel for D = 128, exact-order kernel otherwise;
  *                  1: exact-order kernel everywhere -- scores, block statistics and outputs are

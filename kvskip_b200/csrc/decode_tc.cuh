@@ -246,7 +246,8 @@ __device__ __forceinline__ void tc_fill_gap(const kvskip_params& p, const int32_
 template <int NC, bool MASKED, bool STATS, bool LOAD_V>
 __global__ void __launch_bounds__((NC + 1) * 32, NC <= 3 ? 2 : 1)
 decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* __restrict__ split_done,
-                 const int min_blocks, const int* __restrict__ t_dev) {
+                 const int min_blocks, const int* __restrict__ t_dev, const int32_t* __restrict__ pages,
+                 const int max_pages) {
   using Cfg = TcCfg<NC, LOAD_V>;
   constexpr int G = 4, D = 128;
   constexpr int S = Cfg::kStages;
@@ -318,14 +319,19 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
       for (int i = 0; i < n; ++i) {
         const int s = i % S;
         if (i >= S && !mbar_wait(&empty[s], ((i / S) - 1) & 1, 0x200u + s)) break;
-        const int t0 = (MASKED ? list[i0 + i] : i0 + i) * TILE;
+        const int blk = MASKED ? list[i0 + i] : i0 + i;
+        // contiguous cache: rows blk*64.. of sequence b; paged cache: the whole page the table
+        // names for block blk (the maps then run over pages instead of sequences; an entry
+        // outside the pool is out of bounds for the map and reads as zeros)
+        const int t0 = pages ? 0 : blk * TILE;
+        const int bp = pages ? pages[static_cast<int64_t>(b) * max_pages + blk] : b;
         unsigned char* dst = ring + s * Cfg::kStageBytes;
         mbar_expect_tx(&full[s], Cfg::kStageBytes);
-        tma_load_4d(dst, &maps.k, &full[s], 0, t0, h, b);
-        tma_load_4d(dst + TC_HALF_BYTES, &maps.k, &full[s], 64, t0, h, b);
+        tma_load_4d(dst, &maps.k, &full[s], 0, t0, h, bp);
+        tma_load_4d(dst + TC_HALF_BYTES, &maps.k, &full[s], 64, t0, h, bp);
         if constexpr (LOAD_V) {
-          tma_load_4d(dst + 2 * TC_HALF_BYTES, &maps.v, &full[s], 0, t0, h, b);
-          tma_load_4d(dst + 3 * TC_HALF_BYTES, &maps.v, &full[s], 64, t0, h, b);
+          tma_load_4d(dst + 2 * TC_HALF_BYTES, &maps.v, &full[s], 0, t0, h, bp);
+          tma_load_4d(dst + 3 * TC_HALF_BYTES, &maps.v, &full[s], 64, t0, h, bp);
         }
       }
     }
@@ -343,10 +349,11 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
       if (!mbar_wait(&full[s], (i / S) & 1, 0x210u + s)) break;
       const uint32_t kbase = smem_u32(ring + s * Cfg::kStageBytes);
       if constexpr (LOAD_V) {
-        // Device-resident length: the tensor map reaches past T, so the rows of the last block
-        // beyond T hold whatever the cache holds there.  Their weights are zero, but 0 x NaN is
-        // not: clear those V rows (whole 128-byte rows of both halves, so the swizzle is moot).
-        if (t_dev != nullptr && blk * TILE + TILE > T) {
+        // Device-resident length or paged cache: the tensor map reaches past T, so the rows of the
+        // last block beyond T hold whatever the cache holds there.  Their weights are zero, but
+        // 0 x NaN is not: clear those V rows (whole 128-byte rows of both halves, so the swizzle
+        // is moot).
+        if ((t_dev != nullptr || pages != nullptr) && blk * TILE + TILE > T) {
           const int r0 = T - blk * TILE;
           unsigned char* vst = ring + s * Cfg::kStageBytes + 2 * TC_HALF_BYTES;
           for (int o = r0 * 128 + lane * 16; o < TILE * 128; o += 32 * 16) {

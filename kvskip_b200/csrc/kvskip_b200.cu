@@ -185,24 +185,34 @@ int split_done_region(int units, int** out) {
   return KVSKIP_OK;
 }
 
+// What the _dyn and _paged entry points add to a launch: the length on the device, a page table.
+struct DynArgs {
+  const int* t_dev = nullptr;
+  const int32_t* pages = nullptr;   // [B, max_pages] page of every 64-token block
+  int max_pages = 0;
+  int num_pages = 0;                // pages in the pool
+};
+
 template <int NC, bool MASKED, bool STATS, bool LOAD_V>
-int launch_tc_nc(const kvskip_params& p, const kvb::TmaMaps& maps, int* done, int min_blocks, const int* t_dev,
+int launch_tc_nc(const kvskip_params& p, const kvb::TmaMaps& maps, int* done, int min_blocks, const DynArgs& dyn,
                  cudaStream_t stream) {
   using Cfg = kvb::TcCfg<NC, LOAD_V>;
   auto kernel = kvb::decode_tc_kernel<NC, MASKED, STATS, LOAD_V>;
   if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes)) return rc;
   KVB_CUDA(launch_overlapped(kernel, dim3(p.num_splits, p.Hkv, p.B), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, p,
-                             maps, done, min_blocks, t_dev));
+                             maps, done, min_blocks, dyn.t_dev, dyn.pages, dyn.max_pages));
   return KVSKIP_OK;
 }
 
 template <bool MASKED, bool STATS, bool LOAD_V>
-int launch_tc(const kvskip_params& p, const int* t_dev, cudaStream_t stream) {
+int launch_tc(const kvskip_params& p, const DynArgs& dyn, cudaStream_t stream) {
   kvb::TmaMaps maps;
-  if (int rc = make_kv_map(&maps.k, p.k, p.k_sb, p.k_sh, p.k_st, p.B, p.Hkv, p.T, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+  // contiguous cache: (D, T, Hkv, B); paged cache: (D, 64, Hkv, pages) over the pool
+  const int map_b = dyn.pages ? dyn.num_pages : p.B, map_t = dyn.pages ? KVSKIP_TILE : p.T;
+  if (int rc = make_kv_map(&maps.k, p.k, p.k_sb, p.k_sh, p.k_st, map_b, p.Hkv, map_t, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
   if (LOAD_V) {
-    if (int rc = make_kv_map(&maps.v, p.v, p.v_sb, p.v_sh, p.v_st, p.B, p.Hkv, p.T, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+    if (int rc = make_kv_map(&maps.v, p.v, p.v_sb, p.v_sh, p.v_st, map_b, p.Hkv, map_t, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
   } else {
     maps.v = maps.k;
@@ -223,8 +233,8 @@ int launch_tc(const kvskip_params& p, const int* t_dev, cudaStream_t stream) {
   const bool multi_wave =
       !MASKED && total >= 4 * static_cast<int64_t>(sms) && g_half_cta.load(std::memory_order_relaxed);
   const int min_blocks = (total > sms) ? 24 : 1;
-  if (int rc = multi_wave ? launch_tc_nc<3, MASKED, STATS, LOAD_V>(p, maps, done, min_blocks, t_dev, stream)
-                          : launch_tc_nc<6, MASKED, STATS, LOAD_V>(p, maps, done, min_blocks, t_dev, stream))
+  if (int rc = multi_wave ? launch_tc_nc<3, MASKED, STATS, LOAD_V>(p, maps, done, min_blocks, dyn, stream)
+                          : launch_tc_nc<6, MASKED, STATS, LOAD_V>(p, maps, done, min_blocks, dyn, stream))
     return rc;
   if (LOAD_V && p.num_splits > 1 && done == nullptr) {
     kvb::merge_kernel<128><<<p.B * p.Hq, 128, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits,
@@ -235,13 +245,13 @@ int launch_tc(const kvskip_params& p, const int* t_dev, cudaStream_t stream) {
   return KVSKIP_OK;
 }
 
-int dispatch_tc(const kvskip_params& p, bool masked, bool stats, bool load_v, const int* t_dev, cudaStream_t s) {
-  if (!masked && !stats && load_v) return launch_tc<false, false, true>(p, t_dev, s);
-  if (!masked && stats && load_v) return launch_tc<false, true, true>(p, t_dev, s);
-  if (!masked && stats && !load_v) return launch_tc<false, true, false>(p, t_dev, s);
-  if (masked && !stats && load_v) return launch_tc<true, false, true>(p, t_dev, s);
-  if (masked && stats && load_v) return launch_tc<true, true, true>(p, t_dev, s);
-  if (masked && stats && !load_v) return launch_tc<true, true, false>(p, t_dev, s);
+int dispatch_tc(const kvskip_params& p, bool masked, bool stats, bool load_v, const DynArgs& dyn, cudaStream_t s) {
+  if (!masked && !stats && load_v) return launch_tc<false, false, true>(p, dyn, s);
+  if (!masked && stats && load_v) return launch_tc<false, true, true>(p, dyn, s);
+  if (!masked && stats && !load_v) return launch_tc<false, true, false>(p, dyn, s);
+  if (masked && !stats && load_v) return launch_tc<true, false, true>(p, dyn, s);
+  if (masked && stats && load_v) return launch_tc<true, true, true>(p, dyn, s);
+  if (masked && stats && !load_v) return launch_tc<true, true, false>(p, dyn, s);
   return fail(KVSKIP_E_ARG, "kvskip: unsupported flag combination (load_v=false needs stats=true)");
 }
 
@@ -335,9 +345,14 @@ int kvskip_max_smem_bytes(int D, int stages, int load_v) {
 }
 
 namespace {
-int decode_impl(const kvskip_params* p, int D, int G, int stages, int masked, int stats, int load_v, const int* t_dev,
+int decode_impl(const kvskip_params* p, int D, int G, int stages, int masked, int stats, int load_v, const DynArgs& dyn,
                 void* stream) {
   if (int rc = check_common(p, D, G)) return rc;
+  if (dyn.pages) {
+    if (dyn.num_pages < 1 || dyn.max_pages < (p->T + KVSKIP_TILE - 1) / KVSKIP_TILE)
+      return fail(KVSKIP_E_ARG, "paged cache: the page table needs an entry for every block of the sequence");
+    if (p->p_out) return fail(KVSKIP_E_ARG, "paged cache: write_p is not supported");
+  }
   if (stages != 2 && stages != 3) return fail(KVSKIP_E_ARG, "kvskip: unsupported head dim / stages");
   if (!load_v && !stats) return fail(KVSKIP_E_ARG, "kvskip: unsupported flag combination (load_v=false needs stats=true)");
   if (masked && (!p->block_idx || !p->block_cnt)) return fail(KVSKIP_E_ARG, "masked mode needs block_idx and block_cnt");
@@ -347,8 +362,10 @@ int decode_impl(const kvskip_params* p, int D, int G, int stages, int masked, in
     return fail(KVSKIP_E_ARG, "num_splits > 1 needs part_acc / part_ml scratch");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int path = g_decode_path.load(std::memory_order_relaxed);
-  if (D == 128 && path != 1) return dispatch_tc(*p, masked, stats, load_v, t_dev, s);
-  if (t_dev) return fail(KVSKIP_E_ARG, "a device-resident length needs the tensor-core path (D = 128, decode_path != 1)");
+  if (D == 128 && path != 1) return dispatch_tc(*p, masked, stats, load_v, dyn, s);
+  if (dyn.t_dev || dyn.pages)
+    return fail(KVSKIP_E_ARG,
+                "a device-resident length or a paged cache needs the tensor-core path (D = 128, decode_path != 1)");
   if (path == 2) return fail(KVSKIP_E_ARG, "the tensor-core path exists for D = 128 only");
   return D == 128 ? dispatch_exact<128>(*p, masked, stats, load_v, s) : dispatch_exact<64>(*p, masked, stats, load_v, s);
 }
@@ -356,13 +373,27 @@ int decode_impl(const kvskip_params* p, int D, int G, int stages, int masked, in
 
 int kvskip_launch_decode(const kvskip_params* p, int D, int G, int stages, int masked, int stats, int load_v,
                          void* stream) {
-  return decode_impl(p, D, G, stages, masked, stats, load_v, nullptr, stream);
+  return decode_impl(p, D, G, stages, masked, stats, load_v, DynArgs{}, stream);
 }
 
 int kvskip_launch_decode_dyn(const kvskip_params* p, int D, int G, int stages, int masked, int stats, int load_v,
                              const int* t_dev, void* stream) {
   if (!t_dev) return fail(KVSKIP_E_ARG, "t_dev is null");
-  return decode_impl(p, D, G, stages, masked, stats, load_v, t_dev, stream);
+  DynArgs dyn;
+  dyn.t_dev = t_dev;
+  return decode_impl(p, D, G, stages, masked, stats, load_v, dyn, stream);
+}
+
+int kvskip_launch_decode_paged(const kvskip_params* p, int D, int G, int stages, int masked, int stats, int load_v,
+                               const int32_t* page_table, int max_pages, int num_pages, const int* t_dev,
+                               void* stream) {
+  if (!page_table) return fail(KVSKIP_E_ARG, "page_table is null");
+  DynArgs dyn;
+  dyn.t_dev = t_dev;
+  dyn.pages = page_table;
+  dyn.max_pages = max_pages;
+  dyn.num_pages = num_pages;
+  return decode_impl(p, D, G, stages, masked, stats, load_v, dyn, stream);
 }
 
 // ---- split-K decode for callers that cannot allocate device memory -------------------------
@@ -461,7 +492,7 @@ int kvskip_launch_pv(const kvskip_params* p, int D, int G, void* stream) {
 }
 
 namespace {
-int plan_impl(const kvskip_plan_params* p, const int* t_dev, void* stream) {
+int plan_impl(const kvskip_plan_params* p, const DynArgs& dyn, void* stream) {
   if (!p) return fail(KVSKIP_E_ARG, "null parameter block");
   if (p->Hq != 4 * p->Hkv) return fail(KVSKIP_E_ARG, "planner kernels: D = 128, G = 4");
   const int nb = (p->T + KVSKIP_TILE - 1) / KVSKIP_TILE;
@@ -478,16 +509,32 @@ int plan_impl(const kvskip_plan_params* p, const int* t_dev, void* stream) {
   if (smem > 40 * 1024)
     if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::plan_kernel), 200 * 1024)) return rc;
   KVB_CUDA(launch_overlapped(kvb::plan_kernel, dim3(chunks, p->Hkv, p->B), dim3(kvb::PL_THREADS), smem,
-                             static_cast<cudaStream_t>(stream), *p, done, t_dev));
+                             static_cast<cudaStream_t>(stream), *p, done, dyn.t_dev, dyn.pages, dyn.max_pages,
+                             dyn.num_pages));
   return KVSKIP_OK;
 }
 }  // namespace
 
-int kvskip_launch_plan(const kvskip_plan_params* p, void* stream) { return plan_impl(p, nullptr, stream); }
+int kvskip_launch_plan(const kvskip_plan_params* p, void* stream) { return plan_impl(p, DynArgs{}, stream); }
 
 int kvskip_launch_plan_dyn(const kvskip_plan_params* p, const int* t_dev, void* stream) {
   if (!t_dev) return fail(KVSKIP_E_ARG, "t_dev is null");
-  return plan_impl(p, t_dev, stream);
+  DynArgs dyn;
+  dyn.t_dev = t_dev;
+  return plan_impl(p, dyn, stream);
+}
+
+int kvskip_launch_plan_paged(const kvskip_plan_params* p, const int32_t* page_table, int max_pages, int num_pages,
+                             const int* t_dev, void* stream) {
+  if (!page_table) return fail(KVSKIP_E_ARG, "page_table is null");
+  if (p && (num_pages < 1 || max_pages < (p->T + KVSKIP_TILE - 1) / KVSKIP_TILE))
+    return fail(KVSKIP_E_ARG, "paged cache: the page table needs an entry for every block of the sequence");
+  DynArgs dyn;
+  dyn.t_dev = t_dev;
+  dyn.pages = page_table;
+  dyn.max_pages = max_pages;
+  dyn.num_pages = num_pages;
+  return plan_impl(p, dyn, stream);
 }
 
 namespace {
@@ -613,6 +660,23 @@ int kvskip_launch_index_blocks_dyn(const int64_t* ids, int64_t ids_stride, int n
                                    uint8_t* out, int NBC, void* stream) {
   if (!t_dev) return fail(KVSKIP_E_ARG, "t_dev is null");
   return index_blocks_impl(ids, ids_stride, n, T_bound, t_dev, out, NBC, stream);
+}
+
+int kvskip_launch_append(uint16_t* k, uint16_t* v, int64_t sb, int64_t sh, int64_t st, const uint16_t* k_new,
+                         const uint16_t* v_new, int B, int Hkv, int D, int T, const int* t_dev,
+                         const int32_t* page_table, int max_pages, int num_pages, void* stream) {
+  if (!k || !v || !k_new || !v_new || B < 1 || Hkv < 1 || T < 1) return fail(KVSKIP_E_ARG, "append: bad arguments");
+  if (D % 8 || D < 8 || D > 1024) return fail(KVSKIP_E_ARG, "append: D must be a multiple of 8, at most 1024");
+  if ((sb | sh | st) % 8 || (reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                             reinterpret_cast<uintptr_t>(k_new) | reinterpret_cast<uintptr_t>(v_new)) % 16)
+    return fail(KVSKIP_E_ARG, "append: 16-byte aligned rows (strides multiples of 8 elements)");
+  if (B > 65535) return fail(KVSKIP_E_LIMIT, "B is a grid dim: at most 65535");
+  if (page_table && (num_pages < 1 || max_pages < (T + KVSKIP_TILE - 1) / KVSKIP_TILE))
+    return fail(KVSKIP_E_ARG, "paged cache: the page table needs an entry for every block of the sequence");
+  kvb::append_kernel<<<dim3(Hkv, B), D / 8, 0, static_cast<cudaStream_t>(stream)>>>(
+      k, v, sb, sh, st, k_new, v_new, D, T, t_dev, page_table, max_pages, num_pages);
+  KVB_CUDA(cudaGetLastError());
+  return KVSKIP_OK;
 }
 
 int kvskip_launch_advance(int* t_dev, int delta, void* stream) {

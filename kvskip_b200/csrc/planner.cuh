@@ -77,8 +77,12 @@ constexpr int PL_CHUNK = 32;   // blocks whose centroid scores one CTA computes 
 // head reading nb * 512 bytes of key sums is latency-bound at long contexts.
 // With a device-resident length (t_dev != nullptr) p.T is the bound the grid was sized for; CTAs
 // whose chunk lies beyond the current length leave without being counted.
+// With a paged cache (pages != nullptr) p.k is the page pool [pages, Hkv, 64, D] (k_sb = page stride)
+// and the key of the new token is row (T-1) % 64 of page pages[b, (T-1) / 64].
 __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_params p, int* __restrict__ done,
-                                                          const int* __restrict__ t_dev) {
+                                                          const int* __restrict__ t_dev,
+                                                          const int32_t* __restrict__ pages, const int max_pages,
+                                                          const int num_pages) {
   const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int64_t bh = static_cast<int64_t>(b) * p.Hkv + h;
@@ -110,9 +114,19 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
   const int blk0 = chunk * PL_CHUNK;
   const int tok_blk = (T - 1) / TILE;
   if (p.add_token && tok_blk >= blk0 && tok_blk < blk0 + PL_CHUNK) {   // D == 128 == PL_THREADS
-    const __nv_bfloat16* kr = reinterpret_cast<const __nv_bfloat16*>(p.k) + b * p.k_sb + h * p.k_sh +
-                              static_cast<int64_t>(T - 1) * p.k_st;
-    csum[static_cast<int64_t>(tok_blk) * PL_D + tid] += __bfloat162float(kr[tid]);
+    int64_t seq = b, row = T - 1;
+    if (pages) {
+      seq = pages[static_cast<int64_t>(b) * max_pages + tok_blk];
+      row = (T - 1) % TILE;
+      if (seq < 0 || seq >= num_pages) {   // a table entry outside the pool: nothing is read
+        if (tid == 0) atomicCAS(&g_status, 0u, 0x300u);
+        seq = -1;
+      }
+    }
+    if (seq >= 0) {
+      const __nv_bfloat16* kr = reinterpret_cast<const __nv_bfloat16*>(p.k) + seq * p.k_sb + h * p.k_sh + row * p.k_st;
+      csum[static_cast<int64_t>(tok_blk) * PL_D + tid] += __bfloat162float(kr[tid]);
+    }
   }
   __syncthreads();
 
@@ -430,6 +444,30 @@ __global__ void __launch_bounds__(256) index_blocks_kernel(const int64_t* __rest
     out[static_cast<int64_t>(r) * NBC + t / TILE] = 1;
     out[static_cast<int64_t>(r) * NBC + (t + 1) / TILE] = 1;
   }
+}
+
+// The new token's K and V rows into the cache: grid (Hkv, B) x D/8 threads, 16 bytes per thread
+// and tensor.  T (or *t_dev) is the length after the append, so the row is T-1; with a page table
+// it is row (T-1) % 64 of page pages[b, (T-1) / 64].
+__global__ void append_kernel(uint16_t* __restrict__ k, uint16_t* __restrict__ v, const int64_t sb, const int64_t sh,
+                              const int64_t st, const uint16_t* __restrict__ k_new, const uint16_t* __restrict__ v_new,
+                              const int D, int T, const int* __restrict__ t_dev, const int32_t* __restrict__ pages,
+                              const int max_pages, const int num_pages) {
+  const int h = blockIdx.x, b = blockIdx.y, Hkv = gridDim.x;
+  if (t_dev) T = max(1, min(*t_dev, T));
+  int64_t seq = b, row = T - 1;
+  if (pages) {
+    seq = pages[static_cast<int64_t>(b) * max_pages + (T - 1) / TILE];
+    row = (T - 1) % TILE;
+    if (seq < 0 || seq >= num_pages) {
+      if (threadIdx.x == 0) atomicCAS(&g_status, 0u, 0x301u);
+      return;
+    }
+  }
+  const int64_t dst = seq * sb + h * sh + row * st + 8 * threadIdx.x;
+  const int64_t src = (static_cast<int64_t>(b) * Hkv + h) * D + 8 * threadIdx.x;
+  *reinterpret_cast<uint4*>(k + dst) = *reinterpret_cast<const uint4*>(k_new + src);
+  *reinterpret_cast<uint4*>(v + dst) = *reinterpret_cast<const uint4*>(v_new + src);
 }
 
 // The device-resident sequence length of a captured decode step: one thread adds delta.

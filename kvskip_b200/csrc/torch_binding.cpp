@@ -67,6 +67,28 @@ const int* tdev_ptr(const c10::optional<at::Tensor>& t_dev) {
   return t_dev->data_ptr<int32_t>();
 }
 
+// Page table of a paged cache: contiguous int32 [B, max_pages]; the pools are [pages, Hkv, 64, D].
+struct Paged {
+  const int32_t* table = nullptr;
+  int max_pages = 0, num_pages = 0;
+};
+Paged paged_args(const c10::optional<at::Tensor>& page_table, const at::Tensor& k, const at::Tensor* v, int64_t B,
+                 int64_t seq_len) {
+  Paged pg;
+  if (!page_table.has_value()) return pg;
+  const at::Tensor& t = *page_table;
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kInt && t.dim() == 2 && t.is_contiguous() && t.size(0) == B,
+              "page_table: contiguous int32 [B, max_pages]");
+  TORCH_CHECK(seq_len >= 1 && t.size(1) >= (seq_len + KVSKIP_TILE - 1) / KVSKIP_TILE,
+              "page_table: one entry per 64-token block of seq_len");
+  TORCH_CHECK(k.size(2) == KVSKIP_TILE && (!v || (v->size(2) == KVSKIP_TILE && v->size(0) == k.size(0))),
+              "paged cache: pools are [pages, Hkv, 64, D]");
+  pg.table = t.data_ptr<int32_t>();
+  pg.max_pages = static_cast<int>(t.size(1));
+  pg.num_pages = static_cast<int>(k.size(0));
+  return pg;
+}
+
 }  // namespace
 
 // [out bf16 [B,Hq,D] (undefined without load_v), lse [B,Hq], blk_max, blk_sum ([B,Hq,nb] or
@@ -75,14 +97,17 @@ std::vector<at::Tensor> decode(const at::Tensor& q, const at::Tensor& k, const a
                                const c10::optional<at::Tensor>& block_idx,
                                const c10::optional<at::Tensor>& block_cnt, bool stats, bool load_v,
                                int64_t num_splits, int64_t stages, bool want_f32, bool write_p,
-                               const c10::optional<at::Tensor>& t_dev) {
+                               const c10::optional<at::Tensor>& t_dev, const c10::optional<at::Tensor>& page_table,
+                               int64_t seq_len) {
   need_q(q);
   need_kv(k, "k");
   need_kv(v, "v");
   const c10::cuda::CUDAGuard guard(q.device());
-  const int64_t B = q.size(0), Hq = q.size(1), D = q.size(2), Hkv = k.size(1), T = k.size(2);
-  TORCH_CHECK(k.size(0) == B && v.size(0) == B && k.size(3) == D && v.size(3) == D && v.size(1) == Hkv &&
-                  v.size(2) == T, "shape mismatch between q, k, v");
+  const int64_t B = q.size(0), Hq = q.size(1), D = q.size(2), Hkv = k.size(1);
+  const Paged pg = paged_args(page_table, k, &v, B, seq_len);
+  const int64_t T = pg.table ? seq_len : k.size(2);
+  TORCH_CHECK((pg.table || (k.size(0) == B && v.size(0) == B)) && k.size(3) == D && v.size(3) == D &&
+                  v.size(1) == Hkv && v.size(2) == k.size(2), "shape mismatch between q, k, v");
   TORCH_CHECK(Hq % Hkv == 0, "Hq must be a multiple of Hkv");
   TORCH_CHECK(num_splits >= 1, "num_splits >= 1");
   TORCH_CHECK(load_v || stats, "load_v=false only makes sense with stats=true");
@@ -107,6 +132,7 @@ std::vector<at::Tensor> decode(const at::Tensor& q, const at::Tensor& k, const a
 
   kvskip_params p{};
   fill_qkv(p, q, k, v);
+  p.T = static_cast<int32_t>(T);
   p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
   if (masked) {
     TORCH_CHECK(block_cnt.has_value(), "block_cnt is required with block_idx");
@@ -136,7 +162,11 @@ std::vector<at::Tensor> decode(const at::Tensor& q, const at::Tensor& k, const a
   p.nb = static_cast<int32_t>(nb);
   p.t_pad = nb * KVSKIP_TILE;
   if (write_p) p.p_out = u16m(pbuf);
-  if (const int* td = tdev_ptr(t_dev))
+  if (pg.table)
+    raise_on(kvskip_launch_decode_paged(&p, static_cast<int>(D), static_cast<int>(Hq / Hkv), static_cast<int>(stages),
+                                        masked, stats, load_v, pg.table, pg.max_pages, pg.num_pages, tdev_ptr(t_dev),
+                                        cur_stream()));
+  else if (const int* td = tdev_ptr(t_dev))
     raise_on(kvskip_launch_decode_dyn(&p, static_cast<int>(D), static_cast<int>(Hq / Hkv), static_cast<int>(stages),
                                       masked, stats, load_v, td, cur_stream()));
   else
@@ -243,10 +273,13 @@ void plan(const at::Tensor& q, const at::Tensor& k, at::Tensor& csum, const at::
           at::Tensor& block_cnt, double scale, double delta, int64_t max_age, int64_t local, bool add_token,
           const c10::optional<at::Tensor>& idx, const c10::optional<at::Tensor>& calib,
           const c10::optional<at::Tensor>& est, bool calib_on, int64_t calib_kind,
-          const c10::optional<at::Tensor>& aix, const c10::optional<at::Tensor>& t_dev) {
+          const c10::optional<at::Tensor>& aix, const c10::optional<at::Tensor>& t_dev,
+          const c10::optional<at::Tensor>& page_table, int64_t seq_len) {
   TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && q.dim() == 3 && q.stride(2) == 1, "q: CUDA bf16 [B, Hq, D]");
   need_kv(k, "k");
-  const int64_t B = q.size(0), Hq = q.size(1), D = q.size(2), Hkv = k.size(1), T = k.size(2);
+  const int64_t B = q.size(0), Hq = q.size(1), D = q.size(2), Hkv = k.size(1);
+  const Paged pg = paged_args(page_table, k, nullptr, B, seq_len);
+  const int64_t T = pg.table ? seq_len : k.size(2);
   TORCH_CHECK(D == 128 && Hq == 4 * Hkv, "planner kernels: D = 128, G = 4");
   need_f32(csum, "csum"); need_f32(lse_ref, "lse_ref"); need_f32(cs_ref, "cs_ref");
   need_f32(lse_att, "lse_att"); need_f32(cs_now, "cs_now");
@@ -304,7 +337,9 @@ void plan(const at::Tensor& q, const at::Tensor& k, at::Tensor& csum, const at::
   p.T = static_cast<int32_t>(T); p.NBC = static_cast<int32_t>(NBC);
   p.local = static_cast<int32_t>(local); p.max_age = static_cast<int32_t>(max_age); p.add_token = add_token;
   p.scale = static_cast<float>(scale); p.delta = static_cast<float>(delta);
-  if (const int* td = tdev_ptr(t_dev))
+  if (pg.table)
+    raise_on(kvskip_launch_plan_paged(&p, pg.table, pg.max_pages, pg.num_pages, tdev_ptr(t_dev), cur_stream()));
+  else if (const int* td = tdev_ptr(t_dev))
     raise_on(kvskip_launch_plan_dyn(&p, td, cur_stream()));
   else
     raise_on(kvskip_launch_plan(&p, cur_stream()));
@@ -375,12 +410,14 @@ std::vector<at::Tensor> refresh_step(const at::Tensor& q, const at::Tensor& k, c
                                      const c10::optional<at::Tensor>& idx, const c10::optional<at::Tensor>& calib,
                                      const c10::optional<at::Tensor>& est, bool calib_on, int64_t calib_kind,
                                      double calib_rate, bool calib_free, const c10::optional<at::Tensor>& aix,
-                                     double aix_thr, const c10::optional<at::Tensor>& t_dev) {
+                                     double aix_thr, const c10::optional<at::Tensor>& t_dev,
+                                     const c10::optional<at::Tensor>& page_table, int64_t seq_len) {
   plan(q, k, csum, lse_ref, cs_ref, keep, lse_att, age, flags, cs_now, trig, block_idx, block_cnt, scale, delta, max_age,
-       local, true, idx, calib, est, calib_on, calib_kind, aix, t_dev);
-  auto r = decode(q, k, v, scale, block_idx, block_cnt, true, true, num_splits, 2, false, false, t_dev);
-  update(r[2], r[3], trig, cs_now, keep, lse_ref, cs_ref, lse_att, k.size(2), level, local, flags, idx, est, calib,
-         calib_rate, calib_free, calib_kind, aix, aix_thr, t_dev);
+       local, true, idx, calib, est, calib_on, calib_kind, aix, t_dev, page_table, seq_len);
+  auto r = decode(q, k, v, scale, block_idx, block_cnt, true, true, num_splits, 2, false, false, t_dev, page_table,
+                  seq_len);
+  update(r[2], r[3], trig, cs_now, keep, lse_ref, cs_ref, lse_att, page_table.has_value() ? seq_len : k.size(2), level,
+         local, flags, idx, est, calib, calib_rate, calib_free, calib_kind, aix, aix_thr, t_dev);
   return {r[0], r[1], r[2], r[3]};
 }
 
@@ -473,6 +510,26 @@ void index_blocks(const at::Tensor& ids, int64_t T, at::Tensor& out, const c10::
                                         cur_stream()));
 }
 
+// The newest token's K and V rows (k_new, v_new [B,Hkv,D]) into row T-1 of a contiguous cache
+// [B,Hkv,cap,D] or, with a page table, of a page pool [pages,Hkv,64,D]; T is the length after the
+// append (read from t_dev if given, T then bounds it).
+void append(at::Tensor& k, at::Tensor& v, const at::Tensor& k_new, const at::Tensor& v_new, int64_t T,
+            const c10::optional<at::Tensor>& t_dev, const c10::optional<at::Tensor>& page_table) {
+  need_kv(k, "k"); need_kv(v, "v");
+  const int64_t B = k_new.size(0), Hkv = k.size(1), D = k.size(3);
+  TORCH_CHECK(k_new.is_cuda() && v_new.is_cuda() && k_new.scalar_type() == at::kBFloat16 &&
+                  v_new.scalar_type() == at::kBFloat16 && k_new.is_contiguous() && v_new.is_contiguous() &&
+                  k_new.dim() == 3 && k_new.sizes() == v_new.sizes() && k_new.size(1) == Hkv && k_new.size(2) == D,
+              "k_new, v_new: contiguous CUDA bf16 [B, Hkv, D]");
+  TORCH_CHECK(k.sizes() == v.sizes() && k.strides() == v.strides(), "k and v must share shape and strides");
+  const Paged pg = paged_args(page_table, k, &v, B, T);
+  TORCH_CHECK(pg.table || (k.size(0) == B && T >= 1 && T <= k.size(2)), "append: T within the cache");
+  const c10::cuda::CUDAGuard guard(k.device());
+  raise_on(kvskip_launch_append(u16m(k), u16m(v), k.stride(0), k.stride(1), k.stride(2), u16(k_new), u16(v_new),
+                                static_cast<int>(B), static_cast<int>(Hkv), static_cast<int>(D), static_cast<int>(T),
+                                tdev_ptr(t_dev), pg.table, pg.max_pages, pg.num_pages, cur_stream()));
+}
+
 // *t_dev += delta in stream order
 void advance(at::Tensor& t_dev, int64_t delta) {
   TORCH_CHECK(t_dev.is_cuda() && t_dev.scalar_type() == at::kInt && t_dev.numel() == 1,
@@ -505,7 +562,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("block_idx"), py::arg("block_cnt"), py::arg("scale"), py::arg("delta"), py::arg("max_age"),
         py::arg("local"), py::arg("add_token"), py::arg("idx") = py::none(), py::arg("calib") = py::none(),
         py::arg("est") = py::none(), py::arg("calib_on") = false, py::arg("calib_kind") = 0,
-        py::arg("aix") = py::none(), py::arg("t_dev") = py::none());
+        py::arg("aix") = py::none(), py::arg("t_dev") = py::none(), py::arg("page_table") = py::none(),
+        py::arg("seq_len") = 0);
   m.def("update", &update, "refresh planner: stored set and references (after the pass)",
         py::arg("blk_max"), py::arg("blk_sum"), py::arg("trig"), py::arg("cs_now"), py::arg("keep"),
         py::arg("lse_ref"), py::arg("cs_ref"), py::arg("lse_att"), py::arg("T"), py::arg("level"), py::arg("local"),
@@ -519,7 +577,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("decode", &decode, "split-K decode attention", py::arg("q"), py::arg("k"), py::arg("v"), py::arg("scale"),
         py::arg("block_idx") = py::none(), py::arg("block_cnt") = py::none(), py::arg("stats") = false,
         py::arg("load_v") = true, py::arg("num_splits") = 1, py::arg("stages") = 2, py::arg("want_f32") = false,
-        py::arg("write_p") = false, py::arg("t_dev") = py::none());
+        py::arg("write_p") = false, py::arg("t_dev") = py::none(), py::arg("page_table") = py::none(),
+        py::arg("seq_len") = 0);
   m.def("pv", &pv, "two-pass V-skip, pass 2", py::arg("P"), py::arg("v"), py::arg("blk_scale"), py::arg("block_idx"),
         py::arg("block_cnt"), py::arg("num_splits") = 1, py::arg("want_f32") = false);
   m.def("refresh_step", &refresh_step, "plan -> masked+stats attention -> update for one layer, one call",
@@ -529,7 +588,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("local"), py::arg("level"), py::arg("num_splits"), py::arg("idx") = py::none(),
         py::arg("calib") = py::none(), py::arg("est") = py::none(), py::arg("calib_on") = false,
         py::arg("calib_kind") = 0, py::arg("calib_rate") = 0.0, py::arg("calib_free") = false,
-        py::arg("aix") = py::none(), py::arg("aix_thr") = 0.0, py::arg("t_dev") = py::none());
+        py::arg("aix") = py::none(), py::arg("aix_thr") = 0.0, py::arg("t_dev") = py::none(),
+        py::arg("page_table") = py::none(), py::arg("seq_len") = 0);
   m.def("merge", &merge, "merge of R partial (max, sum, acc) rows", py::arg("part_acc"), py::arg("part_ml"));
   m.def("pack_partial", &pack_partial, "rank-local (out_f32, lse) -> packed (acc, m, l) rows", py::arg("out_f32"),
         py::arg("lse"));
@@ -538,6 +598,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("out_f32"), py::arg("lse"), py::arg("buf_ptrs"), py::arg("flag_ptrs"), py::arg("rank"), py::arg("seq"));
   m.def("index_blocks", &index_blocks, "token-index blocks of one step", py::arg("ids"), py::arg("T"), py::arg("out"),
         py::arg("t_dev") = py::none());
+  m.def("append", &append, "the newest token's K and V rows into the cache (contiguous or paged)", py::arg("k"),
+        py::arg("v"), py::arg("k_new"), py::arg("v_new"), py::arg("T"), py::arg("t_dev") = py::none(),
+        py::arg("page_table") = py::none());
   m.def("advance", &advance, "device-resident sequence length += delta, in stream order", py::arg("t_dev"),
         py::arg("delta") = 1);
   m.def("set_option", &set_option, "process-wide option, e.g. (\"decode_path\", 1) for the exact-order kernels",

@@ -121,15 +121,23 @@ def _q3(q):
 
 def decode(q, k, v, scale: float, *, plan: Plan | None = None, stats: bool = False, load_v: bool = True,
            num_splits: int | None = None, stages: int = 2, out_f32: bool = False, write_p: bool = False,
-           t_dev: torch.Tensor | None = None) -> dict:
+           t_dev: torch.Tensor | None = None, page_table: torch.Tensor | None = None,
+           seq_len: int | None = None) -> dict:
     """One layer's decode attention.  Returns dict(out bf16 [B,Hq,D] (None without load_v),
     lse fp32 [B,Hq], num_splits[, blk_max, blk_sum fp32 [B,Hq,nb]][, out_f32][, p fp16 [B,Hq,nb*64]]).
 
     t_dev (one-element int32 CUDA tensor, not in the reference): the sequence length is read from
     it on the device; k and v are then views of the whole provisioned cache and their length is
-    only a bound (it sizes the launch and the statistics rows).  For captured decode steps."""
+    only a bound (it sizes the launch and the statistics rows).  For captured decode steps.
+
+    page_table (int32 [B, max_pages], not in the reference) with seq_len: k and v are page pools
+    [pages, Hkv, 64, D] and block j of sequence b is page page_table[b, j] (`kvskip_b200.cache.PagedKV`)."""
     q = _q3(q)
     B, Hkv, T = q.shape[0], k.shape[1], k.shape[2]
+    if page_table is not None:
+        if seq_len is None:
+            raise ValueError("a paged cache needs seq_len")
+        T = int(seq_len)
     if num_splits is None:
         n_items = math.ceil(T / TILE) if plan is None else plan.max_cnt
         # the tensor-core kernel owns an SM; three CTAs of the exact-order kernel share one
@@ -140,7 +148,8 @@ def decode(q, k, v, scale: float, *, plan: Plan | None = None, stats: bool = Fal
             num_splits = num_splits_for(B * Hkv, n_items, sms=per_sm * num_sms())
     bi, bc = (None, None) if plan is None else (plan.block_idx, plan.block_cnt)
     out, lse, bmax, bsum, o32, pbuf = ext().decode(q, k, v, float(scale), bi, bc, stats, load_v,
-                                                   int(num_splits), int(stages), out_f32, write_p, t_dev)
+                                                   int(num_splits), int(stages), out_f32, write_p, t_dev,
+                                                   page_table, int(seq_len or 0))
     res = {"out": out if load_v else None, "lse": lse, "num_splits": num_splits}
     if stats:
         res["blk_max"], res["blk_sum"] = bmax, bsum

@@ -169,7 +169,7 @@ class RefreshLayer:
         return bool(self.cfg.index_heads) or self.cfg.calib_auto_ix is not None
 
     # ---- one decode step ------------------------------------------------------------------
-    def step(self, q, k, v, scale, idx_blocks=None, t_dev=None, update_stream=None):
+    def step(self, q, k, v, scale, idx_blocks=None, t_dev=None, update_stream=None, page_table=None, seq_len=None):
         """q [B,Hq,D]; k, v [B,Hkv,T,D] views that already hold the token of this step at T-1.
         idx_blocks: bool/uint8 [B, >= nb] token-index blocks of this step (index heads / auto latch).
         t_dev: one-element int32 CUDA tensor holding the sequence length; k and v are then views of
@@ -179,16 +179,22 @@ class RefreshLayer:
         it (it prepares this layer's next step), so it can overlap whatever follows on the current
         stream; the caller makes the current stream wait for update_stream before this layer's
         next step (e.g. once at the end of a decode step).
+        page_table, seq_len: k and v are page pools [pages,Hkv,64,D] and page_table int32
+        [B, max_pages] names the page of every block (`kvskip_b200.cache.PagedKV`); seq_len is the
+        length (the bound, with t_dev).  The first step of a layer needs contiguous views.
         Returns out bf16 [B,Hq,D]."""
         if q.dim() == 4:
             q = q.squeeze(2)
+        paged = page_table is not None
+        if paged and (seq_len is None or self.state is None or not hasattr(self.ops, "fused_step")):
+            raise ValueError("a paged cache needs seq_len, the CUDA backend, and a first step on contiguous views")
         if self.state is None:
             if t_dev is not None:
                 raise ValueError("the first step of a layer builds the state on the host: run it with views of "
                                  "the current length and without t_dev")
             return self._init(q, k, v, scale)
         cfg, s = self.cfg, self.state
-        B, T = k.shape[0], k.shape[2]
+        B, T = q.shape[0], (int(seq_len) if paged else k.shape[2])
         nb = math.ceil(T / BLOCK)
         if nb > s["NBC"]:
             self._grow(nb + cfg.margin)
@@ -211,9 +217,9 @@ class RefreshLayer:
             ext.plan(q, k, s["csum"], s["lse_ref"], s["cs_ref"], s["keep"], s["lse_att"], s["age"], s["flags"],
                      s["cs_now"], s["trig"], s["block_idx"], s["block_cnt"], float(scale), float(cfg.delta),
                      int(self.max_age_now()), int(cfg.local), True, idx, s["calib"] if cal else None, s["est"],
-                     bool(cal and self.t >= cfg.calib_hold), kind, s["aix"] if auto else None, t_dev)
+                     bool(cal and self.t >= cfg.calib_hold), kind, s["aix"] if auto else None, t_dev, page_table, T)
             out, lse, bmax, bsum, _, _ = ext.decode(q, k, v, float(scale), s["block_idx"], s["block_cnt"], True, True,
-                                                    int(ns), 2, False, False, t_dev)
+                                                    int(ns), 2, False, False, t_dev, page_table, T)
             update_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(update_stream):
                 ext.update(bmax, bsum, s["trig"], s["cs_now"], s["keep"], s["lse_ref"], s["cs_ref"], s["lse_att"], T,
@@ -230,7 +236,8 @@ class RefreshLayer:
                 s["cs_now"], s["trig"], s["block_idx"], s["block_cnt"], float(scale), float(cfg.delta),
                 int(self.max_age_now()), int(cfg.local), float(cfg.level), int(ns), idx, s["calib"] if cal else None,
                 s["est"], bool(cal and self.t >= cfg.calib_hold), kind, float(cfg.calib or 0.0),
-                bool(cfg.calib_free), s["aix"] if auto else None, float(cfg.calib_auto_ix or 0.0), t_dev)
+                bool(cfg.calib_free), s["aix"] if auto else None, float(cfg.calib_auto_ix or 0.0), t_dev,
+                page_table, T)
             self.last = {"blk_max": bmax, "blk_sum": bsum, "lse": lse, "first": False}
             return out
         if t_dev is not None:

@@ -100,3 +100,32 @@ def test_step_graph_runs_eager_steps_before_capturing(monkeypatch):
     assert layer.t == 7 and g.captures == 2 and g.replays == 5
     assert calls == ["launch", "launch", "capture", "launch", "replay", "capture", "launch", "replay", "replay", "replay",
                      "replay"]
+
+
+def test_paged_cache_bookkeeping_on_cpu():
+    """Page hand-out, prefill scatter and gather of PagedKV need no GPU (the append kernel does)."""
+    import torch
+    from kvskip_b200.cache import PagedKV
+    B, H, D, T = 3, 2, 16, 150
+    g = torch.Generator().manual_seed(0)
+    k = torch.randn(B, H, T, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, H, T, D, generator=g).to(torch.bfloat16)
+    pg = PagedKV(B * 4 + 2, B, H, D, 256, "cpu", order="shuffled", seed=1)
+    pg.write(k, v)
+    used = pg.table_host[:, :3].reshape(-1).tolist()
+    assert len(set(used)) == B * 3 and (pg.table_host[:, 3:] == -1).all()       # distinct pages, none beyond
+    gk, gv = pg.gather()
+    assert torch.equal(gk, k) and torch.equal(gv, v)
+    pg.reserve(256)
+    assert (pg.table_host >= 0).all() and len(set(pg.table_host.reshape(-1).tolist())) == B * 4
+    for _ in range(256 - T):
+        pg.note_replayed()
+    assert pg.get_seq_length() == 256
+    import pytest
+    with pytest.raises(RuntimeError, match="reserved"):
+        pg.note_replayed()
+    with pytest.raises(RuntimeError, match="exceed"):
+        pg.reserve(257)
+    small = PagedKV(2, B, H, D, 256, "cpu")
+    with pytest.raises(RuntimeError, match="exhausted"):
+        small.reserve(64)
