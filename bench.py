@@ -202,6 +202,19 @@ def _attention_cases(dev, K, synth, g, add, flush):
             add(f"dense B={B} T={T}", time_cuda(lambda: K.decode(q, k, v, D ** -0.5), 30, flush), kv_bytes(B, T),
                 splits=ns)
             del q, k, v
+    # the same dense pass over a paged cache: 64-token pages handed out in shuffled order
+    for B in (1, 16):
+        T = 65536
+        nb = T // 64
+        q = (torch.randn(B, HQ, D, device=dev, generator=g) / math.sqrt(D)).to(torch.bfloat16)
+        pool_k = torch.randn(B * nb, HKV, 64, D, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+        pool_v = torch.randn(B * nb, HKV, 64, D, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+        table = torch.randperm(B * nb, device=dev, generator=g).to(torch.int32).view(B, nb).contiguous()
+        ns = K.num_splits_for(B * HKV, nb)
+        add(f"dense, paged cache (shuffled 64-token pages) B={B} T={T}",
+            time_cuda(lambda: K.decode(q, pool_k, pool_v, D ** -0.5, page_table=table, seq_len=T), 30, flush),
+            kv_bytes(B, T), splits=ns)
+        del q, pool_k, pool_v, table
     # masked + statistics and single-pass V-skip: batch 1, 64k, planted bodies (union about 55 %)
     q, k, v, scale, keep = synth.body_union_case(3, T_HEAD)
     q, k, v, keep = q.to(dev), k.to(dev), v.to(dev), keep.to(dev)
