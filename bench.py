@@ -515,14 +515,20 @@ def main():
         from kvskip_b200.refresh import RefreshConfig, RefreshLayer
         del k, v
         T0 = args.context or (T_HEAD // 2 if B > 4 else T_HEAD)
-        walk = synth.planner_walk_device(5, T0, args.warmup + args.steps + 1, dev, B=B)
-        layer = RefreshLayer(RefreshConfig())
+        n_steps = args.warmup + args.steps + 1
+        walk = synth.planner_walk_device(5, T0, n_steps, dev, B=B)
+        ids = synth.token_ids_with_repeats(99, B, T0 + n_steps).to(dev)
+        # the policy of the planner-loop cases: peak calibration, warm-up period, automatic token index
+        cfg = RefreshConfig(calib=0.05, calib_warm=(32, 8), calib_kind="peak", calib_auto_ix=0.1)
+        layer = RefreshLayer(cfg)
+        idx = torch.zeros(B, math.ceil((T0 + 1) / 64) + cfg.margin, dtype=torch.uint8, device=dev)
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-        for t in range(args.warmup + args.steps + 1):
+        for t in range(n_steps):
             if t == args.warmup + 1:
                 ev[0].record()
             Tt = T0 + t + 1
-            layer.step(walk.q[t], walk.k[:, :, :Tt], walk.v[:, :, :Tt], walk.scale)
+            K.ext().index_blocks(ids, Tt, idx)
+            layer.step(walk.q[t], walk.k[:, :, :Tt], walk.v[:, :, :Tt], walk.scale, idx)
         ev[1].record()
         torch.cuda.synchronize()
         print(json.dumps({"profile": "planner", "batch": B, "context": T0,
