@@ -184,16 +184,6 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
   __threadfence();
   if (tid == 0) done[bh] = 0;
 
-  // the scalars the decision needs at the very end are requested now, by the thread that decides,
-  // so their round trips overlap the fold instead of following it one after the other
-  float pre_lse_att[PL_G] = {0.f, 0.f, 0.f, 0.f}, pre_calib = 0.f;
-  int pre_age = 0;
-  if (tid == 0) {
-#pragma unroll
-    for (int g = 0; g < PL_G; ++g) pre_lse_att[g] = p.lse_att[static_cast<int64_t>(b) * p.Hq + h * PL_G + g];
-    if (p.calib && p.calib_on) pre_calib = p.calib[bh];
-    pre_age = p.age[bh];
-  }
   // attended flags of every block into shared memory: independent, coalesced loads
   extern __shared__ unsigned char pl_att[];   // [nb]
   for (int i = tid; i < nb; i += PL_THREADS) pl_att[i] = attended(i) ? 1 : 0;
@@ -249,14 +239,14 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
         if (wS[w][g] > 0.f) S += wS[w][g] * __expf(wM[w][g] - M);
       if (S > 0.f) {
         const float est = M + __logf(S);
-        miss = fmaxf(miss, 1.f / (1.f + __expf(pre_lse_att[g] - est)));
+        miss = fmaxf(miss, 1.f / (1.f + __expf(p.lse_att[static_cast<int64_t>(b) * p.Hq + h * PL_G + g] - est)));
       }
     }
     if (p.est) p.est[bh] = miss;
     float dec = miss;
     if (p.calib && p.calib_on)
-      dec = p.calib_kind ? miss + pre_calib : 1.f / (1.f + __expf(-(pl_logit(miss) + pre_calib)));
-    const int a = pre_age + 1;
+      dec = p.calib_kind ? miss + p.calib[bh] : 1.f / (1.f + __expf(-(pl_logit(miss) + p.calib[bh])));
+    const int a = p.age[bh] + 1;
     const bool tr = dec > p.delta || a >= p.max_age || (fl & 1);
     p.age[bh] = tr ? 0 : a;
     p.trig[bh] = tr ? 1 : 0;
