@@ -100,10 +100,12 @@ class CAbi:
         self._call("decode_noalloc", C.byref(p), D, Hq // Hkv, 2, int(block_idx is not None), 0, 1, _stream())
 
     def decode(self, q, k, v, scale, block_idx=None, block_cnt=None, stats=False, load_v=True, num_splits=1,
-               stages=2, want_f32=False, write_p=False):
-        """Same arguments and return list as the extension's decode()."""
+               stages=2, want_f32=False, write_p=False, t_dev=None, page_table=None, seq_len=None):
+        """Same arguments and return list as the extension's decode().  t_dev (int32 CUDA scalar):
+        kvskip_launch_decode_dyn; page_table (int32 [B, max_pages]) with seq_len:
+        kvskip_launch_decode_paged over page pools k, v [pages,Hkv,64,D]."""
         B, Hq, D = q.shape
-        Hkv, T = k.shape[1], k.shape[2]
+        Hkv, T = k.shape[1], (k.shape[2] if page_table is None else int(seq_len))
         nb = math.ceil(T / TILE)
         dev = q.device
         f32 = dict(dtype=torch.float32, device=dev)
@@ -125,8 +127,16 @@ class CAbi:
         p.out, p.out_f32, p.lse = _ptr(out), _ptr(o32), _ptr(lse)
         p.blk_max, p.blk_sum, p.nb = _ptr(bmax), _ptr(bsum), nb
         p.t_pad, p.p_out = nb * TILE, _ptr(pbuf)
-        self._call("decode", C.byref(p), D, Hq // Hkv, stages, int(block_idx is not None), int(stats), int(load_v),
-                   _stream())
+        p.T = T
+        flags = (C.byref(p), D, Hq // Hkv, stages, int(block_idx is not None), int(stats), int(load_v))
+        if page_table is not None:
+            assert page_table.dtype == torch.int32 and page_table.is_contiguous() and page_table.shape[0] == B
+            self._call("decode_paged", *flags, C.c_void_p(_ptr(page_table)), page_table.shape[1], k.shape[0],
+                       C.c_void_p(_ptr(t_dev)), _stream())
+        elif t_dev is not None:
+            self._call("decode_dyn", *flags, C.c_void_p(_ptr(t_dev)), _stream())
+        else:
+            self._call("decode", *flags, _stream())
         self._keep = (pacc, pml)   # scratch must outlive the asynchronous launch
         return [out, lse, bmax, bsum, o32, pbuf]
 
@@ -197,6 +207,18 @@ class CAbi:
         p.B, p.Hkv, p.NBC, p.Hq = keep.shape[0], keep.shape[1], keep.shape[2], lse_att.shape[1]
         p.T, p.local, p.level = T, local, level
         self._call("update", C.byref(p), _stream())
+
+    def append(self, k, v, k_new, v_new, T, t_dev=None, page_table=None):
+        """kvskip_launch_append: rows of the newest token into a contiguous cache or a page pool."""
+        B, Hkv, D = k_new.shape
+        pt = page_table
+        self._call("append", C.c_void_p(_ptr(k)), C.c_void_p(_ptr(v)), C.c_int64(k.stride(0)), C.c_int64(k.stride(1)),
+                   C.c_int64(k.stride(2)), C.c_void_p(_ptr(k_new)), C.c_void_p(_ptr(v_new)), B, Hkv, D, int(T),
+                   C.c_void_p(_ptr(t_dev)), C.c_void_p(_ptr(pt)), 0 if pt is None else pt.shape[1],
+                   0 if pt is None else k.shape[0], _stream())
+
+    def advance(self, t_dev, delta=1):
+        self._call("advance", C.c_void_p(_ptr(t_dev)), int(delta), _stream())
 
     def read_bw(self, x, out, blocks):
         self._call("read", C.c_void_p(x.data_ptr()), C.c_int64(x.numel() * x.element_size()),

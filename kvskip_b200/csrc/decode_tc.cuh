@@ -243,37 +243,11 @@ __device__ __forceinline__ void tc_fill_gap(const kvskip_params& p, const int32_
   }
 }
 
-// Length of the pieces the block lists of a launch are cut into, from the total number of listed
-// blocks `tot` of all `heads` (batch x kv head) lists and the number of CTAs the GPU runs at a
-// time (`slots`).  A piece costs its blocks plus a fixed part (set-up, first loads, merge) worth
-// about TC_PIECE_FIXED blocks, and the launch takes as long as its waves of `slots` CTAs: for
-// k = 1, 2, ... waves the shortest piece that is sure to fit (every list rounds up, hence the
-// `heads` CTAs of slack) is ceil(tot / (k slots - heads)); the k with the smallest k (L + fixed)
-// wins.  Every CTA evaluates this from the same counts, so all agree, on every run.
-constexpr int TC_PIECE_FIXED = 10;
-__device__ __forceinline__ int tc_piece_len(const int tot, const int heads, const int slots, const int len_min) {
-  int best_len = 24, best_cost = 0x7fffffff;
-  for (int k = 1; k <= 12; ++k) {
-    const int room = k * slots - heads;
-    if (room < slots / 2) continue;                      // more lists than CTAs: no slack to speak of
-    const int len = max(len_min, (tot + room - 1) / room);
-    const int cost = k * (len + TC_PIECE_FIXED);
-    if (cost < best_cost) {
-      best_cost = cost;
-      best_len = len;
-    }
-    if (len == len_min) break;                           // more waves cannot shorten the pieces further
-  }
-  return best_len;
-}
-
-// Grid (Hkv, B, splits): the split index is the slowest, so that the CTAs of the first pieces of
-// every list are dispatched before the surplus CTAs of any list.
 template <int NC, bool MASKED, bool STATS, bool LOAD_V>
 __global__ void __launch_bounds__((NC + 1) * 32, NC <= 3 ? 2 : 1)
 decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* __restrict__ split_done,
-                 const int piece_min, const int slots, const int* __restrict__ t_dev,
-                 const int32_t* __restrict__ pages, const int max_pages) {
+                 const int min_blocks, const int* __restrict__ t_dev, const int32_t* __restrict__ pages,
+                 const int max_pages) {
   using Cfg = TcCfg<NC, LOAD_V>;
   constexpr int G = 4, D = 128;
   constexpr int S = Cfg::kStages;
@@ -287,7 +261,7 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
   uint64_t* full = reinterpret_cast<uint64_t*>(sL + NC * 4);               // [S]
   uint64_t* empty = full + S;                                              // [S]
 
-  const int split = blockIdx.z, h = blockIdx.x, b = blockIdx.y;
+  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   if (tid == 0) {
@@ -318,18 +292,12 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
   }
   // Splits actually used for this (batch, kv head).  A block list can be much shorter than the
   // length the grid was sized for (a head that does not refresh reads a tenth of the blocks a
-  // refreshing one reads): with the merge inside the kernel the list is cut into pieces whose
-  // length follows from the lists of the whole launch (tc_piece_len) and the surplus CTAs leave at
-  // once, instead of every CTA paying its fixed cost for a handful of blocks.
+  // refreshing one reads): with the merge inside the kernel the list is cut into at most
+  // ceil(n_items / min_blocks) pieces and the surplus CTAs leave at once, instead of every CTA
+  // paying its fixed cost for a handful of blocks.
   int S_use = p.num_splits;
-  if (MASKED && LOAD_V && split_done != nullptr && piece_min > 0) {
-    const int heads = p.B * p.Hkv;
-    int tot = 0;
-    for (int i = lane; i < heads; i += 32) tot += p.block_cnt[i];
-    tot = __reduce_add_sync(0xffffffffu, tot);
-    const int len = tc_piece_len(tot, heads, slots, piece_min);
-    S_use = max(1, min(p.num_splits, (n_items + len - 1) / len));
-  }
+  if (MASKED && LOAD_V && split_done != nullptr && min_blocks > 1)
+    S_use = max(1, min(p.num_splits, (n_items + min_blocks - 1) / min_blocks));
   if (split >= S_use) return;
   const int per = (n_items + S_use - 1) / S_use;
   const int i0 = min(n_items, split * per);

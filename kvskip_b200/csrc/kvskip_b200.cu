@@ -194,13 +194,13 @@ struct DynArgs {
 };
 
 template <int NC, bool MASKED, bool STATS, bool LOAD_V>
-int launch_tc_nc(const kvskip_params& p, const kvb::TmaMaps& maps, int* done, int piece_min, int slots,
-                 const DynArgs& dyn, cudaStream_t stream) {
+int launch_tc_nc(const kvskip_params& p, const kvb::TmaMaps& maps, int* done, int min_blocks, const DynArgs& dyn,
+                 cudaStream_t stream) {
   using Cfg = kvb::TcCfg<NC, LOAD_V>;
   auto kernel = kvb::decode_tc_kernel<NC, MASKED, STATS, LOAD_V>;
   if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes)) return rc;
-  KVB_CUDA(launch_overlapped(kernel, dim3(p.Hkv, p.B, p.num_splits), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, p,
-                             maps, done, piece_min, slots, dyn.t_dev, dyn.pages, dyn.max_pages));
+  KVB_CUDA(launch_overlapped(kernel, dim3(p.num_splits, p.Hkv, p.B), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, p,
+                             maps, done, min_blocks, dyn.t_dev, dyn.pages, dyn.max_pages));
   return KVSKIP_OK;
 }
 
@@ -226,15 +226,15 @@ int launch_tc(const kvskip_params& p, const DynArgs& dyn, cudaStream_t stream) {
   int* done = nullptr;
   if (LOAD_V && p.num_splits > 1)
     if (int rc = split_done_region(p.B * p.Hkv, &done)) return rc;
-  // A dense launch of four or more waves uses the half-size CTA (two per SM), so that set-up and
-  // merge of one overlap the other's streaming; with a block list, where many CTAs leave at once
-  // and the rest differ in length, the full-size CTA measured faster.  Block lists are cut into
-  // pieces of at least 4 blocks, sized in the kernel from all lists of the launch.
+  // With more CTAs than SMs a short block list is cut into pieces of at least 24 blocks.  A dense
+  // launch of four or more waves uses the half-size CTA (two per SM), so that set-up and merge of
+  // one overlap the other's streaming; with a block list, where many CTAs leave at once and the
+  // rest differ in length, the full-size CTA measured faster.
   const bool multi_wave =
       !MASKED && total >= 4 * static_cast<int64_t>(sms) && g_half_cta.load(std::memory_order_relaxed);
-  const int piece_min = 4;
-  if (int rc = multi_wave ? launch_tc_nc<3, MASKED, STATS, LOAD_V>(p, maps, done, piece_min, 2 * sms, dyn, stream)
-                          : launch_tc_nc<6, MASKED, STATS, LOAD_V>(p, maps, done, piece_min, sms, dyn, stream))
+  const int min_blocks = (total > sms) ? 24 : 1;
+  if (int rc = multi_wave ? launch_tc_nc<3, MASKED, STATS, LOAD_V>(p, maps, done, min_blocks, dyn, stream)
+                          : launch_tc_nc<6, MASKED, STATS, LOAD_V>(p, maps, done, min_blocks, dyn, stream))
     return rc;
   if (LOAD_V && p.num_splits > 1 && done == nullptr) {
     kvb::merge_kernel<128><<<p.B * p.Hq, 128, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits,
@@ -354,7 +354,6 @@ int decode_impl(const kvskip_params* p, int D, int G, int stages, int masked, in
     if (p->p_out) return fail(KVSKIP_E_ARG, "paged cache: write_p is not supported");
   }
   if (stages != 2 && stages != 3) return fail(KVSKIP_E_ARG, "kvskip: unsupported head dim / stages");
-  if (p->num_splits > 65535 || p->B > 65535) return fail(KVSKIP_E_LIMIT, "num_splits and B are grid dims: at most 65535");
   if (!load_v && !stats) return fail(KVSKIP_E_ARG, "kvskip: unsupported flag combination (load_v=false needs stats=true)");
   if (masked && (!p->block_idx || !p->block_cnt)) return fail(KVSKIP_E_ARG, "masked mode needs block_idx and block_cnt");
   if (stats && (!p->blk_max || !p->blk_sum)) return fail(KVSKIP_E_ARG, "stats mode needs blk_max and blk_sum");

@@ -106,15 +106,13 @@ def make_plan(keep: torch.Tensor, sync: bool = True) -> Plan:
 
 def splits_for_unsynced_plan(bh: int, nb: int) -> int:
     """Split count for a block list whose true lengths are not known on the host (sized for nb).
-    The tensor-core kernel sizes the pieces itself from all lists of the launch and lets surplus
-    CTAs leave at once (they are dispatched last), so the count given here is only the most pieces
-    a single list may be cut into: enough for a head that reads every block to spread out in
-    pieces of 16 blocks (8 at batch 1), at most 64, while the grid stays within eight CTAs per SM
-    (a surplus CTA still costs its dispatch)."""
+    The tensor-core kernel cuts every list into pieces of >= 24 blocks and lets surplus CTAs leave
+    at once, so at small batch it pays to provision enough splits for a head that reads every block
+    to spread over many SMs; at larger batch the grid is several waves anyway."""
     base = num_splits_for(bh, nb)
-    sms = num_sms()
-    want = -(-nb // (8 if bh * 8 <= sms else 16))
-    return max(base, min(64, want, (8 * sms) // bh))
+    if bh * base <= 2 * num_sms():
+        return min(64, max(base, -(-nb // 24)))
+    return base
 
 
 def _q3(q):

@@ -157,3 +157,28 @@ def test_planner_loop_on_a_paged_cache_matches_contiguous(graph):
     gk, gv = pg.gather()
     assert torch.equal(gk, kc[:, :, :T0 + steps]) and torch.equal(gv, vc[:, :, :T0 + steps])
     assert K.ext().device_status() == 0
+
+
+def test_dyn_and_paged_entry_points_through_ctypes():
+    """The C ABI itself (no PyTorch binding in between): kvskip_launch_decode_dyn / _decode_paged /
+    _append / _advance give what the by-value launch gives."""
+    from kvskip_b200.cabi import CAbi
+    abi = CAbi()
+    cap, B, T = 1024, 2, 700
+    q, k, v, scale = synth.dense_case(77, B, cap)
+    q, k, v = q.to(DEV), k.to(DEV), v.to(DEV)
+    ref = abi.decode(q, k[:, :, :T], v[:, :, :T], scale, stats=True, num_splits=4, want_f32=True)
+    t_dev = torch.tensor([T - 1], dtype=torch.int32, device=DEV)
+    abi.advance(t_dev, 1)
+    dyn = abi.decode(q, k, v, scale, stats=True, num_splits=4, want_f32=True, t_dev=t_dev)
+    nb = math.ceil(T / 64)
+    assert torch.equal(ref[4], dyn[4]) and torch.equal(ref[1], dyn[1]) and torch.equal(ref[2], dyn[2][..., :nb])
+    pg = _paged_from(k, v, T - 1, cap, seed=5)
+    pg.reserve(T)
+    abi.append(pg.k, pg.v, k[:, :, T - 1].contiguous(), v[:, :, T - 1].contiguous(), cap, t_dev=t_dev, page_table=pg.table)
+    paged = abi.decode(q, pg.k, pg.v, scale, stats=True, num_splits=4, want_f32=True, page_table=pg.table, seq_len=T)
+    assert torch.equal(ref[4], paged[4]) and torch.equal(ref[1], paged[1]) and torch.equal(ref[2], paged[2])
+    kc, vc = k.clone(), v.clone()
+    kc[:, :, T - 1] = 0
+    abi.append(kc, vc, k[:, :, T - 1].contiguous(), v[:, :, T - 1].contiguous(), T)
+    assert torch.equal(kc, k) and torch.equal(vc, v)
