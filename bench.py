@@ -608,10 +608,20 @@ def main():
     vn_d = stage_d[nq + nkv:].view(B, HKV, D)
     out_h = torch.empty(B, HQ, D, dtype=torch.bfloat16).pin_memory()
 
-    def e2e_step():
+    # the step as a user of the library would run it in a decode loop: host-to-device copy, append,
+    # attention and the copy back captured once (kvskip_b200.graph.StepGraph) and replayed, with
+    # a host synchronisation after every step because the next token depends on this output
+    from kvskip_b200.graph import StepGraph
+
+    def e2e_launch():
         stage_d.copy_(stage_h, non_blocking=True)
         K.ext().append(k, v, kn_d, vn_d, T)
         out_h.copy_(K.decode(q_d, k, v, scale)["out"], non_blocking=True)
+
+    e2e_graph = StepGraph(e2e_launch, eager=2)
+
+    def e2e_step():
+        e2e_graph.step()
         torch.cuda.synchronize()
     for _ in range(3):
         e2e_step()
@@ -680,7 +690,7 @@ def main():
             "cpu_baseline": cpu,
             "e2e": {"value": world * nbytes * args.steps / (ms2 * 1e-3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "note": "q and the new token's K/V rows from pinned host memory, output back to pinned host "
+                    "note": "one CUDA-graph replay per step: q and the new token's K/V rows from pinned host memory, append, attention, output back to pinned host "
                             "memory, host sync every step; the KV cache is resident state"},
             "gpu_launches": args.steps,   # one decode kernel per step; the split merge runs inside it
             "clocks": clocks,

@@ -70,7 +70,9 @@ class StepGraph:
         sig = self._scalars()
         if self.graph is None or sig != self.signature:
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            # thread-local capture mode: CUDA calls of other threads (e.g. a communication
+            # library's watchdog) do not invalidate the capture
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                 result = self.launch()          # recorded, not run; advances the layers' counters
             self.graph, self.result, self.signature = graph, result, sig
             self.captures += 1

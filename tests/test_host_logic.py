@@ -66,7 +66,7 @@ def test_step_graph_runs_eager_steps_before_capturing(monkeypatch):
             calls.append("replay")
 
     class FakeCapture:
-        def __init__(self, g):
+        def __init__(self, g, **kw):
             pass
 
         def __enter__(self):
