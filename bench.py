@@ -229,6 +229,12 @@ def _attention_cases(dev, K, synth, g, add, flush):
     add("vskip1 (previous-step normaliser, tau 1e-4) B=1 T=65536",
         time_cuda(lambda: K.vskip_one_pass(q, k, v, scale, tau=1e-4, lse_prev=lse), 30, flush),
         kv_bytes(1, T_HEAD, 0.5 * (1 + vk)), v_kept=round(vk, 4), bytes="all K + V of voted blocks")
+    two = K.vskip_two_pass(q, k, v, scale, "topp", 0.99)
+    kept2 = float(two["kept_frac"])
+    add("vskip two-pass (statistics + P pass over K, then P.V over the selected blocks, top-p 0.99) B=1 T=65536",
+        time_cuda(lambda: K.vskip_two_pass(q, k, v, scale, "topp", 0.99, sync=False), 30, flush),
+        kv_bytes(1, T_HEAD, 0.5 * (1 + kept2)), v_kept=round(kept2, 4),
+        bytes="all K + V of the selected blocks (P written and re-read in fp16 not counted)")
     del q, k, v
 
 

@@ -20,6 +20,7 @@
 #include "planner.cuh"
 #include "vskip.cuh"
 #include "vskip_tc.cuh"
+#include "pv_tc.cuh"
 
 namespace {
 
@@ -311,6 +312,25 @@ int launch_vskip1_tc(const kvskip_params& p, cudaStream_t stream) {
   return KVSKIP_OK;
 }
 
+int launch_pv_tc(const kvskip_params& p, cudaStream_t stream) {
+  auto kernel = kvb::pv_tc_kernel;
+  if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), kvb::PvTcCfg::kSmemBytes)) return rc;
+  kvb::TmaMaps maps;
+  if (int rc = make_kv_map(&maps.v, p.v, p.v_sb, p.v_sh, p.v_st, p.B, p.Hkv, p.T, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  maps.k = maps.v;
+  int* done = nullptr;
+  if (p.num_splits > 1)
+    if (int rc = split_done_region(p.B * p.Hkv, &done)) return rc;
+  KVB_CUDA(launch_overlapped(kernel, dim3(p.num_splits, p.Hkv, p.B), dim3(kvb::TC_THREADS), kvb::PvTcCfg::kSmemBytes,
+                             stream, p, maps, done));
+  if (p.num_splits > 1 && done == nullptr) {
+    kvb::sum_splits_kernel<128><<<p.B * p.Hq, 128, 0, stream>>>(p);
+    KVB_CUDA(cudaGetLastError());
+  }
+  return KVSKIP_OK;
+}
+
 template <int D>
 int launch_pv_t(const kvskip_params& p, cudaStream_t stream) {
   using Cfg = kvb::PvCfg<D>;
@@ -488,6 +508,7 @@ int kvskip_launch_pv(const kvskip_params* p, int D, int G, void* stream) {
     return fail(KVSKIP_E_ARG, "pv needs p_in, blk_scale, block_idx, block_cnt, out");
   if (p->num_splits > 1 && !p->part_acc) return fail(KVSKIP_E_ARG, "num_splits > 1 needs part_acc scratch");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (D == 128 && g_decode_path.load(std::memory_order_relaxed) != 1) return launch_pv_tc(*p, s);
   return D == 128 ? launch_pv_t<128>(*p, s) : launch_pv_t<64>(*p, s);
 }
 

@@ -398,9 +398,25 @@ __global__ void __launch_bounds__(PL_THREADS) update_kernel(const kvskip_update_
     else lo = pl_bisect_smem(x, ey, nb, lane, lse, p.level);
     for (int i = lane; i < nb; i += 32)
       if (x[i] - lse >= lo) skeep[i] = 1;
-    for (int i = lane; i < p.NBC; i += 32) {
-      p.lse_ref[hrow * p.NBC + i] = i < nb ? x[i] : -INFINITY;
-      p.cs_ref[hrow * p.NBC + i] = i < nb ? p.cs_now[hrow * p.NBC + i] : 0.f;
+    // new references: the centroid scores are fetched eight at a time before anything is stored
+    // (the compiler may not move a load above a store through another pointer of the same type,
+    // so a load-store loop would pay one memory round trip per iteration)
+    constexpr int RU = 8;
+    for (int base = lane; base < p.NBC; base += 32 * RU) {
+      float c[RU];
+#pragma unroll
+      for (int j = 0; j < RU; ++j) {
+        const int i = base + 32 * j;
+        c[j] = i < nb ? p.cs_now[hrow * p.NBC + i] : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < RU; ++j) {
+        const int i = base + 32 * j;
+        if (i < p.NBC) {
+          p.lse_ref[hrow * p.NBC + i] = i < nb ? x[i] : -INFINITY;
+          p.cs_ref[hrow * p.NBC + i] = c[j];
+        }
+      }
     }
   }
   __syncthreads();
