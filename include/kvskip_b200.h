@@ -226,6 +226,18 @@ int kvskip_launch_index_blocks_dyn(const int64_t* ids, int64_t ids_stride, int n
                                    uint8_t* out, int NBC, void* stream);
 int kvskip_launch_advance(int* t_dev, int delta, void* stream);
 
+/* Block selection between the two passes of the two-pass V-skip, in one launch (the reference's
+ * caller does it with torch ops: kernels/kvskip.py:122-147 select_blocks, :165-177, :70-85
+ * make_plan).  blk_max, blk_sum fp32 [B,4*Hkv,nb] from the statistics pass; rule 0: per query head
+ * the heaviest blocks whose softmax mass reaches `value` (top-p), rule 1: blocks of weight >=
+ * `value`; a kv head keeps the union over its four heads plus block 0 and the `local` newest.
+ * Outputs: keep u8 [B,Hkv,nb], block_idx int32 [B,Hkv,nb] (ascending) with block_cnt [B,Hkv], and
+ * weight fp32 [B,Hkv,nb,4] = exp(blk_max - log-sum-exp of the kept blocks), 0 where not kept: the
+ * blk_scale of kvskip_launch_pv. */
+int kvskip_launch_select(const float* blk_max, const float* blk_sum, int B, int Hkv, int nb, int rule, float value,
+                         int local, uint8_t* keep, int32_t* block_idx, int32_t* block_cnt, float* weight,
+                         void* stream);
+
 /* Paged cache (no counterpart in the reference, which reads [B,Hkv,T,D] views; its notes name a
  * cache in which a 64-token block is a page as the natural layout next to the block lists).
  * k and v of the parameter block are page pools [num_pages, Hkv, 64, D] (k_sb = page stride, k_sh,

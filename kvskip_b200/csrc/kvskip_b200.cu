@@ -700,6 +700,23 @@ int kvskip_launch_append(uint16_t* k, uint16_t* v, int64_t sb, int64_t sh, int64
   return KVSKIP_OK;
 }
 
+int kvskip_launch_select(const float* blk_max, const float* blk_sum, int B, int Hkv, int nb, int rule, float value,
+                         int local, uint8_t* keep, int32_t* block_idx, int32_t* block_cnt, float* weight,
+                         void* stream) {
+  if (!blk_max || !blk_sum || !keep || !block_idx || !block_cnt || !weight || B < 1 || Hkv < 1 || nb < 1)
+    return fail(KVSKIP_E_ARG, "select: bad arguments");
+  if (rule != 0 && rule != 1) return fail(KVSKIP_E_ARG, "select: rule 0 (top-p) or 1 (tau)");
+  if (B > 65535) return fail(KVSKIP_E_LIMIT, "B is a grid dim: at most 65535");
+  const int smem = 2 * kvb::PL_G * nb * static_cast<int>(sizeof(float)) + nb;
+  if (smem > 220 * 1024) return fail(KVSKIP_E_LIMIT, "select: more than %d blocks", 220 * 1024 / 33);
+  if (smem > 48 * 1024)
+    if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::select_kernel), 220 * 1024)) return rc;
+  KVB_CUDA(launch_overlapped(kvb::select_kernel, dim3(Hkv, B), dim3(kvb::PL_THREADS), smem,
+                             static_cast<cudaStream_t>(stream), blk_max, blk_sum, nb, Hkv, rule, value, local, keep,
+                             block_idx, block_cnt, weight));
+  return KVSKIP_OK;
+}
+
 int kvskip_launch_advance(int* t_dev, int delta, void* stream) {
   if (!t_dev) return fail(KVSKIP_E_ARG, "t_dev is null");
   kvb::advance_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(t_dev, delta);

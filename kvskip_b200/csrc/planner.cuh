@@ -462,6 +462,75 @@ __global__ void __launch_bounds__(256) index_blocks_kernel(const int64_t* __rest
   }
 }
 
+// Block selection between the two passes of the two-pass V-skip, on the device: what the
+// reference's caller does with a dozen torch launches (format37/kvskip kernels/kvskip.py:122-147
+// select_blocks, :165-177 the weights of vskip_two_pass, :70-85 make_plan).  Grid (Hkv, B), a warp
+// per query head.  Per head: block log-weights x = blk_max + log blk_sum, their log-sum-exp, and
+//   rule 0 ("topp")  the fewest heaviest blocks whose mass reaches `value`: the same bisection as
+//                    update_kernel's top-p cut (kept set {x - lse >= lo});
+//   rule 1 ("tau")   blocks whose weight exp(x - lse) is at least `value`.
+// The kv head keeps the union over its four heads plus block 0 and the `local` newest.  Outputs:
+// keep u8 [B,Hkv,nb], the ascending block list and its length, and for the second pass the
+// weights exp(blk_max - lse_kept) [B,Hkv,nb,4] (0 on blocks not kept), lse_kept = log-sum-exp of
+// x over the kept set.
+__global__ void __launch_bounds__(PL_THREADS) select_kernel(const float* __restrict__ blk_max,
+                                                            const float* __restrict__ blk_sum, const int nb,
+                                                            const int Hkv, const int rule, const float value,
+                                                            const int local, uint8_t* __restrict__ keep,
+                                                            int32_t* __restrict__ block_idx,
+                                                            int32_t* __restrict__ block_cnt,
+                                                            float* __restrict__ weight) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t bh = static_cast<int64_t>(b) * Hkv + h;
+  const int64_t hrow = bh * PL_G + warp;
+  extern __shared__ float sel_smem[];
+  float* x = sel_smem + warp * nb;
+  float* ey = sel_smem + (PL_G + warp) * nb;
+  uint8_t* skeep = reinterpret_cast<uint8_t*>(sel_smem + 2 * PL_G * nb);
+  __shared__ int scan[PL_THREADS];
+  pdl_wait_prior();          // the statistics come from the kernel before this one
+  pdl_launch_dependents();
+
+  float mx = -INFINITY;
+#pragma unroll 8
+  for (int i = lane; i < nb; i += 32) {
+    const float val = blk_max[hrow * nb + i] + __logf(blk_sum[hrow * nb + i]);
+    x[i] = val;
+    mx = fmaxf(mx, val);
+  }
+  for (int i = tid; i < nb; i += PL_THREADS) skeep[i] = pl_always(i, nb, local) ? 1 : 0;
+  mx = warp_max(mx);
+  __syncthreads();
+  float se = 0.f;
+  for (int i = lane; i < nb; i += 32) se += __expf(x[i] - mx);
+  const float lse = mx + __logf(warp_sum(se));
+  float lo;
+  if (rule == 0) {
+    if (nb <= 8 * 32) lo = pl_bisect_regs<8>(x, nb, lane, lse, value);
+    else if (nb <= 16 * 32) lo = pl_bisect_regs<16>(x, nb, lane, lse, value);
+    else if (nb <= 32 * 32) lo = pl_bisect_regs<32>(x, nb, lane, lse, value);
+    else if (nb <= 64 * 32) lo = pl_bisect_regs<64>(x, nb, lane, lse, value);
+    else lo = pl_bisect_smem(x, ey, nb, lane, lse, value);
+  } else {
+    lo = __logf(value);
+  }
+  for (int i = lane; i < nb; i += 32)
+    if (rule == 0 ? (x[i] - lse >= lo) : (__expf(x[i] - lse) >= value)) skeep[i] = 1;
+  __syncthreads();
+  // weights of the second pass, relative to the mass of the kept set
+  float m2 = -INFINITY, s2 = 0.f;
+  for (int i = lane; i < nb; i += 32)
+    if (skeep[i]) pl_fold(m2, s2, x[i]);
+  const float M = warp_max(m2);
+  const float S = warp_sum(s2 > 0.f ? s2 * __expf(m2 - M) : 0.f);
+  const float lse_kept = M + __logf(S);
+  for (int i = lane; i < nb; i += 32)
+    weight[(bh * nb + i) * PL_G + warp] = skeep[i] ? __expf(blk_max[hrow * nb + i] - lse_kept) : 0.f;
+  for (int i = tid; i < nb; i += PL_THREADS) keep[bh * nb + i] = skeep[i];
+  pl_compact(nb, block_idx + bh * nb, block_cnt + bh, scan, [&](int i) { return skeep[i] != 0; });
+}
+
 // The new token's K and V rows into the cache: grid (Hkv, B) x D/8 threads, 16 bytes per thread
 // and tensor.  T (or *t_dev) is the length after the append, so the row is T-1; with a page table
 // it is row (T-1) % 64 of page pages[b, (T-1) / 64].

@@ -530,6 +530,25 @@ void append(at::Tensor& k, at::Tensor& v, const at::Tensor& k_new, const at::Ten
                                 tdev_ptr(t_dev), pg.table, pg.max_pages, pg.num_pages, cur_stream()));
 }
 
+// Block selection of the two-pass V-skip on the device: [keep u8 [B,Hkv,nb], block_idx, block_cnt, weight [B,Hkv,nb,4]]
+std::vector<at::Tensor> select_dev(const at::Tensor& blk_max, const at::Tensor& blk_sum, int64_t rule, double value,
+                               int64_t local) {
+  need_f32(blk_max, "blk_max"); need_f32(blk_sum, "blk_sum");
+  TORCH_CHECK(blk_max.dim() == 3 && blk_max.sizes() == blk_sum.sizes() && blk_max.size(1) % 4 == 0,
+              "blk_max, blk_sum: fp32 [B, 4*Hkv, nb]");
+  const int64_t B = blk_max.size(0), Hkv = blk_max.size(1) / 4, nb = blk_max.size(2);
+  const c10::cuda::CUDAGuard guard(blk_max.device());
+  at::Tensor keep = at::empty({B, Hkv, nb}, blk_max.options().dtype(at::kByte));
+  at::Tensor bi = at::empty({B, Hkv, nb}, blk_max.options().dtype(at::kInt));
+  at::Tensor bc = at::empty({B, Hkv}, blk_max.options().dtype(at::kInt));
+  at::Tensor w = at::empty({B, Hkv, nb, 4}, blk_max.options());
+  raise_on(kvskip_launch_select(blk_max.data_ptr<float>(), blk_sum.data_ptr<float>(), static_cast<int>(B),
+                                static_cast<int>(Hkv), static_cast<int>(nb), static_cast<int>(rule),
+                                static_cast<float>(value), static_cast<int>(local), keep.data_ptr<uint8_t>(),
+                                bi.data_ptr<int32_t>(), bc.data_ptr<int32_t>(), w.data_ptr<float>(), cur_stream()));
+  return {keep, bi, bc, w};
+}
+
 // *t_dev += delta in stream order
 void advance(at::Tensor& t_dev, int64_t delta) {
   TORCH_CHECK(t_dev.is_cuda() && t_dev.scalar_type() == at::kInt && t_dev.numel() == 1,
@@ -601,6 +620,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("append", &append, "the newest token's K and V rows into the cache (contiguous or paged)", py::arg("k"),
         py::arg("v"), py::arg("k_new"), py::arg("v_new"), py::arg("T"), py::arg("t_dev") = py::none(),
         py::arg("page_table") = py::none());
+  m.def("select", &select_dev, "two-pass V-skip: block selection, list and second-pass weights in one launch",
+        py::arg("blk_max"), py::arg("blk_sum"), py::arg("rule"), py::arg("value"), py::arg("local") = 2);
   m.def("advance", &advance, "device-resident sequence length += delta, in stream order", py::arg("t_dev"),
         py::arg("delta") = 1);
   m.def("set_option", &set_option, "process-wide option, e.g. (\"decode_path\", 1) for the exact-order kernels",

@@ -197,14 +197,28 @@ def pv(P, v, blk_scale, plan: Plan, num_splits: int | None = None, out_f32: bool
 
 
 def vskip_two_pass(q, k, v, scale: float, rule: str = "topp", value: float = 0.99, local: int = 2,
-                   sync: bool = True, out_f32: bool = False) -> dict:
+                   sync: bool = True, out_f32: bool = False, device_select: bool = True) -> dict:
     """Two-pass V-skip: a statistics pass over all of K that also writes P = exp(s - block max) in
-    fp16, block selection per GQA union, then a pass over P and V of the selected blocks."""
+    fp16, block selection per GQA union, then a pass over P and V of the selected blocks.
+    device_select (not in the reference): the selection between the passes runs as one kernel;
+    False gives the reference's torch formulation (sort + cumulative sum)."""
     q = _q3(q)
     B, Hq, _ = q.shape
     Hkv = k.shape[1]
     G = Hq // Hkv
     first = decode(q, k, v, scale, stats=True, load_v=False, write_p=True)
+    if device_select and G == 4 and rule in ("topp", "tau"):
+        # selection, block list and second-pass weights in one launch instead of a dozen torch ops
+        keep8, bi, bc, weight = ext().select(first["blk_max"], first["blk_sum"], 0 if rule == "topp" else 1,
+                                             float(value), int(local))
+        nb = keep8.shape[-1]
+        plan = Plan(bi, bc, int(bc.max()) if sync else nb, nb)
+        out, o32 = pv(first["p"], v, weight, plan, out_f32=out_f32)
+        keep = keep8.bool()
+        res = {"out": out, "keep": keep, "kept_frac": keep.float().mean().item() if sync else None}
+        if out_f32:
+            res["out_f32"] = o32
+        return res
     logw = first["blk_max"] + torch.log(first["blk_sum"])
     keep = select_blocks(logw, G, rule, value, local)
     keep_q = keep.repeat_interleave(G, dim=1)

@@ -516,3 +516,28 @@ def test_exchange_merge_two_gpus_matches_all_gather():
     assert ret["ok0"] and ret["ok1"], dict(ret)
     assert ret["status0"] == 0 and ret["status1"] == 0
     assert ret["err"] < TOL_F32
+
+
+@pytest.mark.parametrize("rule,value", [("topp", 0.99), ("topp", 0.9), ("tau", 1e-4), ("tau", 1e-3)])
+def test_device_selection_matches_torch_selection(rule, value):
+    """The one-launch selection between the two passes against the reference's torch formulation
+    (sort + cumulative sum, kernels/kvskip.py:122-147): same kept blocks except where a block sits
+    on the threshold within float rounding, same list, weights to float accuracy."""
+    q, k, v, scale, _ = synth.body_union_case(3, 8192 + 40)
+    q, k, v = cuda(q, k, v)
+    first = K.decode(q, k, v, scale, stats=True, load_v=False)
+    logw = first["blk_max"] + torch.log(first["blk_sum"])
+    keep_t = K.select_blocks(logw, 4, rule, value, 2)
+    keep8, bi, bc, w = K.ext().select(first["blk_max"], first["blk_sum"], 0 if rule == "topp" else 1, value, 2)
+    keep_d = keep8.bool()
+    assert (keep_d != keep_t).float().mean() < 2e-3
+    assert 0.05 < keep_d.float().mean() < 0.999
+    plan = K.make_plan(keep_d)
+    assert torch.equal(bc, plan.block_cnt)
+    n = int(bc.max())
+    valid = torch.arange(n, device=bi.device)[None, None, :] < bc[..., None]
+    assert torch.equal(torch.where(valid, bi[..., :n], 0), torch.where(valid, plan.block_idx[..., :n], 0))
+    kq = keep_d.repeat_interleave(4, dim=1)
+    lk = logw.masked_fill(~kq, float("-inf")).logsumexp(-1, keepdim=True)
+    w_t = torch.exp(first["blk_max"] - lk).masked_fill(~kq, 0.0).view(*keep_d.shape[:2], 4, -1).transpose(2, 3)
+    assert torch.allclose(w, w_t, rtol=2e-5, atol=1e-12)
