@@ -1,6 +1,6 @@
 """Generates the golden vectors under tests/golden/ by running the REFERENCE's own Python code on CPU.
 
-Needs a checkout of format37/kvskip (default /root/reference, or KVSKIP_REFERENCE); it is only
+Needs a checkout of format37/kvskip (its location in KVSKIP_REFERENCE); it is only
 run by a developer when the fixtures have to be regenerated, never by the tests:
 
     python tests/golden/make_golden.py
