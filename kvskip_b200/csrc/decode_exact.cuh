@@ -410,7 +410,9 @@ __global__ void __launch_bounds__(D) exchange_merge_kernel(const float* __restri
     const volatile unsigned int* f = peers.flags[rank] + static_cast<int64_t>(d) * N + row;
     bool got = false;
     for (uint32_t it = 0; it < (1u << 21); ++it) {
-      if (*f == seq) { got = true; break; }
+      // ">= seq" in wrap-safe form: a peer that has already gone on to its next step has
+      // overwritten this flag with the next value, which still says that step `seq` arrived
+      if (static_cast<int>(*f - seq) >= 0) { got = true; break; }
       __nanosleep(100);
     }
     if (!got) {
