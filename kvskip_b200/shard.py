@@ -109,6 +109,10 @@ class PeerExchange:
     all-gather path bit for bit.  All ranks must call it once per step, in the same order."""
 
     def __init__(self, n_rows: int, D: int, group=None, device=None):
+        import os
+        # plain peer stores only: no NVLink multicast object is bound to the buffer (a rank that
+        # dies while its memory is bound to one can fault its peers' GPUs)
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
         group = group or dist.group.WORLD
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
