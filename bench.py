@@ -427,6 +427,27 @@ def multi_gpu_cases(dev, rank, world, peak):
                               "kernel over peer memory", "us": round(us2, 2), "GBps": round(gbs2, 1),
                       "frac_of_peak": round(gbs2 / (peak * world), 4), "scaling": "strong",
                       "bit_identical_to_all_gather_path": same, "status_word": int(K.ext().device_status())})
+        # and with that exchange inside the attention kernel's split merge: the whole step is one launch
+        fn3 = lambda: shard.decode_sequence_sharded(q, k, v, D ** -0.5, exchange=xchg, fused=True)  # noqa: E731
+        c3 = fn3()
+        same3 = bool(torch.equal(a["out_f32"], c3["out_f32"]) and torch.equal(a["lse"], c3["lse"]))
+        for _ in range(5):
+            fn3()
+        dist.barrier()
+        torch.cuda.synchronize()
+        s.record()
+        for _ in range(iters):
+            fn3()
+        e.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([s.elapsed_time(e) * 1e3 / iters], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us3 = float(t)
+        gbs3 = kv_bytes(1, T) / (us3 * 1e-6) / 1e9
+        cases.append({"case": f"sequence-sharded dense B=1 T={T} over {world} GPUs, attention + exchange + merge in one "
+                              "kernel (peer stores from the split merge)", "us": round(us3, 2), "GBps": round(gbs3, 1),
+                      "frac_of_peak": round(gbs3 / (peak * world), 4), "scaling": "strong",
+                      "bit_identical_to_all_gather_path": same3, "status_word": int(K.ext().device_status())})
     except Exception as ex:  # noqa: BLE001
         cases.append({"case": "sequence-sharded, fused peer exchange", "error": str(ex)[:200]})
     del k, v

@@ -202,6 +202,17 @@ int kvskip_launch_exchange_merge(const float* out_f32, const float* lse, float* 
                                  unsigned int* const* peer_flags, int rank, int R, int64_t N, int D, unsigned int seq,
                                  uint16_t* out, float* res_f32, float* res_lse, void* stream);
 
+/* Sequence shards, everything in one kernel: kvskip_launch_decode whose split merge also does the
+ * exchange of kvskip_launch_exchange_merge -- the CTA that merges the splits of a (batch, kv head)
+ * stores the result as a packed triple into every rank's buffer (plain peer stores), flags its
+ * rows, waits (bounded, status word 0x510 + peer) for the peers' flags and merges the R triples in
+ * ascending rank order; p->out / out_f32 / lse receive the result over the whole sequence.  Same
+ * buffers, flags, seq convention and bits as kvskip_launch_exchange_merge (N = B * Hq rows).
+ * Needs num_splits > 1, D = 128 and at most half as many (batch, kv head) pairs as SMs. */
+int kvskip_launch_decode_xchg(const kvskip_params* p, int D, int G, int stages, int masked, int stats,
+                              float* const* peer_bufs, unsigned int* const* peer_flags, int rank, int R,
+                              unsigned int seq, void* stream);
+
 /* Token-index blocks of one decode step on the device (the reference builds them with torch ops,
  * src/lab.py:149-167): ids int64 [n, ids_stride], current token at T-1; out uint8 [n, NBC], a
  * block is marked if it holds an earlier copy of the current token or the position after one. */

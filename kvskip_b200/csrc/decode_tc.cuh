@@ -243,11 +243,25 @@ __device__ __forceinline__ void tc_fill_gap(const kvskip_params& p, const int32_
   }
 }
 
+// Sequence shards: the cross-GPU exchange inside the attention kernel.  With R > 0 the CTA that
+// merges the splits of a (batch, kv head) does not write the result but stores it, as the packed
+// triple (acc = out, m = lse / ln 2, l = 1) of exchange_merge_kernel, into every rank's buffer
+// over NVLink (plain peer stores), flags its four rows, waits -- bounded -- for the peers' flags
+// on its own rank's array and merges the R triples in ascending rank order.  Same buffers, slots,
+// flags and arithmetic as exchange_merge_kernel, so the two give the same bits.
+struct XchgArgs {
+  XchgPeers peers;
+  int rank;
+  int R;                 // 0: no exchange
+  long long N;           // rows of the exchange (B * Hq)
+  unsigned int seq;
+};
+
 template <int NC, bool MASKED, bool STATS, bool LOAD_V>
 __global__ void __launch_bounds__((NC + 1) * 32, NC <= 3 ? 2 : 1)
 decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* __restrict__ split_done,
                  const int min_blocks, const int* __restrict__ t_dev, const int32_t* __restrict__ pages,
-                 const int max_pages) {
+                 const int max_pages, const XchgArgs xa) {
   using Cfg = TcCfg<NC, LOAD_V>;
   constexpr int G = 4, D = 128;
   constexpr int S = Cfg::kStages;
@@ -462,6 +476,8 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
       if (s_last) {
         __threadfence();
         const int S2 = S_use;             // partials used; their stride stays p.num_splits
+        constexpr int XW = D + 2;
+        const bool xchg = xa.R > 0;
         for (int o = tid; o < G * D; o += TC_THREADS) {
           const int g = o / D, d = o % D;
           const int64_t hq = static_cast<int64_t>(b) * p.Hq + h * G + g;
@@ -476,9 +492,63 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
             a += __ldcg(p.part_acc + (hq * p.num_splits + s2) * D + d) * w;
           }
           const float o32 = l > 0.f ? a / l : 0.f;
-          reinterpret_cast<__nv_bfloat16*>(p.out)[hq * D + d] = __float2bfloat16(o32);
-          if (p.out_f32) p.out_f32[hq * D + d] = o32;
-          if (d == 0 && p.lse) p.lse[hq] = l > 0.f ? (m + log2f(l)) * LN2 : -INFINITY;
+          const float lse_nat = l > 0.f ? (m + log2f(l)) * LN2 : -INFINITY;
+          if (!xchg) {
+            reinterpret_cast<__nv_bfloat16*>(p.out)[hq * D + d] = __float2bfloat16(o32);
+            if (p.out_f32) p.out_f32[hq * D + d] = o32;
+            if (d == 0 && p.lse) p.lse[hq] = lse_nat;
+          } else {
+            const int64_t slot = ((static_cast<int64_t>(xa.seq & 1u) * xa.R + xa.rank) * xa.N + hq) * XW;
+            for (int r = 0; r < xa.R; ++r) {
+              float* dst = xa.peers.buf[r] + slot;
+              dst[d] = o32;
+              if (d == 0) {
+                dst[D] = lse_nat == -INFINITY ? -INFINITY : lse_nat * LOG2E;
+                dst[D + 1] = lse_nat == -INFINITY ? 0.f : 1.f;
+              }
+            }
+          }
+        }
+        if (xchg) {
+          const int64_t hq0x = static_cast<int64_t>(b) * p.Hq + h * G;
+          __threadfence_system();       // the rows are visible on every GPU before their flags
+          __syncthreads();
+          if (tid < G * xa.R) {
+            const int g = tid / xa.R, r = tid % xa.R;
+            volatile unsigned int* f = xa.peers.flags[r] + static_cast<int64_t>(xa.rank) * xa.N + hq0x + g;
+            *f = xa.seq;
+          }
+          if (tid < G * xa.R) {         // this rank's copy of the flags of its four rows, one per peer
+            const int g = tid / xa.R, r = tid % xa.R;
+            const volatile unsigned int* f = xa.peers.flags[xa.rank] + static_cast<int64_t>(r) * xa.N + hq0x + g;
+            bool got = false;
+            for (uint32_t it = 0; it < (1u << 21); ++it) {
+              if (static_cast<int>(*f - xa.seq) >= 0) { got = true; break; }
+              __nanosleep(100);
+            }
+            if (!got) atomicCAS(&g_status, 0u, 0x510u + r);
+          }
+          __threadfence_system();
+          __syncthreads();
+          const float* mine = xa.peers.buf[xa.rank] + (static_cast<int64_t>(xa.seq & 1u) * xa.R) * xa.N * XW;
+          for (int o = tid; o < G * D; o += TC_THREADS) {
+            const int g = o / D, d = o % D;
+            const int64_t row = hq0x + g;
+            float m = -INFINITY;
+            for (int r = 0; r < xa.R; ++r) m = fmaxf(m, __ldcg(mine + (static_cast<int64_t>(r) * xa.N + row) * XW + D));
+            const float mu = (m == -INFINITY) ? 0.f : m;
+            float l = 0.f, acc2 = 0.f;
+            for (int r = 0; r < xa.R; ++r) {
+              const float* pr = mine + (static_cast<int64_t>(r) * xa.N + row) * XW;
+              const float w = ex2(__ldcg(pr + D) - mu);
+              l += __ldcg(pr + D + 1) * w;
+              acc2 += __ldcg(pr + d) * w;
+            }
+            const float o32 = l > 0.f ? acc2 / l : 0.f;
+            reinterpret_cast<__nv_bfloat16*>(p.out)[row * D + d] = __float2bfloat16(o32);
+            if (p.out_f32) p.out_f32[row * D + d] = o32;
+            if (d == 0 && p.lse) p.lse[row] = l > 0.f ? (m + log2f(l)) * LN2 : -INFINITY;
+          }
         }
         if (tid == 0) split_done[b * p.Hkv + h] = 0;
       }

@@ -192,6 +192,7 @@ struct DynArgs {
   const int32_t* pages = nullptr;   // [B, max_pages] page of every 64-token block
   int max_pages = 0;
   int num_pages = 0;                // pages in the pool
+  kvb::XchgArgs xa{};               // R > 0: cross-GPU exchange inside the kernel (sequence shards)
 };
 
 template <int NC, bool MASKED, bool STATS, bool LOAD_V>
@@ -201,7 +202,7 @@ int launch_tc_nc(const kvskip_params& p, const kvb::TmaMaps& maps, int* done, in
   auto kernel = kvb::decode_tc_kernel<NC, MASKED, STATS, LOAD_V>;
   if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes)) return rc;
   KVB_CUDA(launch_overlapped(kernel, dim3(p.num_splits, p.Hkv, p.B), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, p,
-                             maps, done, min_blocks, dyn.t_dev, dyn.pages, dyn.max_pages));
+                             maps, done, min_blocks, dyn.t_dev, dyn.pages, dyn.max_pages, dyn.xa));
   return KVSKIP_OK;
 }
 
@@ -227,6 +228,10 @@ int launch_tc(const kvskip_params& p, const DynArgs& dyn, cudaStream_t stream) {
   int* done = nullptr;
   if (LOAD_V && p.num_splits > 1)
     if (int rc = split_done_region(p.B * p.Hkv, &done)) return rc;
+  if (dyn.xa.R > 0 && (!LOAD_V || done == nullptr || 2 * p.B * p.Hkv > sms))
+    return fail(KVSKIP_E_ARG,
+                "exchange inside the kernel: needs V, num_splits > 1 and at most half as many (batch, kv head) "
+                "pairs as SMs (the CTAs that wait for their peers must leave room for the others)");
   // With more CTAs than SMs a short block list is cut into pieces of at least 24 blocks.  A dense
   // launch of four or more waves uses the half-size CTA (two per SM), so that set-up and merge of
   // one overlap the other's streaming; with a block list, where many CTAs leave at once and the
@@ -402,6 +407,28 @@ int kvskip_launch_decode_dyn(const kvskip_params* p, int D, int G, int stages, i
   DynArgs dyn;
   dyn.t_dev = t_dev;
   return decode_impl(p, D, G, stages, masked, stats, load_v, dyn, stream);
+}
+
+int kvskip_launch_decode_xchg(const kvskip_params* p, int D, int G, int stages, int masked, int stats,
+                              float* const* peer_bufs, unsigned int* const* peer_flags, int rank, int R,
+                              unsigned int seq, void* stream) {
+  if (!p || !peer_bufs || !peer_flags) return fail(KVSKIP_E_ARG, "decode_xchg: null argument");
+  if (R < 1 || R > kvb::XCHG_MAX_RANKS || rank < 0 || rank >= R)
+    return fail(KVSKIP_E_LIMIT, "decode_xchg: 1..%d ranks", kvb::XCHG_MAX_RANKS);
+  if (seq == 0) return fail(KVSKIP_E_ARG, "decode_xchg: seq >= 1");
+  DynArgs dyn;
+  for (int r = 0; r < R; ++r) {
+    if (!peer_bufs[r] || !peer_flags[r]) return fail(KVSKIP_E_ARG, "decode_xchg: null peer pointer");
+    dyn.xa.peers.buf[r] = peer_bufs[r];
+    dyn.xa.peers.flags[r] = peer_flags[r];
+  }
+  dyn.xa.rank = rank;
+  dyn.xa.R = R;
+  dyn.xa.N = static_cast<long long>(p->B) * p->Hq;
+  dyn.xa.seq = seq;
+  if (D != 128 || g_decode_path.load(std::memory_order_relaxed) == 1)
+    return fail(KVSKIP_E_ARG, "decode_xchg: tensor-core path only (D = 128, decode_path != 1)");
+  return decode_impl(p, D, G, stages, masked, stats, 1, dyn, stream);
 }
 
 int kvskip_launch_decode_paged(const kvskip_params* p, int D, int G, int stages, int masked, int stats, int load_v,

@@ -93,12 +93,21 @@ Paged paged_args(const c10::optional<at::Tensor>& page_table, const at::Tensor& 
 
 // [out bf16 [B,Hq,D] (undefined without load_v), lse [B,Hq], blk_max, blk_sum ([B,Hq,nb] or
 //  undefined), out_f32 or undefined, P fp16 [B,Hq,nb*64] or undefined]
-std::vector<at::Tensor> decode(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double scale,
-                               const c10::optional<at::Tensor>& block_idx,
-                               const c10::optional<at::Tensor>& block_cnt, bool stats, bool load_v,
-                               int64_t num_splits, int64_t stages, bool want_f32, bool write_p,
-                               const c10::optional<at::Tensor>& t_dev, const c10::optional<at::Tensor>& page_table,
-                               int64_t seq_len) {
+namespace {
+// peers of a sequence-sharded step: device addresses of every rank's buffer and flag array
+struct XchgHost {
+  std::vector<int64_t> buf_ptrs, flag_ptrs;
+  int64_t rank = 0, seq = 0;
+};
+}  // namespace
+
+std::vector<at::Tensor> decode_common(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double scale,
+                                      const c10::optional<at::Tensor>& block_idx,
+                                      const c10::optional<at::Tensor>& block_cnt, bool stats, bool load_v,
+                                      int64_t num_splits, int64_t stages, bool want_f32, bool write_p,
+                                      const c10::optional<at::Tensor>& t_dev,
+                                      const c10::optional<at::Tensor>& page_table, int64_t seq_len,
+                                      const XchgHost* xh) {
   need_q(q);
   need_kv(k, "k");
   need_kv(v, "v");
@@ -162,7 +171,20 @@ std::vector<at::Tensor> decode(const at::Tensor& q, const at::Tensor& k, const a
   p.nb = static_cast<int32_t>(nb);
   p.t_pad = nb * KVSKIP_TILE;
   if (write_p) p.p_out = u16m(pbuf);
-  if (pg.table)
+  if (xh) {
+    const int64_t R = static_cast<int64_t>(xh->buf_ptrs.size());
+    TORCH_CHECK(R >= 1 && R <= 8 && xh->flag_ptrs.size() == xh->buf_ptrs.size() && !pg.table && !t_dev.has_value() &&
+                    load_v, "decode_exchange arguments");
+    float* bufs[8];
+    unsigned int* flags[8];
+    for (int64_t r = 0; r < R; ++r) {
+      bufs[r] = reinterpret_cast<float*>(xh->buf_ptrs[r]);
+      flags[r] = reinterpret_cast<unsigned int*>(xh->flag_ptrs[r]);
+    }
+    raise_on(kvskip_launch_decode_xchg(&p, static_cast<int>(D), static_cast<int>(Hq / Hkv), static_cast<int>(stages),
+                                       masked, stats, bufs, flags, static_cast<int>(xh->rank), static_cast<int>(R),
+                                       static_cast<unsigned int>(xh->seq), cur_stream()));
+  } else if (pg.table)
     raise_on(kvskip_launch_decode_paged(&p, static_cast<int>(D), static_cast<int>(Hq / Hkv), static_cast<int>(stages),
                                         masked, stats, load_v, pg.table, pg.max_pages, pg.num_pages, tdev_ptr(t_dev),
                                         cur_stream()));
@@ -173,6 +195,32 @@ std::vector<at::Tensor> decode(const at::Tensor& q, const at::Tensor& k, const a
     raise_on(kvskip_launch_decode(&p, static_cast<int>(D), static_cast<int>(Hq / Hkv), static_cast<int>(stages),
                                   masked, stats, load_v, cur_stream()));
   return {out, lse, bmax, bsum, out32, pbuf};
+}
+
+std::vector<at::Tensor> decode(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double scale,
+                               const c10::optional<at::Tensor>& block_idx,
+                               const c10::optional<at::Tensor>& block_cnt, bool stats, bool load_v,
+                               int64_t num_splits, int64_t stages, bool want_f32, bool write_p,
+                               const c10::optional<at::Tensor>& t_dev, const c10::optional<at::Tensor>& page_table,
+                               int64_t seq_len) {
+  return decode_common(q, k, v, scale, block_idx, block_cnt, stats, load_v, num_splits, stages, want_f32, write_p, t_dev,
+                       page_table, seq_len, nullptr);
+}
+
+// Sequence shards: attention over this rank's blocks, exchange with the peers and merge, one kernel.
+// Returns what decode returns, for the whole sequence.
+std::vector<at::Tensor> decode_exchange(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double scale,
+                                        const c10::optional<at::Tensor>& block_idx,
+                                        const c10::optional<at::Tensor>& block_cnt, int64_t num_splits,
+                                        const std::vector<int64_t>& buf_ptrs, const std::vector<int64_t>& flag_ptrs,
+                                        int64_t rank, int64_t seq) {
+  XchgHost xh;
+  xh.buf_ptrs = buf_ptrs;
+  xh.flag_ptrs = flag_ptrs;
+  xh.rank = rank;
+  xh.seq = seq;
+  return decode_common(q, k, v, scale, block_idx, block_cnt, false, true, num_splits, 2, true, false, c10::nullopt,
+                       c10::nullopt, 0, &xh);
 }
 
 // Two-pass V-skip, second pass: [out bf16, out_f32 or undefined]
@@ -613,6 +661,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("pack_partial", &pack_partial, "rank-local (out_f32, lse) -> packed (acc, m, l) rows", py::arg("out_f32"),
         py::arg("lse"));
   m.def("merge_packed", &merge_packed, "merge of R packed partial buffers [R,N,D+2]", py::arg("parts"));
+  m.def("decode_exchange", &decode_exchange,
+        "sequence shards: local attention, peer-memory exchange and merge in one kernel", py::arg("q"), py::arg("k"),
+        py::arg("v"), py::arg("scale"), py::arg("block_idx") = py::none(), py::arg("block_cnt") = py::none(),
+        py::arg("num_splits") = 2, py::arg("buf_ptrs"), py::arg("flag_ptrs"), py::arg("rank"), py::arg("seq"));
   m.def("exchange_merge", &exchange_merge, "sequence shards: peer-memory exchange and merge in one kernel",
         py::arg("out_f32"), py::arg("lse"), py::arg("buf_ptrs"), py::arg("flag_ptrs"), py::arg("rank"), py::arg("seq"));
   m.def("index_blocks", &index_blocks, "token-index blocks of one step", py::arg("ids"), py::arg("T"), py::arg("out"),

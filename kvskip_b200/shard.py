@@ -130,6 +130,20 @@ class PeerExchange:
         torch.cuda.synchronize(device)
         dist.barrier(group)                       # every rank's flags are zero before anyone writes
 
+    def decode(self, q, k_local, v_local, scale, plan=None, num_splits=None):
+        """Local attention + exchange + merge in one launch (kvskip_launch_decode_xchg).  Needs at
+        least two splits and at most half as many (batch, kv head) pairs as SMs."""
+        q = q.squeeze(2) if q.dim() == 4 else q
+        B, Hq, D = q.shape
+        if num_splits is None:
+            n_items = math.ceil(k_local.shape[2] / BLOCK) if plan is None else plan.max_cnt
+            num_splits = max(2, K.num_splits_for(B * k_local.shape[1], n_items))
+        bi, bc = (None, None) if plan is None else (plan.block_idx, plan.block_cnt)
+        self.seq += 1
+        out, lse, _, _, o32, _ = K.ext().decode_exchange(q, k_local, v_local, float(scale), bi, bc, int(num_splits),
+                                                         self.buf_ptrs, self.flag_ptrs, self.rank, self.seq)
+        return {"out": out, "out_f32": o32, "lse": lse}
+
     def __call__(self, out_f32: torch.Tensor, lse: torch.Tensor):
         self.seq += 1
         return K.ext().exchange_merge(out_f32.reshape(self.n_rows, self.D), lse.reshape(self.n_rows),
@@ -137,12 +151,16 @@ class PeerExchange:
 
 
 def decode_sequence_sharded(q, k_local, v_local, scale, plan=None, group=None, num_splits=None, backend=None,
-                            exchange: "PeerExchange | None" = None):
+                            exchange: "PeerExchange | None" = None, fused: bool = False):
     """One decode step with the sequence split over the ranks of `group`.  k_local / v_local
     hold this rank's block range; `plan` (optional) lists local block indices.  Every rank
     returns the full result.  With `exchange` (a PeerExchange built once for this shape) the
-    triples travel by peer stores inside one kernel instead of an all-gather."""
+    triples travel by peer stores inside one kernel instead of an all-gather; with `fused` as well
+    that kernel is the attention kernel itself (its split merge stores to the peers, waits and
+    merges), so the whole step is one launch."""
     B, Hq = q.shape[0], q.shape[1]
+    if exchange is not None and fused:
+        return exchange.decode(q, k_local, v_local, scale, plan=plan, num_splits=num_splits)
     if exchange is not None:
         r = K.decode(q, k_local, v_local, scale, plan=plan, num_splits=num_splits, out_f32=True)
         out, o32, lse = exchange(r["out_f32"], r["lse"])

@@ -475,6 +475,28 @@ def test_exchange_merge_single_rank():
     assert K.ext().device_status() == 0
 
 
+def test_decode_exchange_single_rank(path):
+    """Attention + exchange + merge in one kernel with one rank (its own buffer is the only peer):
+    the outputs are those of the plain launch with the same split count."""
+    if path == "exact":
+        pytest.skip("the exchange inside the kernel exists on the tensor-core path")
+    q, k, v, scale, keep = synth.sink_body_case(8, T=8192 + 13, B=2)
+    qc, kc, vc = cuda(q, k, v)
+    N, D = 2 * 32, 128
+    buf = torch.zeros(2 * N * (D + 2) + N, dtype=torch.float32, device=DEV)
+    bp, fp = [buf.data_ptr()], [buf.data_ptr() + 4 * 2 * N * (D + 2)]
+    plan = K.make_plan(keep.to(DEV))
+    for seq, pl in ((1, None), (2, plan), (3, None)):
+        bi, bc = (None, None) if pl is None else (pl.block_idx, pl.block_cnt)
+        out, lse, _, _, o32, _ = K.ext().decode_exchange(qc, kc, vc, scale, bi, bc, 6, bp, fp, 0, seq)
+        ref = K.decode(qc, kc, vc, scale, plan=pl, num_splits=6, out_f32=True)
+        assert torch.equal(o32, ref["out_f32"]) and torch.equal(out, ref["out"])
+        assert torch.allclose(lse, ref["lse"], rtol=0, atol=1e-5)
+    with pytest.raises(RuntimeError, match="num_splits > 1"):
+        K.ext().decode_exchange(qc, kc, vc, scale, None, None, 1, bp, fp, 0, 4)
+    assert K.ext().device_status() == 0
+
+
 def _xchg_rank(rank, world, port, ret):
     import os
     import torch.distributed as dist
@@ -494,6 +516,9 @@ def _xchg_rank(rank, world, port, ret):
             a = shard.decode_sequence_sharded(qc, kl, vl, scale)
             b = shard.decode_sequence_sharded(qc, kl, vl, scale, exchange=xchg)
             ok = ok and torch.equal(a["out_f32"], b["out_f32"]) and torch.equal(a["lse"], b["lse"])
+            c = shard.decode_sequence_sharded(qc, kl, vl, scale, exchange=xchg, fused=True)   # one launch in all
+            ok = ok and torch.equal(a["out_f32"], c["out_f32"]) and torch.equal(a["lse"], c["lse"])
+            ok = ok and torch.equal(a["out"], c["out"])
         if rank == 0:
             ref = oracle.decode_f64(q, k, v, scale)
             ret["err"] = rel_err(b["out_f32"], ref["out"])
