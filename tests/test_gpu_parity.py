@@ -497,6 +497,47 @@ def test_decode_exchange_single_rank(path):
     assert K.ext().device_status() == 0
 
 
+def test_decode_exchange_four_ranks_emulated(path):
+    """The one-launch sequence-sharded step as rank 0 of four, on one GPU and without any kernel
+    waiting for another: the triples and flags of ranks 1..3 are placed in rank 0's buffer
+    beforehand (as their kernels would have stored them), the peers' own buffers are scratch.
+    The result equals pack -> merge of the four partials."""
+    if path == "exact":
+        pytest.skip("the exchange inside the kernel exists on the tensor-core path")
+    from kvskip_b200 import shard
+    R, B = 4, 1
+    q, k, v, scale, keep = synth.sink_body_case(12, T=16384 + 50, B=B)
+    qc, kc, vc = cuda(q, k, v)
+    nb = keep.shape[-1]
+    N, D, W = B * 32, 128, 130
+    n_float = 2 * R * N * W
+    bufs = [torch.zeros(n_float + R * N, dtype=torch.float32, device=DEV) for _ in range(R)]
+    bp = [b_.data_ptr() for b_ in bufs]
+    fp = [b_.data_ptr() + 4 * n_float for b_ in bufs]
+    parts = []
+    for r in range(R):
+        lo, hi = shard.block_range(nb, r, R)
+        parts.append(shard.local_partial(qc, kc[:, :, lo * 64:hi * 64], vc[:, :, lo * 64:hi * 64], scale, num_splits=5))
+    want = shard.merge_partials(torch.stack(parts), B, 32)
+    for seq in (1, 2):
+        par = seq & 1
+        mine = bufs[0][:n_float].view(2, R, N, W)
+        flags = bufs[0][n_float:].view(torch.int32).view(R, N)
+        for r in range(1, R):
+            mine[par, r] = parts[r]
+            flags[r] = seq
+        lo, hi = shard.block_range(nb, 0, R)
+        out, lse, _, _, o32, _ = K.ext().decode_exchange(qc, kc[:, :, lo * 64:hi * 64], vc[:, :, lo * 64:hi * 64], scale,
+                                                         None, None, 5, bp, fp, 0, seq)
+        assert torch.equal(o32.view(B, 32, D), want["out_f32"]) and torch.equal(lse.view(B, 32), want["lse"])
+        # rank 0's own triple reached every peer's buffer, with its flags
+        for r in range(1, R):
+            theirs = bufs[r][:n_float].view(2, R, N, W)
+            assert torch.equal(theirs[par, 0], parts[0])
+            assert (bufs[r][n_float:].view(torch.int32).view(R, N)[0] == seq).all()
+    assert K.ext().device_status() == 0
+
+
 def _xchg_rank(rank, world, port, ret):
     import os
     import torch.distributed as dist
