@@ -498,7 +498,7 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="profiling run: warm-up and timed steps of the headline workload only (use with a small "
                          "--batch under ncu), prints a short JSON line")
-    ap.add_argument("--mode", default="dense", choices=["dense", "masked", "masked_stats", "vskip1", "planner"],
+    ap.add_argument("--mode", default="dense", choices=["dense", "masked", "masked_stats", "vskip1", "twopass", "planner"],
                     help="kernel variant of a --profile run")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -576,8 +576,14 @@ def main():
             elif args.mode == "masked_stats":
                 step = lambda: K.decode(q, k, v, scale, plan=plan, stats=True)  # noqa: E731
             else:
+                if B == 1:      # planted bodies (config 3), so that there is something to skip
+                    q, k, v, scale, _ = synth.body_union_case(3, T)
+                    q, k, v = q.to(dev), k.to(dev), v.to(dev)
                 lse = K.decode(q, k, v, scale)["lse"]
-                step = lambda: K.vskip_one_pass(q, k, v, scale, lse_prev=lse)  # noqa: E731
+                if args.mode == "vskip1":
+                    step = lambda: K.vskip_one_pass(q, k, v, scale, tau=1e-4, lse_prev=lse)  # noqa: E731
+                else:
+                    step = lambda: K.vskip_two_pass(q, k, v, scale, "topp", 0.99, sync=False)  # noqa: E731
                 nbytes = kv_bytes(B, T)
         for _ in range(args.warmup):
             step()

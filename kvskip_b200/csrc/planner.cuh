@@ -270,7 +270,9 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
 // lies between lo and hi every further step sees the same set, so the kept set {y >= lo} can no
 // longer change and the loop stops (the 32-step set is identical; lo itself is not an output).
 // Register form: R values of y and exp(y) per lane, nb <= 32 R.
-template <int R>
+// ORDERED = false (block selection of the two-pass V-skip, which has no reference order to keep):
+// four interleaved partial sums per lane instead of one chain of R dependent additions.
+template <int R, bool ORDERED = true>
 __device__ __forceinline__ float pl_bisect_regs(const float* x, const int nb, const int lane, const float lse,
                                                 const float level) {
   float y[R], e[R];
@@ -293,12 +295,23 @@ __device__ __forceinline__ float pl_bisect_regs(const float* x, const int nb, co
     const float mid = 0.5f * (lo + hi);
     float a = 0.f;
     int n_mid = 0;
+    if constexpr (ORDERED) {
 #pragma unroll
-    for (int r = 0; r < R; ++r)
-      if (y[r] >= mid) {
-        a += e[r];
-        ++n_mid;
+      for (int r = 0; r < R; ++r)
+        if (y[r] >= mid) {
+          a += e[r];
+          ++n_mid;
+        }
+    } else {
+      float a4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const bool in = y[r] >= mid;
+        a4[r & 3] += in ? e[r] : 0.f;
+        n_mid += in ? 1 : 0;
       }
+      a = (a4[0] + a4[1]) + (a4[2] + a4[3]);
+    }
     n_mid = __reduce_add_sync(0xffffffffu, n_mid);
     if (warp_sum(a) >= level) { lo = mid; n_lo = n_mid; } else { hi = mid; n_hi = n_mid; }
   }
@@ -507,10 +520,10 @@ __global__ void __launch_bounds__(PL_THREADS) select_kernel(const float* __restr
   const float lse = mx + __logf(warp_sum(se));
   float lo;
   if (rule == 0) {
-    if (nb <= 8 * 32) lo = pl_bisect_regs<8>(x, nb, lane, lse, value);
-    else if (nb <= 16 * 32) lo = pl_bisect_regs<16>(x, nb, lane, lse, value);
-    else if (nb <= 32 * 32) lo = pl_bisect_regs<32>(x, nb, lane, lse, value);
-    else if (nb <= 64 * 32) lo = pl_bisect_regs<64>(x, nb, lane, lse, value);
+    if (nb <= 8 * 32) lo = pl_bisect_regs<8, false>(x, nb, lane, lse, value);
+    else if (nb <= 16 * 32) lo = pl_bisect_regs<16, false>(x, nb, lane, lse, value);
+    else if (nb <= 32 * 32) lo = pl_bisect_regs<32, false>(x, nb, lane, lse, value);
+    else if (nb <= 64 * 32) lo = pl_bisect_regs<64, false>(x, nb, lane, lse, value);
     else lo = pl_bisect_smem(x, ey, nb, lane, lse, value);
   } else {
     lo = __logf(value);
