@@ -505,11 +505,14 @@ __global__ void __launch_bounds__(PL_THREADS) select_kernel(const float* __restr
   pdl_wait_prior();          // the statistics come from the kernel before this one
   pdl_launch_dependents();
 
+  const bool in_regs = nb <= 64 * 32;     // the bisection keeps its values in registers: ey[] is free
   float mx = -INFINITY;
-#pragma unroll 8
+#pragma unroll 16
   for (int i = lane; i < nb; i += 32) {
-    const float val = blk_max[hrow * nb + i] + __logf(blk_sum[hrow * nb + i]);
+    const float bm = blk_max[hrow * nb + i];
+    const float val = bm + __logf(blk_sum[hrow * nb + i]);
     x[i] = val;
+    if (in_regs) ey[i] = bm;              // block maxima for the weights, no second trip to global memory
     mx = fmaxf(mx, val);
   }
   for (int i = tid; i < nb; i += PL_THREADS) skeep[i] = pl_always(i, nb, local) ? 1 : 0;
@@ -539,7 +542,8 @@ __global__ void __launch_bounds__(PL_THREADS) select_kernel(const float* __restr
   const float S = warp_sum(s2 > 0.f ? s2 * __expf(m2 - M) : 0.f);
   const float lse_kept = M + __logf(S);
   for (int i = lane; i < nb; i += 32)
-    weight[(bh * nb + i) * PL_G + warp] = skeep[i] ? __expf(blk_max[hrow * nb + i] - lse_kept) : 0.f;
+    weight[(bh * nb + i) * PL_G + warp] =
+        skeep[i] ? __expf((in_regs ? ey[i] : blk_max[hrow * nb + i]) - lse_kept) : 0.f;
   for (int i = tid; i < nb; i += PL_THREADS) keep[bh * nb + i] = skeep[i];
   pl_compact(nb, block_idx + bh * nb, block_cnt + bh, scan, [&](int i) { return skeep[i] != 0; });
 }
