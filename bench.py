@@ -111,6 +111,7 @@ def reference_arm(args):
     """The CPU restatement of the path (oracle/), all host threads, on a bounded sample."""
     import torch  # noqa: F401
     import oracle
+    oracle.use_all_cores()
     from kvskip_b200 import synth
     Bs = 2
     q, k, v, scale = synth.dense_case(1234, Bs, T_HEAD)
@@ -691,6 +692,7 @@ def main():
         cpu = None
         if world == 1:
             import oracle
+            oracle.use_all_cores()
             from kvskip_b200 import synth
             Bs, reps = 2, 12
             cq, ck, cv, cs = synth.dense_case(1234, Bs, T_HEAD)

@@ -41,6 +41,14 @@ def num_threads() -> int:
     return int(lib().kvo_num_threads())
 
 
+def use_all_cores() -> int:
+    """All cores this process may run on, whatever OMP_NUM_THREADS says (torchrun exports 1)."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().kvo_set_num_threads(int(n))
+    return num_threads()
+
+
 def _p(t):
     if t is None:
         return ctypes.c_void_p(0)

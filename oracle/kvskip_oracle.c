@@ -47,6 +47,16 @@ static inline uint16_t f2bf16(float f) { /* round to nearest even, as __float2bf
 
 int kvo_version(void) { return 3; }
 
+/* Threads of the parallel loops from now on (a launcher may have exported OMP_NUM_THREADS=1). */
+void kvo_set_num_threads(int n) {
+#ifdef _OPENMP
+  extern void omp_set_num_threads(int);
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int kvo_num_threads(void) {
 #ifdef _OPENMP
   extern int omp_get_max_threads(void);
