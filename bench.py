@@ -345,8 +345,15 @@ def _planner_cases(dev, peak, K, synth, RefreshConfig, RefreshLayer, cases):
         frac = read / max(1, total)
         # bytes actually read per layer-step, averaged over the L layers (layer 0 reads everything)
         nbytes = kv_bytes(B, T0 + steps // 2, (frac * (L - 1) + 1.0) / L)
+        # planner metadata of a layer-step on top of K+V: key sums read, statistics written and
+        # re-read, references / current scores, membership bytes and the block list
+        nb_mid = math.ceil((T0 + steps // 2) / 64)
+        meta = (B * HKV * nb_mid * D * 4 + 4 * B * HQ * nb_mid * 4 + 3 * B * HQ * nb_mid * 4 + B * HKV * nb_mid * 6
+                + 2 * B * HQ * D * 2) * (L - 1) / L
         cases.append({"case": label, "us": round(us, 2), "blocks_read_planner_layers": round(frac, 4),
                       "GBps": round(nbytes / (us * 1e-6) / 1e9, 1),
+                      "GBps_kv_plus_metadata": round((nbytes + meta) / (us * 1e-6) / 1e9, 1),
+                      "metadata_share_of_bytes": round(meta / (nbytes + meta), 4),
                       "frac_of_peak": round(nbytes / (us * 1e-6) / 1e9 / peak, 4),
                       "host_us": round(host_us, 2),
                       "us_graph": round(us_g, 2), "us_graph_replay": round(us_replay, 2),
