@@ -145,7 +145,7 @@ int kvskip_launch_decode(const kvskip_params* p, int D, int G, int stages, int m
  *     KVSKIP_E_LIMIT with a message saying so;
  *   - the first call on a device looks the array's address up (cudaGetSymbolAddress, with that
  *     device current) and opts the kernel into its shared-memory size; make that first call
- *     before starting any stream capture;
+ *     during start-up, outside the latency-critical part of the host program;
  *   - all calls on a device share the array: two calls whose kernels overlap on the GPU (different
  *     streams) race on it; calls on one stream are ordered and safe.  The array keeps the last
  *     call's contents and nothing in it needs clearing.
