@@ -258,6 +258,7 @@ int kvskip_launch_select(const float* blk_max, const float* blk_sum, int B, int 
  * kernel and is skipped (status word 0x300 / 0x301) where a single row is addressed.  t_dev may be
  * null (length by value) or a device-resident length as above.  Tensor-core path only (D = 128);
  * write_p is not supported.  `update` and the token index do not touch K/V and need no variant.
+ * kvskip_launch_vskip1_paged is the single-pass V-skip over the same pools (length by value).
  * kvskip_launch_append writes the K and V rows of the newest token (row T-1, T the length after
  * the append) from k_new, v_new [B,Hkv,D] into a contiguous cache (page_table null; sb, sh, st its
  * element strides) or into the pool. */
@@ -266,6 +267,8 @@ int kvskip_launch_decode_paged(const kvskip_params* p, int D, int G, int stages,
                                void* stream);
 int kvskip_launch_plan_paged(const kvskip_plan_params* p, const int32_t* page_table, int max_pages, int num_pages,
                              const int* t_dev, void* stream);
+int kvskip_launch_vskip1_paged(const kvskip_params* p, int D, int G, const int32_t* page_table, int max_pages,
+                               int num_pages, void* stream);
 int kvskip_launch_append(uint16_t* k, uint16_t* v, int64_t sb, int64_t sh, int64_t st, const uint16_t* k_new,
                          const uint16_t* v_new, int B, int Hkv, int D, int T, const int* t_dev,
                          const int32_t* page_table, int max_pages, int num_pages, void* stream);

@@ -295,19 +295,20 @@ int launch_vskip1_t(const kvskip_params& p, cudaStream_t stream) {
   return KVSKIP_OK;
 }
 
-int launch_vskip1_tc(const kvskip_params& p, cudaStream_t stream) {
+int launch_vskip1_tc(const kvskip_params& p, const DynArgs& dyn, cudaStream_t stream) {
   auto kernel = kvb::vskip1_tc_kernel;
   if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), kvb::Vs1TcCfg::kSmemBytes)) return rc;
   kvb::TmaMaps maps;
-  if (int rc = make_kv_map(&maps.k, p.k, p.k_sb, p.k_sh, p.k_st, p.B, p.Hkv, p.T, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+  const int map_b = dyn.pages ? dyn.num_pages : p.B, map_t = dyn.pages ? KVSKIP_TILE : p.T;
+  if (int rc = make_kv_map(&maps.k, p.k, p.k_sb, p.k_sh, p.k_st, map_b, p.Hkv, map_t, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
-  if (int rc = make_kv_map(&maps.v, p.v, p.v_sb, p.v_sh, p.v_st, p.B, p.Hkv, p.T, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+  if (int rc = make_kv_map(&maps.v, p.v, p.v_sb, p.v_sh, p.v_st, map_b, p.Hkv, map_t, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
   int* done = nullptr;
   if (p.num_splits > 1)
     if (int rc = split_done_region(p.B * p.Hkv, &done)) return rc;
   KVB_CUDA(launch_overlapped(kernel, dim3(p.num_splits, p.Hkv, p.B), dim3(kvb::TC_THREADS),
-                             kvb::Vs1TcCfg::kSmemBytes, stream, p, maps, done));
+                             kvb::Vs1TcCfg::kSmemBytes, stream, p, maps, done, dyn.pages, dyn.max_pages));
   if (p.num_splits > 1 && done == nullptr) {
     kvb::merge_kernel<128><<<p.B * p.Hq, 128, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits,
                                                           static_cast<int64_t>(p.B) * p.Hq, true, p.out, p.out_f32,
@@ -525,8 +526,24 @@ int kvskip_launch_vskip1(const kvskip_params* p, int D, int G, void* stream) {
   if (!p->out || !p->lse) return fail(KVSKIP_E_ARG, "out and lse are required");
   if (p->num_splits > 1 && (!p->part_ml || !p->part_acc)) return fail(KVSKIP_E_ARG, "num_splits > 1 needs scratch");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (D == 128 && g_decode_path.load(std::memory_order_relaxed) != 1) return launch_vskip1_tc(*p, s);
+  if (D == 128 && g_decode_path.load(std::memory_order_relaxed) != 1) return launch_vskip1_tc(*p, DynArgs{}, s);
   return D == 128 ? launch_vskip1_t<128>(*p, s) : launch_vskip1_t<64>(*p, s);
+}
+
+int kvskip_launch_vskip1_paged(const kvskip_params* p, int D, int G, const int32_t* page_table, int max_pages,
+                               int num_pages, void* stream) {
+  if (int rc = check_common(p, D, G)) return rc;
+  if (!p->out || !p->lse) return fail(KVSKIP_E_ARG, "out and lse are required");
+  if (p->num_splits > 1 && (!p->part_ml || !p->part_acc)) return fail(KVSKIP_E_ARG, "num_splits > 1 needs scratch");
+  if (!page_table || num_pages < 1 || max_pages < (p->T + KVSKIP_TILE - 1) / KVSKIP_TILE)
+    return fail(KVSKIP_E_ARG, "paged cache: the page table needs an entry for every block of the sequence");
+  if (D != 128 || g_decode_path.load(std::memory_order_relaxed) == 1)
+    return fail(KVSKIP_E_ARG, "a paged cache needs the tensor-core path (D = 128, decode_path != 1)");
+  DynArgs dyn;
+  dyn.pages = page_table;
+  dyn.max_pages = max_pages;
+  dyn.num_pages = num_pages;
+  return launch_vskip1_tc(*p, dyn, static_cast<cudaStream_t>(stream));
 }
 
 int kvskip_launch_pv(const kvskip_params* p, int D, int G, void* stream) {

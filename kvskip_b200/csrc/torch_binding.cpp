@@ -271,15 +271,18 @@ std::vector<at::Tensor> pv(const at::Tensor& P, const at::Tensor& v, const at::T
 // Single-pass V-skip: [out bf16, lse, out_f32 or undefined, vcount int32 [B,Hkv] or undefined]
 std::vector<at::Tensor> vskip1(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double scale,
                                double tau, int64_t local, int64_t num_splits, bool want_f32, bool count,
-                               const c10::optional<at::Tensor>& lse_prev) {
+                               const c10::optional<at::Tensor>& lse_prev,
+                               const c10::optional<at::Tensor>& page_table, int64_t seq_len) {
   need_q(q);
   need_kv(k, "k");
   need_kv(v, "v");
   TORCH_CHECK(tau > 0.0 && local >= 0 && num_splits >= 1, "tau > 0, local >= 0, num_splits >= 1");
   const c10::cuda::CUDAGuard guard(q.device());
-  const int64_t B = q.size(0), Hq = q.size(1), D = q.size(2), Hkv = k.size(1), T = k.size(2);
-  TORCH_CHECK(k.size(0) == B && v.size(0) == B && k.size(3) == D && v.size(3) == D && v.size(1) == Hkv &&
-                  v.size(2) == T, "shape mismatch between q, k, v");
+  const int64_t B = q.size(0), Hq = q.size(1), D = q.size(2), Hkv = k.size(1);
+  const Paged pg = paged_args(page_table, k, &v, B, seq_len);
+  const int64_t T = pg.table ? seq_len : k.size(2);
+  TORCH_CHECK((pg.table || (k.size(0) == B && v.size(0) == B)) && k.size(3) == D && v.size(3) == D &&
+                  v.size(1) == Hkv && v.size(2) == k.size(2), "shape mismatch between q, k, v");
   TORCH_CHECK(Hq % Hkv == 0, "Hq must be a multiple of Hkv");
   const auto f32 = q.options().dtype(at::kFloat);
   at::Tensor out = at::empty({B, Hq, D}, q.options());
@@ -293,6 +296,7 @@ std::vector<at::Tensor> vskip1(const at::Tensor& q, const at::Tensor& k, const a
   }
   kvskip_params p{};
   fill_qkv(p, q, k, v);
+  p.T = static_cast<int32_t>(T);
   p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
   p.num_splits = static_cast<int32_t>(num_splits);
   if (num_splits > 1) {
@@ -311,7 +315,11 @@ std::vector<at::Tensor> vskip1(const at::Tensor& q, const at::Tensor& k, const a
                     lse_prev->numel() == B * Hq, "lse_prev: contiguous fp32 [B, Hq]");
     p.lse_prev = lse_prev->data_ptr<float>();
   }
-  raise_on(kvskip_launch_vskip1(&p, static_cast<int>(D), static_cast<int>(Hq / Hkv), cur_stream()));
+  if (pg.table)
+    raise_on(kvskip_launch_vskip1_paged(&p, static_cast<int>(D), static_cast<int>(Hq / Hkv), pg.table, pg.max_pages,
+                                        pg.num_pages, cur_stream()));
+  else
+    raise_on(kvskip_launch_vskip1(&p, static_cast<int>(D), static_cast<int>(Hq / Hkv), cur_stream()));
   return {out, lse, out32, vcount};
 }
 
@@ -640,7 +648,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("t_dev") = py::none());
   m.def("vskip1", &vskip1, "single-pass V-skip", py::arg("q"), py::arg("k"), py::arg("v"), py::arg("scale"),
         py::arg("tau"), py::arg("local") = 2, py::arg("num_splits") = 1, py::arg("want_f32") = false,
-        py::arg("count") = false, py::arg("lse_prev") = py::none());
+        py::arg("count") = false, py::arg("lse_prev") = py::none(), py::arg("page_table") = py::none(),
+        py::arg("seq_len") = 0);
   m.def("decode", &decode, "split-K decode attention", py::arg("q"), py::arg("k"), py::arg("v"), py::arg("scale"),
         py::arg("block_idx") = py::none(), py::arg("block_cnt") = py::none(), py::arg("stats") = false,
         py::arg("load_v") = true, py::arg("num_splits") = 1, py::arg("stages") = 2, py::arg("want_f32") = false,

@@ -21,7 +21,8 @@ struct Vs1TcCfg {
 };
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
-vskip1_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* __restrict__ split_done) {
+vskip1_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* __restrict__ split_done,
+                 const int32_t* __restrict__ pages, const int max_pages) {
   constexpr int G = 4, D = 128;
   constexpr int NC = TC_CONSUMERS;
   extern __shared__ unsigned char smem_raw[];
@@ -58,6 +59,10 @@ vskip1_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
   __syncthreads();
   pdl_wait_prior();          // nothing written by the previous kernel on the stream is read above
   pdl_launch_dependents();
+  // contiguous cache: rows blk*64.. of sequence b; paged cache (pages != nullptr): the whole page
+  // the table names for block blk -- the maps then run over the page pool
+  auto row_of = [&](int blk) { return pages ? 0 : blk * TILE; };
+  auto seq_of = [&](int blk) { return pages ? pages[static_cast<int64_t>(b) * max_pages + blk] : b; };
 
   const int lrow = lane & 7, lmat = lane >> 3;
   const int64_t hq0 = static_cast<int64_t>(b) * p.Hq + h * G;
@@ -126,8 +131,8 @@ vskip1_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
   if (sink_rule) {
     if (warp == NC && lane == 0) {
       mbar_expect_tx(pro, Vs1TcCfg::kKBytes);
-      tma_load_4d(ringK, &maps.k, pro, 0, 0, h, b);
-      tma_load_4d(ringK + TC_HALF_BYTES, &maps.k, pro, 64, 0, h, b);
+      tma_load_4d(ringK, &maps.k, pro, 0, 0, h, seq_of(0));
+      tma_load_4d(ringK + TC_HALF_BYTES, &maps.k, pro, 64, 0, h, seq_of(0));
     }
     if (warp == 0) {
       if (mbar_wait(pro, 0, 0x340u)) {
@@ -156,10 +161,10 @@ vskip1_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
       for (int i = 0; i < n; ++i) {
         const int s = i % NC;
         if (i >= NC && !mbar_wait(&kempty[s], ((i / NC) - 1) & 1, 0x350u + s)) break;
-        const int t0 = (i0 + i) * TILE;
+        const int t0 = row_of(i0 + i), bp = seq_of(i0 + i);
         mbar_expect_tx(&kfull[s], Vs1TcCfg::kKBytes);
-        tma_load_4d(ringK + s * Vs1TcCfg::kKBytes, &maps.k, &kfull[s], 0, t0, h, b);
-        tma_load_4d(ringK + s * Vs1TcCfg::kKBytes + TC_HALF_BYTES, &maps.k, &kfull[s], 64, t0, h, b);
+        tma_load_4d(ringK + s * Vs1TcCfg::kKBytes, &maps.k, &kfull[s], 0, t0, h, bp);
+        tma_load_4d(ringK + s * Vs1TcCfg::kKBytes + TC_HALF_BYTES, &maps.k, &kfull[s], 64, t0, h, bp);
       }
     }
   } else {
@@ -174,12 +179,23 @@ vskip1_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
     uint32_t pend_b[4][4];          // P of the pending block as B fragments: [16-token step][hi0, hi1, lo0, lo1]
     float pend_alpha[2] = {1.f, 1.f};
     bool pending = false;
+    int pend_rows = TILE;
     uint32_t vphase = 0;
     int loaded = 0;
     bool ok = true;
 
     auto retire = [&]() {           // acc = alpha * acc + V^T P^T for the pending block
       if (!mbar_wait(&vfull[warp], vphase ^ 1u, 0x360u + warp)) { ok = false; return; }
+      if (pages != nullptr && pend_rows < TILE) {
+        // paged cache: the rows of the last page past the sequence hold stale data; their weights
+        // are zero but 0 x NaN is not, so clear them (whole 128-byte rows of both halves)
+        unsigned char* vb = bufV + warp * Vs1TcCfg::kVBytes;
+        for (int o = pend_rows * 128 + lane * 16; o < TILE * 128; o += 32 * 16) {
+          *reinterpret_cast<uint4*>(vb + o) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(vb + TC_HALF_BYTES + o) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        __syncwarp();
+      }
       if (__any_sync(0xffffffffu, pend_alpha[0] != 1.f || pend_alpha[1] != 1.f)) {
 #pragma unroll
         for (int mt = 0; mt < 8; ++mt) {
@@ -252,11 +268,13 @@ vskip1_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
         if (lane == 0) {
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           mbar_expect_tx(&vfull[warp], Vs1TcCfg::kVBytes);
-          tma_load_4d(bufV + warp * Vs1TcCfg::kVBytes, &maps.v, &vfull[warp], 0, blk * TILE, h, b);
-          tma_load_4d(bufV + warp * Vs1TcCfg::kVBytes + TC_HALF_BYTES, &maps.v, &vfull[warp], 64, blk * TILE, h, b);
+          const int tv = row_of(blk), bv = seq_of(blk);
+          tma_load_4d(bufV + warp * Vs1TcCfg::kVBytes, &maps.v, &vfull[warp], 0, tv, h, bv);
+          tma_load_4d(bufV + warp * Vs1TcCfg::kVBytes + TC_HALF_BYTES, &maps.v, &vfull[warp], 64, tv, h, bv);
         }
         vphase ^= 1u;                                        // retire() waits for parity vphase ^ 1
         pending = true;
+        pend_rows = min(TILE, p.T - blk * TILE);             // rows of the block that hold tokens
         ++loaded;
       }
     }

@@ -234,19 +234,24 @@ def vskip_two_pass(q, k, v, scale: float, rule: str = "topp", value: float = 0.9
 
 def vskip_one_pass(q, k, v, scale: float, tau: float = 1e-4, local: int = 2, num_splits: int | None = None,
                    out_f32: bool = False, count: bool = False, lse_prev: torch.Tensor | None = None,
-                   sync: bool = True) -> dict:
+                   sync: bool = True, page_table: torch.Tensor | None = None, seq_len: int | None = None) -> dict:
     """Single-pass V-skip: K is read once; the V block of a tile is read only if some query head of
     the group gives the block an estimated weight >= tau.  The normaliser estimate is `lse_prev`
     (per query head, e.g. the "lse" this function returned one step earlier); without it every
     CTA uses the sink block's log-sum-exp, a lower bound that keeps every block the exact rule
-    keeps.  count=True adds "v_tiles" [B, Hkv] (and "kept_frac" when sync)."""
+    keeps.  count=True adds "v_tiles" [B, Hkv] (and "kept_frac" when sync).
+    page_table with seq_len (not in the reference): k and v are page pools, as in `decode`."""
     q = _q3(q)
     B, Hkv, T = q.shape[0], k.shape[1], k.shape[2]
+    if page_table is not None:
+        if seq_len is None:
+            raise ValueError("a paged cache needs seq_len")
+        T = int(seq_len)
     nb = math.ceil(T / TILE)
     if num_splits is None:
         num_splits = num_splits_for(B * Hkv, nb)
     out, lse, o32, cnt = ext().vskip1(q, k, v, float(scale), float(tau), int(local), int(num_splits),
-                                      out_f32, count, lse_prev)
+                                      out_f32, count, lse_prev, page_table, int(seq_len or 0))
     res = {"out": out, "lse": lse, "num_splits": num_splits}
     if out_f32:
         res["out_f32"] = o32

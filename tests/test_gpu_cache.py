@@ -182,3 +182,22 @@ def test_dyn_and_paged_entry_points_through_ctypes():
     kc[:, :, T - 1] = 0
     abi.append(kc, vc, k[:, :, T - 1].contiguous(), v[:, :, T - 1].contiguous(), T)
     assert torch.equal(kc, k) and torch.equal(vc, v)
+
+
+@pytest.mark.parametrize("T", [4096, 4000])
+def test_paged_single_pass_vskip_matches_contiguous(T):
+    """The single-pass V-skip over a shuffled page pool with NaN in every unused page row: same
+    votes, same outputs as over the contiguous cache."""
+    q, k, v, scale, _ = synth.body_union_case(5, 4096)
+    q, k, v = q.to(DEV), k.to(DEV), v.to(DEV)
+    pg = _paged_from(k, v, T, 4096, seed=T)
+    lse = K.decode(q, k[:, :, :T], v[:, :, :T], scale)["lse"]
+    for prev in (None, lse):
+        for splits in (1, 5):
+            a = K.vskip_one_pass(q, k[:, :, :T], v[:, :, :T], scale, tau=1e-4, lse_prev=prev, num_splits=splits,
+                                 out_f32=True, count=True)
+            b = K.vskip_one_pass(q, pg.k, pg.v, scale, tau=1e-4, lse_prev=prev, num_splits=splits, out_f32=True,
+                                 count=True, page_table=pg.table, seq_len=T)
+            assert torch.equal(a["v_tiles"], b["v_tiles"]) and 0 < a["kept_frac"] < 1
+            assert torch.equal(a["out_f32"], b["out_f32"]) and torch.equal(a["lse"], b["lse"])
+            assert torch.isfinite(b["out_f32"]).all()
