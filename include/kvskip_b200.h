@@ -141,7 +141,7 @@ int kvskip_launch_decode(const kvskip_params* p, int D, int G, int stages, int m
  * Takes the same arguments as kvskip_launch_decode; p->part_acc and p->part_ml are ignored.
  * When num_splits > 1 the split partials go to an array built into the library (one per device
  * that loads it, held until exit) instead of caller scratch:
- *   - limit: B*Hq*num_splits*(D+2) <= KVSKIP_NOALLOC_MAX_FLOATS (4 MiB of floats), else
+ *   - limit: B*Hq*num_splits*(D+2) <= KVSKIP_NOALLOC_MAX_FLOATS (1 Mi floats = 4 MiB), else
  *     KVSKIP_E_LIMIT with a message saying so;
  *   - the first call on a device looks the array's address up (cudaGetSymbolAddress, with that
  *     device current) and opts the kernel into its shared-memory size; make that first call
@@ -284,7 +284,19 @@ int kvskip_launch_append(uint16_t* k, uint16_t* v, int64_t sb, int64_t sh, int64
  *                  full-size CTA per SM.
  *   "pdl"          1 (default): the attention and planner kernels are launched with programmatic
  *                  stream serialisation, so their set-up overlaps the tail of the previous kernel
- *                  on the stream (they wait for it before reading memory); 0: plain launches. */
+ *                  on the stream (they wait for it before reading memory); 0: plain launches.
+ *   "spin_limit"   polls (about 100 ns each) a kernel of the sequence-sharded exchange spends on a
+ *                  peer's flag before it gives up, sets the status word (0x500 + peer from
+ *                  kvskip_launch_exchange_merge, 0x510 + peer from kvskip_launch_decode_xchg),
+ *                  merges what arrived and returns; default 2^21 (about 2 s); 0 restores it.
+ *
+ * Concurrency.  The kernels that merge their splits in the same launch (attention, V-skip, plan)
+ * count finished CTAs in device counters owned by the (device, stream) pair of the launch: launches
+ * on one stream follow one another and share them safely, launches on different streams use
+ * different ones, and a launch captured into a CUDA graph keeps the counters of the stream it was
+ * captured on.  Unsupported: replaying such a graph while other launches of this library run on the
+ * stream it was captured on.  A device that has used more than 64 streams with this library gets a
+ * separate merge launch for the newcomers (plan reports KVSKIP_E_LIMIT). */
 int kvskip_set_option(const char* name, int value);
 int kvskip_get_option(const char* name);
 
@@ -293,7 +305,9 @@ const char* kvskip_last_error(void);
 
 /* Reads (and clears) the current device's kernel status word after synchronising `stream`:
  * 0 if every bounded wait inside the kernels completed, otherwise the code of the first that
- * gave up.  Host-blocking; meant for tests and post-mortems, not for the hot path. */
+ * gave up.  Host-blocking; meant for tests and post-mortems, not for the hot path.  When the word is
+ * non-zero the call also waits for the whole device and clears the split counters a kernel that
+ * gave up may have left behind: no launch of this library may be in flight on another host thread. */
 int kvskip_device_status(void* stream, unsigned int* status);
 
 /* Library version: major * 10000 + minor * 100 + patch. */

@@ -3,7 +3,8 @@
     python -m kvskip_b200.build            # builds what is out of date
     python -m kvskip_b200.build --force
 
-Products (next to this file, git-ignored):
+Products (next to this file, git-ignored; in the directory $KVSKIP_BUILD when that variable is set,
+the reference's name for its build directory, kernels/kvskip.py:33):
     libkvskip_b200.so   nvcc, sm_100a only, no framework dependency: the C ABI of include/kvskip_b200.h
     _kvskip_ext.so      g++, the pybind11/ATen module over it (links libkvskip_b200.so via $ORIGIN)
 """
@@ -18,8 +19,20 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 ROOT = PKG.parent
-LIB = PKG / "libkvskip_b200.so"
-EXT = PKG / "_kvskip_ext.so"
+
+
+def out_dir() -> Path:
+    """Where the two shared objects live: $KVSKIP_BUILD if set (created on demand), else the package."""
+    d = os.environ.get("KVSKIP_BUILD")
+    if not d:
+        return PKG
+    p = Path(d).expanduser().resolve()
+    p.mkdir(parents=True, exist_ok=True)
+    return p
+
+
+LIB = out_dir() / "libkvskip_b200.so"
+EXT = out_dir() / "_kvskip_ext.so"
 
 NVCC_FLAGS = ["-O3", "--use_fast_math", "-lineinfo", "-std=c++17",
               "-gencode", "arch=compute_100a,code=sm_100a",
@@ -65,7 +78,7 @@ def build_ext(force=False, verbose=False) -> Path:
                "-DTORCH_EXTENSION_NAME=_kvskip_ext", "-DTORCH_API_INCLUDE_EXTENSION_H",
                f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
                *[f"-I{p}" for p in inc], CSRC / "torch_binding.cpp",
-               *[f"-L{p}" for p in libdirs], f"-L{PKG}",
+               *[f"-L{p}" for p in libdirs], f"-L{LIB.parent}",
                "-lkvskip_b200", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
                "-Wl,-rpath,$ORIGIN", *[f"-Wl,-rpath,{p}" for p in library_paths("cuda")],
                "-o", EXT]

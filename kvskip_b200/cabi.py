@@ -57,13 +57,18 @@ def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
+def _default_lib():
+    from . import build
+    return build.LIB
+
+
 def _stream():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
 class CAbi:
     def __init__(self, path=None, prefix="kvskip"):
-        self.path = Path(path) if path else HERE / "libkvskip_b200.so"
+        self.path = Path(path) if path else _default_lib()
         if not self.path.exists():
             raise RuntimeError(f"{self.path} is missing: build it with `python -m kvskip_b200.build`")
         self.lib = C.CDLL(str(self.path))

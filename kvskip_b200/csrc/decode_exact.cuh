@@ -363,8 +363,8 @@ __global__ void __launch_bounds__(D) merge_packed_kernel(const float* __restrict
 // merges the R triples from its own buffer in ascending rank order (the arithmetic of
 // merge_packed_kernel, so the bits equal the all-gather path).  Two buffer sets alternate by the
 // parity of seq: a rank can be at most one step ahead of a peer, because finishing a step needs
-// the peer's flags of that step.  The wait is bounded; on expiry the status word is set and the
-// row is written from whatever arrived.
+// the peer's flags of that step.  The wait is bounded (`spin` polls of about 100 ns each); on expiry
+// the status word is set to 0x500 + peer and the row is written from whatever arrived.
 constexpr int XCHG_MAX_RANKS = 8;
 struct XchgPeers {
   float* buf[XCHG_MAX_RANKS];
@@ -375,7 +375,8 @@ template <int D>
 __global__ void __launch_bounds__(D) exchange_merge_kernel(const float* __restrict__ out_f32,
                                                            const float* __restrict__ lse, const XchgPeers peers,
                                                            int rank, int R, int64_t N, unsigned int seq,
-                                                           uint16_t* out, float* res_f32, float* res_lse) {
+                                                           unsigned int spin, uint16_t* out, float* res_f32,
+                                                           float* res_lse) {
   constexpr int W = D + 2;
   const int64_t row = blockIdx.x;
   const int d = threadIdx.x;
@@ -409,7 +410,7 @@ __global__ void __launch_bounds__(D) exchange_merge_kernel(const float* __restri
   if (d < R) {
     const volatile unsigned int* f = peers.flags[rank] + static_cast<int64_t>(d) * N + row;
     bool got = false;
-    for (uint32_t it = 0; it < (1u << 21); ++it) {
+    for (uint32_t it = 0; it < spin; ++it) {
       // ">= seq" in wrap-safe form: a peer that has already gone on to its next step has
       // overwritten this flag with the next value, which still says that step `seq` arrived
       if (static_cast<int>(*f - seq) >= 0) { got = true; break; }

@@ -255,7 +255,73 @@ struct XchgArgs {
   int R;                 // 0: no exchange
   long long N;           // rows of the exchange (B * Hq)
   unsigned int seq;
+  unsigned int spin;     // polls of a peer's flag before the wait gives up (status word 0x510 + peer)
 };
+
+// One element of this rank's packed row (acc = out, then m = lse / ln 2 and l = 1) into every
+// rank's buffer: plain stores, to peer memory over NVLink for r != rank.
+__device__ __forceinline__ void xchg_store(const XchgArgs& xa, const int64_t hq, const int d, const float o32,
+                                           const float lse_nat) {
+  constexpr int D = 128, XW = D + 2;
+  const int64_t slot = ((static_cast<int64_t>(xa.seq & 1u) * xa.R + xa.rank) * xa.N + hq) * XW;
+  for (int r = 0; r < xa.R; ++r) {
+    float* dst = xa.peers.buf[r] + slot;
+    dst[d] = o32;
+    if (d == 0) {
+      dst[D] = lse_nat == -INFINITY ? -INFINITY : lse_nat * LOG2E;
+      dst[D + 1] = lse_nat == -INFINITY ? 0.f : 1.f;
+    }
+  }
+}
+
+// After the four rows of (batch b, kv head h) were stored with xchg_store by this CTA: make them
+// visible system-wide, flag them on every rank, wait -- bounded -- for the peers' flags of the same
+// rows on this rank's own array, and merge the R triples in ascending rank order (the arithmetic of
+// merge_packed_kernel).  Called by every thread of the CTA.
+template <int THREADS>
+__device__ __forceinline__ void xchg_finish(const kvskip_params& p, const XchgArgs& xa, const int b, const int h,
+                                            const int tid) {
+  constexpr int G = 4, D = 128, XW = D + 2;
+  const int64_t hq0x = static_cast<int64_t>(b) * p.Hq + h * G;
+  __threadfence_system();       // the rows are visible on every GPU before their flags
+  __syncthreads();
+  if (tid < G * xa.R) {
+    const int g = tid / xa.R, r = tid % xa.R;
+    volatile unsigned int* f = xa.peers.flags[r] + static_cast<int64_t>(xa.rank) * xa.N + hq0x + g;
+    *f = xa.seq;
+  }
+  if (tid < G * xa.R) {         // this rank's copy of the flags of its four rows, one per peer
+    const int g = tid / xa.R, r = tid % xa.R;
+    const volatile unsigned int* f = xa.peers.flags[xa.rank] + static_cast<int64_t>(r) * xa.N + hq0x + g;
+    bool got = false;
+    for (uint32_t it = 0; it < xa.spin; ++it) {
+      if (static_cast<int>(*f - xa.seq) >= 0) { got = true; break; }
+      __nanosleep(100);
+    }
+    if (!got) atomicCAS(&g_status, 0u, 0x510u + r);
+  }
+  __threadfence_system();
+  __syncthreads();
+  const float* mine = xa.peers.buf[xa.rank] + (static_cast<int64_t>(xa.seq & 1u) * xa.R) * xa.N * XW;
+  for (int o = tid; o < G * D; o += THREADS) {
+    const int g = o / D, d = o % D;
+    const int64_t row = hq0x + g;
+    float m = -INFINITY;
+    for (int r = 0; r < xa.R; ++r) m = fmaxf(m, __ldcg(mine + (static_cast<int64_t>(r) * xa.N + row) * XW + D));
+    const float mu = (m == -INFINITY) ? 0.f : m;
+    float l = 0.f, acc2 = 0.f;
+    for (int r = 0; r < xa.R; ++r) {
+      const float* pr = mine + (static_cast<int64_t>(r) * xa.N + row) * XW;
+      const float w = ex2(__ldcg(pr + D) - mu);
+      l += __ldcg(pr + D + 1) * w;
+      acc2 += __ldcg(pr + d) * w;
+    }
+    const float o32 = l > 0.f ? acc2 / l : 0.f;
+    reinterpret_cast<__nv_bfloat16*>(p.out)[row * D + d] = __float2bfloat16(o32);
+    if (p.out_f32) p.out_f32[row * D + d] = o32;
+    if (d == 0 && p.lse) p.lse[row] = l > 0.f ? (m + log2f(l)) * LN2 : -INFINITY;
+  }
+}
 
 template <int NC, bool MASKED, bool STATS, bool LOAD_V>
 __global__ void __launch_bounds__((NC + 1) * 32, NC <= 3 ? 2 : 1)
@@ -414,6 +480,7 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
   }
   __syncthreads();   // every block has been consumed: the ring is free for the merge of the warps
 
+  const bool xchg = LOAD_V && xa.R > 0;
   if constexpr (LOAD_V) {
     float* red = reinterpret_cast<float*>(ring);   // [NC][G][D]
     if (warp < NC && (lane & 3) < 2) {
@@ -441,8 +508,12 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
       const int64_t hq = static_cast<int64_t>(b) * p.Hq + h * G + g;
       if (S_use == 1) {
         const float o32 = l > 0.f ? sum / l : 0.f;
-        reinterpret_cast<__nv_bfloat16*>(p.out)[hq * D + d] = __float2bfloat16(o32);
-        if (p.out_f32) p.out_f32[hq * D + d] = o32;
+        if (!xchg) {
+          reinterpret_cast<__nv_bfloat16*>(p.out)[hq * D + d] = __float2bfloat16(o32);
+          if (p.out_f32) p.out_f32[hq * D + d] = o32;
+        } else {   // a head this rank reads in one piece (a short or empty list): its row goes to the peers from here
+          xchg_store(xa, hq, d, o32, l > 0.f ? (M + log2f(l)) * LN2 : -INFINITY);
+        }
       } else {
         p.part_acc[(hq * p.num_splits + split) * D + d] = sum;
       }
@@ -456,7 +527,7 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
     for (int w = 0; w < NC; ++w) l += sL[w * 4 + tid] * ex2(sM[w * 4 + tid] - mu);
     const int64_t hq = static_cast<int64_t>(b) * p.Hq + h * G + tid;
     if (S_use == 1) {
-      if (p.lse) p.lse[hq] = l > 0.f ? (M + log2f(l)) * LN2 : -INFINITY;
+      if (p.lse && !xchg) p.lse[hq] = l > 0.f ? (M + log2f(l)) * LN2 : -INFINITY;
     } else {
       p.part_ml[(hq * p.num_splits + split) * 2] = M;
       p.part_ml[(hq * p.num_splits + split) * 2 + 1] = l;
@@ -467,7 +538,9 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
   // same ascending-split order as merge_kernel, without a second launch.  split_done[] counts the
   // finished splits and is put back to zero by the CTA that merges.
   if constexpr (LOAD_V) {
-    if (S_use > 1 && split_done != nullptr) {
+    if (S_use == 1) {
+      if (xchg) xchg_finish<TC_THREADS>(p, xa, b, h, tid);
+    } else if (split_done != nullptr) {
       __shared__ int s_last;
       __threadfence();            // this CTA's partials are visible device-wide before it is counted
       __syncthreads();
@@ -476,8 +549,6 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
       if (s_last) {
         __threadfence();
         const int S2 = S_use;             // partials used; their stride stays p.num_splits
-        constexpr int XW = D + 2;
-        const bool xchg = xa.R > 0;
         for (int o = tid; o < G * D; o += TC_THREADS) {
           const int g = o / D, d = o % D;
           const int64_t hq = static_cast<int64_t>(b) * p.Hq + h * G + g;
@@ -498,58 +569,10 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
             if (p.out_f32) p.out_f32[hq * D + d] = o32;
             if (d == 0 && p.lse) p.lse[hq] = lse_nat;
           } else {
-            const int64_t slot = ((static_cast<int64_t>(xa.seq & 1u) * xa.R + xa.rank) * xa.N + hq) * XW;
-            for (int r = 0; r < xa.R; ++r) {
-              float* dst = xa.peers.buf[r] + slot;
-              dst[d] = o32;
-              if (d == 0) {
-                dst[D] = lse_nat == -INFINITY ? -INFINITY : lse_nat * LOG2E;
-                dst[D + 1] = lse_nat == -INFINITY ? 0.f : 1.f;
-              }
-            }
+            xchg_store(xa, hq, d, o32, lse_nat);
           }
         }
-        if (xchg) {
-          const int64_t hq0x = static_cast<int64_t>(b) * p.Hq + h * G;
-          __threadfence_system();       // the rows are visible on every GPU before their flags
-          __syncthreads();
-          if (tid < G * xa.R) {
-            const int g = tid / xa.R, r = tid % xa.R;
-            volatile unsigned int* f = xa.peers.flags[r] + static_cast<int64_t>(xa.rank) * xa.N + hq0x + g;
-            *f = xa.seq;
-          }
-          if (tid < G * xa.R) {         // this rank's copy of the flags of its four rows, one per peer
-            const int g = tid / xa.R, r = tid % xa.R;
-            const volatile unsigned int* f = xa.peers.flags[xa.rank] + static_cast<int64_t>(r) * xa.N + hq0x + g;
-            bool got = false;
-            for (uint32_t it = 0; it < (1u << 21); ++it) {
-              if (static_cast<int>(*f - xa.seq) >= 0) { got = true; break; }
-              __nanosleep(100);
-            }
-            if (!got) atomicCAS(&g_status, 0u, 0x510u + r);
-          }
-          __threadfence_system();
-          __syncthreads();
-          const float* mine = xa.peers.buf[xa.rank] + (static_cast<int64_t>(xa.seq & 1u) * xa.R) * xa.N * XW;
-          for (int o = tid; o < G * D; o += TC_THREADS) {
-            const int g = o / D, d = o % D;
-            const int64_t row = hq0x + g;
-            float m = -INFINITY;
-            for (int r = 0; r < xa.R; ++r) m = fmaxf(m, __ldcg(mine + (static_cast<int64_t>(r) * xa.N + row) * XW + D));
-            const float mu = (m == -INFINITY) ? 0.f : m;
-            float l = 0.f, acc2 = 0.f;
-            for (int r = 0; r < xa.R; ++r) {
-              const float* pr = mine + (static_cast<int64_t>(r) * xa.N + row) * XW;
-              const float w = ex2(__ldcg(pr + D) - mu);
-              l += __ldcg(pr + D + 1) * w;
-              acc2 += __ldcg(pr + d) * w;
-            }
-            const float o32 = l > 0.f ? acc2 / l : 0.f;
-            reinterpret_cast<__nv_bfloat16*>(p.out)[row * D + d] = __float2bfloat16(o32);
-            if (p.out_f32) p.out_f32[row * D + d] = o32;
-            if (d == 0 && p.lse) p.lse[row] = l > 0.f ? (m + log2f(l)) * LN2 : -INFINITY;
-          }
-        }
+        if (xchg) xchg_finish<TC_THREADS>(p, xa, b, h, tid);
         if (tid == 0) split_done[b * p.Hkv + h] = 0;
       }
     }

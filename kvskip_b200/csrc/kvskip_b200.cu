@@ -158,31 +158,46 @@ cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 }
 
 // Counters of finished splits for the in-kernel merge: zero at load, put back to zero by the CTA
-// that merges.  Sixteen regions used round-robin by successive launches, so launches that overlap
-// on different streams do not share counters.
+// that merges.  A region of counters belongs to a (device, stream) pair: launches on one stream run
+// one after the other (a dependent launch touches its counters only after griddepcontrol.wait), so
+// they can share a region, and launches on different streams never do.  A kernel captured into a
+// CUDA graph keeps the region of the stream it was captured on.  Regions are handed out on first
+// use and never taken back; a device that has seen more than kMergeRegions streams gets no region
+// for the newcomers (the attention kernels then merge with a second launch, plan reports a limit).
 constexpr int kMergeRegion = 4096;
-constexpr int kMergeRegions = 16;
+constexpr int kMergeRegions = 64;
+constexpr int kMaxDevices = 64;
 __device__ int g_split_done[kMergeRegion * kMergeRegions];
-std::atomic<unsigned> g_merge_seq{0};
 std::atomic<int> g_half_cta{1};
+// Polls (of about 100 ns) a kernel spends on a peer's flag before it gives up: about 2 s by default.
+// The "spin_limit" option lowers it, so that a missing peer is reported in microseconds (tests of the
+// failure path; a host that prefers a fast error over a long wait).
+constexpr int kDefaultSpin = 1 << 21;
+std::atomic<int> g_xchg_spin{kDefaultSpin};
 
-int split_done_region(int units, int** out) {
+int split_done_region(int units, cudaStream_t stream, int** out) {
   static std::mutex mu;
-  static int* base[64] = {};
+  static int* base[kMaxDevices] = {};
+  static cudaStream_t owner[kMaxDevices][kMergeRegions];
+  static int used[kMaxDevices] = {};
   *out = nullptr;
   if (units > kMergeRegion) return KVSKIP_OK;          // too many (batch, head) pairs: separate merge launch
   int dev = 0;
   KVB_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return KVSKIP_OK;
-  {
-    std::lock_guard<std::mutex> lock(mu);
-    if (!base[dev]) {
-      void* ptr = nullptr;
-      KVB_CUDA(cudaGetSymbolAddress(&ptr, g_split_done));
-      base[dev] = static_cast<int*>(ptr);
-    }
+  if (dev < 0 || dev >= kMaxDevices) return KVSKIP_OK;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!base[dev]) {
+    void* ptr = nullptr;
+    KVB_CUDA(cudaGetSymbolAddress(&ptr, g_split_done));
+    base[dev] = static_cast<int*>(ptr);
   }
-  *out = base[dev] + (g_merge_seq.fetch_add(1, std::memory_order_relaxed) % kMergeRegions) * kMergeRegion;
+  int r = 0;
+  while (r < used[dev] && owner[dev][r] != stream) ++r;
+  if (r == used[dev]) {
+    if (used[dev] == kMergeRegions) return KVSKIP_OK;
+    owner[dev][used[dev]++] = stream;
+  }
+  *out = base[dev] + r * kMergeRegion;
   return KVSKIP_OK;
 }
 
@@ -227,7 +242,7 @@ int launch_tc(const kvskip_params& p, const DynArgs& dyn, cudaStream_t stream) {
   const int64_t total = static_cast<int64_t>(p.num_splits) * p.Hkv * p.B;
   int* done = nullptr;
   if (LOAD_V && p.num_splits > 1)
-    if (int rc = split_done_region(p.B * p.Hkv, &done)) return rc;
+    if (int rc = split_done_region(p.B * p.Hkv, stream, &done)) return rc;
   if (dyn.xa.R > 0 && (!LOAD_V || done == nullptr || 2 * p.B * p.Hkv > sms))
     return fail(KVSKIP_E_ARG,
                 "exchange inside the kernel: needs V, num_splits > 1 and at most half as many (batch, kv head) "
@@ -306,7 +321,7 @@ int launch_vskip1_tc(const kvskip_params& p, const DynArgs& dyn, cudaStream_t st
     return rc;
   int* done = nullptr;
   if (p.num_splits > 1)
-    if (int rc = split_done_region(p.B * p.Hkv, &done)) return rc;
+    if (int rc = split_done_region(p.B * p.Hkv, stream, &done)) return rc;
   KVB_CUDA(launch_overlapped(kernel, dim3(p.num_splits, p.Hkv, p.B), dim3(kvb::TC_THREADS),
                              kvb::Vs1TcCfg::kSmemBytes, stream, p, maps, done, dyn.pages, dyn.max_pages));
   if (p.num_splits > 1 && done == nullptr) {
@@ -327,7 +342,7 @@ int launch_pv_tc(const kvskip_params& p, cudaStream_t stream) {
   maps.k = maps.v;
   int* done = nullptr;
   if (p.num_splits > 1)
-    if (int rc = split_done_region(p.B * p.Hkv, &done)) return rc;
+    if (int rc = split_done_region(p.B * p.Hkv, stream, &done)) return rc;
   KVB_CUDA(launch_overlapped(kernel, dim3(p.num_splits, p.Hkv, p.B), dim3(kvb::TC_THREADS), kvb::PvTcCfg::kSmemBytes,
                              stream, p, maps, done));
   if (p.num_splits > 1 && done == nullptr) {
@@ -427,6 +442,7 @@ int kvskip_launch_decode_xchg(const kvskip_params* p, int D, int G, int stages, 
   dyn.xa.R = R;
   dyn.xa.N = static_cast<long long>(p->B) * p->Hq;
   dyn.xa.seq = seq;
+  dyn.xa.spin = static_cast<unsigned int>(g_xchg_spin.load(std::memory_order_relaxed));
   if (D != 128 || g_decode_path.load(std::memory_order_relaxed) == 1)
     return fail(KVSKIP_E_ARG, "decode_xchg: tensor-core path only (D = 128, decode_path != 1)");
   return decode_impl(p, D, G, stages, masked, stats, 1, dyn, stream);
@@ -453,7 +469,6 @@ static __device__ __align__(256) float g_noalloc_scratch[KVSKIP_NOALLOC_MAX_FLOA
 namespace {
 // device address of g_noalloc_scratch per device ordinal, looked up once with that device current
 // (in host code the array's name is only a handle for the runtime, not a device address)
-constexpr int kMaxDevices = 64;
 float* g_noalloc_ptr[kMaxDevices] = {};
 std::mutex g_noalloc_mu;
 
@@ -511,6 +526,11 @@ int kvskip_set_option(const char* name, int value) {
     g_use_pdl.store(value ? 1 : 0, std::memory_order_relaxed);
     return KVSKIP_OK;
   }
+  if (!std::strcmp(name, "spin_limit")) {   // 0 restores the default
+    if (value < 0) return fail(KVSKIP_E_ARG, "spin_limit: polls >= 1, or 0 for the default");
+    g_xchg_spin.store(value ? value : kDefaultSpin, std::memory_order_relaxed);
+    return KVSKIP_OK;
+  }
   return fail(KVSKIP_E_ARG, "unknown option %s", name);
 }
 
@@ -518,6 +538,7 @@ int kvskip_get_option(const char* name) {
   if (name && !std::strcmp(name, "decode_path")) return g_decode_path.load(std::memory_order_relaxed);
   if (name && !std::strcmp(name, "pdl")) return g_use_pdl.load(std::memory_order_relaxed);
   if (name && !std::strcmp(name, "half_cta")) return g_half_cta.load(std::memory_order_relaxed);
+  if (name && !std::strcmp(name, "spin_limit")) return g_xchg_spin.load(std::memory_order_relaxed);
   return fail(KVSKIP_E_ARG, "unknown option");
 }
 
@@ -566,8 +587,10 @@ int plan_impl(const kvskip_plan_params* p, const DynArgs& dyn, void* stream) {
     return fail(KVSKIP_E_ARG, "plan: missing state tensor");
   if (p->B > 65535 || p->Hkv > 65535) return fail(KVSKIP_E_LIMIT, "B and Hkv are grid dims: at most 65535");
   int* done = nullptr;
-  if (int rc = split_done_region(p->B * p->Hkv, &done)) return rc;
-  if (!done) return fail(KVSKIP_E_LIMIT, "plan: more than %d (batch, kv head) pairs per call", kMergeRegion);
+  if (int rc = split_done_region(p->B * p->Hkv, static_cast<cudaStream_t>(stream), &done)) return rc;
+  if (!done)
+    return fail(KVSKIP_E_LIMIT, "plan: more than %d (batch, kv head) pairs per call, or more than %d streams used on this device",
+                kMergeRegion, kMergeRegions);
   const int chunks = (nb + kvb::PL_CHUNK - 1) / kvb::PL_CHUNK;
   const int smem = (nb + 15) & ~15;   // attended flags of one head
   if (smem > 200 * 1024) return fail(KVSKIP_E_LIMIT, "plan: more than %d blocks", 200 * 1024);
@@ -691,12 +714,29 @@ int kvskip_launch_exchange_merge(const float* out_f32, const float* lse, float* 
     peers.flags[r] = peer_flags[r];
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (D != 128 && D != 64) return fail(KVSKIP_E_ARG, "kvskip: unsupported head dim");
+  {
+    // One waiting CTA per row: every CTA of the grid must be resident at once, or a CTA that waits
+    // for a peer's row could keep that peer's CTA for another row of this rank off the GPU.
+    int dev = 0, sms = 0, per_sm = 0;
+    KVB_CUDA(cudaGetDevice(&dev));
+    KVB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (D == 128)
+      KVB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kvb::exchange_merge_kernel<128>, 128, 0));
+    else
+      KVB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kvb::exchange_merge_kernel<64>, 64, 0));
+    if (N > static_cast<int64_t>(per_sm) * sms)
+      return fail(KVSKIP_E_LIMIT, "exchange_merge: %lld rows exceed the %d CTAs this GPU keeps resident at once",
+                  static_cast<long long>(N), per_sm * sms);
+  }
   if (D == 128)
-    kvb::exchange_merge_kernel<128><<<static_cast<unsigned>(N), 128, 0, s>>>(out_f32, lse, peers, rank, R, N, seq, out,
-                                                                             res_f32, res_lse);
+    kvb::exchange_merge_kernel<128><<<static_cast<unsigned>(N), 128, 0, s>>>(
+        out_f32, lse, peers, rank, R, N, seq, static_cast<unsigned int>(g_xchg_spin.load(std::memory_order_relaxed)), out,
+        res_f32, res_lse);
   else if (D == 64)
-    kvb::exchange_merge_kernel<64><<<static_cast<unsigned>(N), 64, 0, s>>>(out_f32, lse, peers, rank, R, N, seq, out,
-                                                                           res_f32, res_lse);
+    kvb::exchange_merge_kernel<64><<<static_cast<unsigned>(N), 64, 0, s>>>(
+        out_f32, lse, peers, rank, R, N, seq, static_cast<unsigned int>(g_xchg_spin.load(std::memory_order_relaxed)), out,
+        res_f32, res_lse);
   else
     return fail(KVSKIP_E_ARG, "kvskip: unsupported head dim");
   KVB_CUDA(cudaGetLastError());
@@ -772,7 +812,9 @@ int kvskip_device_status(void* stream, unsigned int* status) {
   if (!status) return fail(KVSKIP_E_ARG, "null status pointer");
   KVB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   KVB_CUDA(cudaMemcpyFromSymbol(status, kvb::g_status, sizeof(unsigned int)));
-  if (*status) {   // a kernel gave up mid-way: clear the word and the split counters it may have left
+  if (*status) {   // a kernel gave up mid-way: wait for everything on the device, then clear the word and the
+                   // split counters the kernel may have left behind (on every stream's region)
+    KVB_CUDA(cudaDeviceSynchronize());
     const unsigned int zero = 0;
     KVB_CUDA(cudaMemcpyToSymbol(kvb::g_status, &zero, sizeof(zero)));
     void* ptr = nullptr;

@@ -194,6 +194,7 @@ vskip1_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
           *reinterpret_cast<uint4*>(vb + o) = make_uint4(0u, 0u, 0u, 0u);
           *reinterpret_cast<uint4*>(vb + TC_HALF_BYTES + o) = make_uint4(0u, 0u, 0u, 0u);
         }
+        fence_proxy_async_smem();   // every writing lane: ordered before the next bulk load into this buffer
         __syncwarp();
       }
       if (__any_sync(0xffffffffu, pend_alpha[0] != 1.f || pend_alpha[1] != 1.f)) {

@@ -34,17 +34,17 @@ _EXT = None
 def ext():
     """The compiled extension module (decode, vskip1, pv, plan, update, read_bw, ...).
 
-    Loaded from the in-tree `_kvskip_ext.so`; if it is missing and a CUDA toolkit is present it is
-    built once (`python -m kvskip_b200.build`).  Raises RuntimeError if it cannot be had: nothing
+    Loaded from the in-tree `_kvskip_ext.so` (from the directory $KVSKIP_BUILD when that is set);
+    if it is missing and a CUDA toolkit is present it is built once (`python -m kvskip_b200.build`).  Raises RuntimeError if it cannot be had: nothing
     in this package computes without it."""
     global _EXT
     if _EXT is None:
-        so = HERE / "_kvskip_ext.so"
-        if not so.exists() or not (HERE / "libkvskip_b200.so").exists():
+        from . import build as _build
+        so = _build.EXT
+        if not so.exists() or not _build.LIB.exists():
             if os.environ.get("KVSKIP_NO_BUILD"):
                 raise RuntimeError(f"kvskip_b200: {so} is missing and KVSKIP_NO_BUILD is set")
             try:
-                from . import build as _build
                 _build.build_all(verbose=bool(os.environ.get("KVSKIP_VERBOSE")))
             except Exception as e:  # noqa: BLE001
                 raise RuntimeError("kvskip_b200: the CUDA extension is not built and building it failed "
@@ -57,6 +57,32 @@ def ext():
             raise RuntimeError(f"kvskip_b200: cannot load {so}: {e}") from e
         _EXT = mod
     return _EXT
+
+
+class DeviceWaitError(RuntimeError):
+    """A bounded wait inside a kernel ran out (a load that never arrived, a peer GPU that never
+    flagged its rows).  `code` is the kernel's status word: 0x2xx / 0x3xx waits on this GPU's own
+    loads, 0x500 + r / 0x510 + r the exchange with rank r of a sequence-sharded step."""
+
+    def __init__(self, code: int, what: str):
+        super().__init__(f"{what}: a device-side wait gave up (status word {code:#x}); the results of that launch "
+                         "are incomplete")
+        self.code = code
+
+
+def check_status(what: str = "kvskip") -> None:
+    """Synchronise the current stream, read the kernels' status word and raise DeviceWaitError if a
+    wait timed out (the word is cleared).  Blocks the host: call it where a synchronisation is
+    acceptable (end of a decode step, after a failed exchange), or set KVSKIP_CHECK_STATUS=1 to
+    have every front-end call do it (debugging)."""
+    code = int(ext().device_status())
+    if code:
+        raise DeviceWaitError(code, what)
+
+
+def _auto_check(what: str) -> None:
+    if os.environ.get("KVSKIP_CHECK_STATUS", "") not in ("", "0"):
+        check_status(what)
 
 
 def num_sms() -> int:
@@ -150,6 +176,7 @@ def decode(q, k, v, scale: float, *, plan: Plan | None = None, stats: bool = Fal
     out, lse, bmax, bsum, o32, pbuf = ext().decode(q, k, v, float(scale), bi, bc, stats, load_v,
                                                    int(num_splits), int(stages), out_f32, write_p, t_dev,
                                                    page_table, int(seq_len or 0))
+    _auto_check("decode")
     res = {"out": out if load_v else None, "lse": lse, "num_splits": num_splits}
     if stats:
         res["blk_max"], res["blk_sum"] = bmax, bsum
@@ -252,6 +279,7 @@ def vskip_one_pass(q, k, v, scale: float, tau: float = 1e-4, local: int = 2, num
         num_splits = num_splits_for(B * Hkv, nb)
     out, lse, o32, cnt = ext().vskip1(q, k, v, float(scale), float(tau), int(local), int(num_splits),
                                       out_f32, count, lse_prev, page_table, int(seq_len or 0))
+    _auto_check("vskip_one_pass")
     res = {"out": out, "lse": lse, "num_splits": num_splits}
     if out_f32:
         res["out_f32"] = o32

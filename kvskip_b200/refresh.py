@@ -80,11 +80,80 @@ def centroid_scores(q32, csum, T, scale):
     return torch.einsum("bkgd,bknd->bkgn", q32.view(B, Hkv, Hq // Hkv, D), cen).reshape(B, Hq, nb) * scale
 
 
+class PlannerState:
+    """The device planner's tensors of one layer, carved out of ONE allocation.
+
+    Names, shapes and dtypes are the ones the kernels take (and the reference's fused driver
+    keeps, src/kvskip_attn.py:420-432), so the views can be handed to either implementation; the
+    storage is this package's: a single byte arena per layer with 256-byte aligned segments, sized
+    for `nbc` blocks of capacity.  One allocation per layer keeps a long decode loop free of
+    allocator traffic, makes a layer's planner state one tensor to save or move, and growing it is
+    one new arena plus a copy of the used prefix of the per-block segments."""
+
+    # name -> (dtype, shape as a function of the geometry, value of unused block capacity or None)
+    LAYOUT = (
+        ("csum", torch.float32, lambda g: (g.B, g.Hkv, g.nbc, g.D), 0.0),
+        ("lse_ref", torch.float32, lambda g: (g.B, g.Hq, g.nbc), float("-inf")),
+        ("cs_ref", torch.float32, lambda g: (g.B, g.Hq, g.nbc), 0.0),
+        ("cs_now", torch.float32, lambda g: (g.B, g.Hq, g.nbc), 0.0),
+        ("block_idx", torch.int32, lambda g: (g.B, g.Hkv, g.nbc), 0),
+        ("keep", torch.uint8, lambda g: (g.B, g.Hkv, g.nbc), 0),
+        ("lse_att", torch.float32, lambda g: (g.B, g.Hq), None),
+        ("calib", torch.float32, lambda g: (g.B, g.Hkv), None),
+        ("est", torch.float32, lambda g: (g.B, g.Hkv), None),
+        ("age", torch.int32, lambda g: (g.B, g.Hkv), None),
+        ("block_cnt", torch.int32, lambda g: (g.B, g.Hkv), None),
+        ("flags", torch.int32, lambda g: (g.Hkv,), None),
+        ("aix", torch.uint8, lambda g: (g.B, g.Hkv), None),
+        ("trig", torch.uint8, lambda g: (g.B, g.Hkv), None),
+    )
+
+    def __init__(self, B, Hq, Hkv, D, nbc, device, scale=1.0):
+        self.B, self.Hq, self.Hkv, self.D, self.nbc, self.scale = B, Hq, Hkv, D, int(nbc), float(scale)
+        offsets, total = [], 0
+        for _, dtype, shape, _ in self.LAYOUT:
+            n = math.prod(shape(self)) * torch.empty((), dtype=dtype).element_size()
+            offsets.append((total, n))
+            total += (n + 255) & ~255
+        self.arena = torch.zeros(total, dtype=torch.uint8, device=device)
+        self.views = {}
+        for (name, dtype, shape, fill), (off, n) in zip(self.LAYOUT, offsets):
+            view = self.arena[off:off + n].view(dtype).view(shape(self))
+            if fill:                       # a zero fill is already there
+                view.fill_(fill)
+            self.views[name] = view
+
+    # dictionary-style access under the reference's key names ("NBC" and "scale" included)
+    def __getitem__(self, key):
+        if key == "NBC":
+            return self.nbc
+        if key == "scale":
+            return self.scale
+        return self.views[key]
+
+    def __contains__(self, key):
+        return key in self.views or key in ("NBC", "scale")
+
+    def load_blocks(self, name, x):
+        """Write x into the first x.shape[2] blocks of a per-block tensor."""
+        self.views[name][:, :, :x.shape[2]] = x
+
+    def grown(self, nbc):
+        """A state with capacity for nbc blocks holding this one's contents."""
+        new = PlannerState(self.B, self.Hq, self.Hkv, self.D, nbc, self.arena.device, self.scale)
+        for name, _, _, fill in self.LAYOUT:
+            if fill is None:
+                new.views[name].copy_(self.views[name])
+            else:
+                new.views[name][:, :, :self.nbc] = self.views[name]
+        return new
+
+
 @dataclass
 class RefreshLayer:
     cfg: RefreshConfig
     ops: object = None
-    state: dict | None = None
+    state: PlannerState | None = None
     t: int = 0
     last: dict = field(default_factory=dict)     # tensors of the latest step (block lists, stats), for inspection
 
@@ -107,46 +176,23 @@ class RefreshLayer:
         cs = centroid_scores(q.float(), csum, T, scale)
         always = K.always_keep(nb, cfg.local, dev)
         lse_att = logw.masked_fill(~(keep | always).repeat_interleave(G, dim=1), float("-inf")).logsumexp(-1)
-        NBC = nb + cfg.margin
-
-        def padded(x, fill, dtype):
-            out = torch.full((*x.shape[:2], NBC, *x.shape[3:]), fill, dtype=dtype, device=dev)
-            out[:, :, :x.shape[2]] = x
-            return out
-
-        flags = torch.zeros(Hkv, dtype=torch.int32, device=dev)
+        st = PlannerState(B, Hq, Hkv, D, nb + cfg.margin, dev, scale)
+        st.load_blocks("keep", keep)
+        st.load_blocks("lse_ref", logw)
+        st.load_blocks("cs_ref", cs)
+        st.load_blocks("csum", csum)
+        st["lse_att"].copy_(lse_att)
         for h in cfg.dense_heads:
-            flags[h] = 1
+            st["flags"][h] = 1
         for h in cfg.index_heads:
-            flags[h] = 4 if cfg.index_union else 2
-        self.state = dict(
-            NBC=NBC, flags=flags, scale=float(scale),
-            keep=padded(keep, 0, torch.uint8),
-            lse_ref=padded(logw, float("-inf"), torch.float32),
-            cs_ref=padded(cs, 0.0, torch.float32),
-            csum=padded(csum, 0.0, torch.float32),
-            lse_att=lse_att.float().contiguous(),
-            age=torch.zeros(B, Hkv, dtype=torch.int32, device=dev),
-            calib=torch.zeros(B, Hkv, dtype=torch.float32, device=dev),
-            est=torch.zeros(B, Hkv, dtype=torch.float32, device=dev),
-            aix=torch.zeros(B, Hkv, dtype=torch.uint8, device=dev),
-            cs_now=torch.zeros(B, Hq, NBC, dtype=torch.float32, device=dev),
-            trig=torch.zeros(B, Hkv, dtype=torch.uint8, device=dev),
-            block_idx=torch.zeros(B, Hkv, NBC, dtype=torch.int32, device=dev),
-            block_cnt=torch.zeros(B, Hkv, dtype=torch.int32, device=dev))
+            st["flags"][h] = 4 if cfg.index_union else 2
+        self.state = st
         self.t = 0
         self.last = {"blk_max": r["blk_max"], "blk_sum": r["blk_sum"], "lse": r["lse"], "first": True}
         return r["out"]
 
     def _grow(self, NBC):
-        fills = dict(keep=0, lse_ref=float("-inf"), cs_ref=0.0, csum=0.0, cs_now=0.0, block_idx=0)
-        s = self.state
-        for name, fill in fills.items():
-            x = s[name]
-            out = torch.full((*x.shape[:2], NBC, *x.shape[3:]), fill, dtype=x.dtype, device=x.device)
-            out[:, :, :x.shape[2]] = x
-            s[name] = out
-        s["NBC"] = NBC
+        self.state = self.state.grown(NBC)
 
     def max_age_now(self) -> int:
         cfg = self.cfg
@@ -193,11 +239,12 @@ class RefreshLayer:
                 raise ValueError("the first step of a layer builds the state on the host: run it with views of "
                                  "the current length and without t_dev")
             return self._init(q, k, v, scale)
-        cfg, s = self.cfg, self.state
+        cfg = self.cfg
         B, T = q.shape[0], (int(seq_len) if paged else k.shape[2])
         nb = math.ceil(T / BLOCK)
-        if nb > s["NBC"]:
+        if nb > self.state["NBC"]:
             self._grow(nb + cfg.margin)
+        s = self.state
         idx = None
         if self.uses_index():
             if idx_blocks is None:

@@ -53,6 +53,11 @@ def block_range(nb: int, rank: int, world: int):
     return lo, min(nb, lo + per)
 
 
+class ExchangeError(RuntimeError):
+    """The exchange step of a sequence-sharded decode did not complete: a rank never joined the
+    collective (its process died or fell behind), or the process group timed out."""
+
+
 class CudaBackend:
     """The product backend: the compiled extension (there is no CPU path in this package; tests of
     the host logic pass a stand-in with the same two callables)."""
@@ -130,6 +135,12 @@ class PeerExchange:
         torch.cuda.synchronize(device)
         dist.barrier(group)                       # every rank's flags are zero before anyone writes
 
+    def check(self) -> None:
+        """Synchronise and raise kvskip.DeviceWaitError if a wait for a peer's rows ran out in one
+        of the exchange launches since the last check (the peer is `code & 0xf`).  The waits are
+        bounded (`spin_limit` option), so a peer that never arrives costs a delay, not a hang."""
+        K.check_status("sequence-sharded exchange")
+
     def decode(self, q, k_local, v_local, scale, plan=None, num_splits=None):
         """Local attention + exchange + merge in one launch (kvskip_launch_decode_xchg).  Needs at
         least two splits and at most half as many (batch, kv head) pairs as SMs."""
@@ -169,7 +180,11 @@ def decode_sequence_sharded(q, k_local, v_local, scale, plan=None, group=None, n
     part = local_partial(q, k_local, v_local, scale, plan=plan, num_splits=num_splits, backend=backend)
     world = dist.get_world_size(group)
     parts = torch.empty(world * part.shape[0], part.shape[1], dtype=part.dtype, device=part.device)
-    dist.all_gather_into_tensor(parts, part, group=group)       # rank-major concatenation
+    try:
+        dist.all_gather_into_tensor(parts, part, group=group)   # rank-major concatenation
+    except RuntimeError as e:   # a rank that never called the collective ends it with the group's timeout
+        raise ExchangeError(f"rank {dist.get_rank(group)} of {world}: the all-gather of the per-shard partials "
+                            f"failed ({str(e).splitlines()[0][:200]})") from e
     return merge_partials(parts.view(world, *part.shape), B, Hq, backend=backend)
 
 

@@ -26,7 +26,8 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
-REF = Path(os.environ.get("KVSKIP_REFERENCE", "/root/reference"))
+# the reference checkout: $KVSKIP_REFERENCE, else a directory `reference` beside this repository
+REF = Path(os.environ.get("KVSKIP_REFERENCE") or ROOT.parent / "reference")
 
 sys.path.insert(0, str(ROOT))
 from kvskip_b200 import synth  # noqa: E402

@@ -55,8 +55,9 @@ def test_ctypes_structs_match_header_sizes():
 def test_front_end_fails_loudly_without_extension(monkeypatch, tmp_path):
     """No CPU fallback: a missing extension is an error, not a slower path."""
     from kvskip_b200 import kvskip as K
+    from kvskip_b200 import build
     monkeypatch.setattr(K, "_EXT", None)
-    monkeypatch.setattr(K, "HERE", tmp_path)
+    monkeypatch.setattr(build, "EXT", tmp_path / "_kvskip_ext.so")
     monkeypatch.setenv("KVSKIP_NO_BUILD", "1")
     with pytest.raises(RuntimeError):
         K.ext()

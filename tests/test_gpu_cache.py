@@ -8,6 +8,7 @@ import math
 import pytest
 import torch
 
+import oracle
 from kvskip_b200 import kvskip as K
 from kvskip_b200 import synth
 from kvskip_b200.cache import GrowingKV, PagedKV
@@ -79,6 +80,15 @@ def test_paged_dense_and_masked_match_contiguous(T):
         b = K.decode(q, pg.k, pg.v, scale, plan=plan, stats=True, out_f32=True, page_table=pg.table, seq_len=T)
         assert torch.equal(a["out_f32"], b["out_f32"]) and torch.equal(a["lse"], b["lse"])
         assert torch.equal(a["blk_max"], b["blk_max"]) and torch.equal(a["blk_sum"], b["blk_sum"])
+        # the paged launch against the CPU oracle on the gathered sequence
+        bi, bc = synth.keep_to_plan(keep)
+        ref = oracle.decode_f64(q.cpu(), gk.cpu(), gv.cpu(), scale, bi, bc)
+        assert float((b["out_f32"].double().cpu() - ref["out"]).norm() / ref["out"].norm()) < 5e-5
+        assert torch.allclose(b["lse"].double().cpu(), ref["lse"], rtol=0, atol=2e-4)
+    ref = oracle.decode_f64(q.cpu(), gk.cpu(), gv.cpu(), scale)
+    paged = K.decode(q, pg.k, pg.v, scale, out_f32=True, page_table=pg.table, seq_len=T)
+    assert float((paged["out_f32"].double().cpu() - ref["out"]).norm() / ref["out"].norm()) < 5e-5
+    assert float((paged["out"].double().cpu() - ref["out"]).norm() / ref["out"].norm()) < 2e-3
     # with the length on the device as well
     t_dev = torch.tensor([T], dtype=torch.int32, device=DEV)
     c = K.decode(q, pg.k, pg.v, scale, out_f32=True, num_splits=3, page_table=pg.table, seq_len=cap, t_dev=t_dev)

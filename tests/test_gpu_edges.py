@@ -85,15 +85,24 @@ def test_unsynced_plan_with_one_full_head():
 
 
 def test_long_context_planner_beyond_3072_blocks(path):
-    """256k tokens = 4096 blocks: one planner step against the CPU restatement, and the attention
-    pass over plan's list against the oracle."""
+    """256k tokens = 4096 blocks (beyond the reference's 3072-block limit): three planner steps, the
+    attention pass over plan's list against the oracle, and the third step's plan and update against
+    the CPU restatement run from a snapshot of the state before that step: refresh decision, list
+    length and list equal wherever the decision does not sit on its threshold, the new stored set
+    equal wherever the kept mass does not sit on the level (rows this long take the shared-memory
+    form of the top-p bisection)."""
     if path == "exact":
         pytest.skip("the planner kernels do not depend on the attention path")
     T0 = 4096 * 64 - 40
     walk = synth.planner_walk_device(77, T0, 3, DEV)
-    layer = RefreshLayer(RefreshConfig())
+    cfg = RefreshConfig(dense_heads=(6,))             # one head refreshes on every step: update's heavy part runs
+    layer = RefreshLayer(cfg)
+    names = ("csum", "lse_ref", "cs_ref", "keep", "lse_att", "age", "flags", "cs_now", "trig", "block_idx",
+             "block_cnt", "est")
     for t in range(3):
         Tt = T0 + t + 1
+        if t == 2:
+            snap = {n: layer.state[n].cpu().clone() for n in names}
         out = layer.step(walk.q[t], walk.k[:, :, :Tt], walk.v[:, :, :Tt], walk.scale)
     nb = math.ceil(Tt / 64)
     s = layer.state
@@ -101,7 +110,36 @@ def test_long_context_planner_beyond_3072_blocks(path):
     mask = layer.read_mask(nb).cpu()
     assert mask[..., 0].all() and mask[..., -2:].all()
     bi, bc = synth.keep_to_plan(mask)
-    ref = oracle.decode_f64(walk.q[2].cpu(), walk.k[:, :, :Tt].cpu(), walk.v[:, :, :Tt].cpu(), walk.scale, bi, bc)
+    qh, kh, vh = walk.q[2].cpu(), walk.k[:, :, :Tt].cpu(), walk.v[:, :, :Tt].cpu()
+    ref = oracle.decode_f64(qh, kh, vh, walk.scale, bi, bc)
     assert rel_err(out, ref["out"]) < TOL_BF16
     # plan on the CPU restatement from the same pre-step state reproduces the decision and the list
+    margin = torch.zeros(1, 8)
+    c = snap
+    oracle.plan(qh, kh, c["csum"], c["lse_ref"], c["cs_ref"], c["keep"], c["lse_att"], c["age"], c["flags"],
+                c["cs_now"], c["trig"], c["block_idx"], c["block_cnt"], walk.scale, cfg.delta, cfg.max_age, cfg.local,
+                True, None, None, c["est"], False, 0, None, dec_margin=margin)
+    safe = ~(margin.abs() < 1e-4)
+    assert safe.float().mean() >= 0.75
+    assert bool(c["trig"][0, 6]) and int(c["block_cnt"][0, 6]) == nb
+    assert torch.equal(s["trig"].cpu()[safe], c["trig"][safe])
+    assert torch.equal(s["block_cnt"].cpu()[safe], c["block_cnt"][safe])
+    for h in range(8):
+        if safe[0, h]:
+            n = int(c["block_cnt"][0, h])
+            assert torch.equal(s["block_idx"][0, h, :n].cpu(), c["block_idx"][0, h, :n]), h
+    assert torch.allclose(s["cs_now"].cpu()[..., :nb], c["cs_now"][..., :nb], rtol=1e-5, atol=1e-6)
+    assert torch.allclose(s["est"].cpu(), c["est"], rtol=1e-4, atol=1e-6)
+    # update on the CPU restatement from the GPU's statistics of that pass: the new stored set
+    for n in ("trig", "cs_now", "est"):
+        c[n] = s[n].cpu().clone()
+    tm = torch.zeros(1, 32)
+    oracle.update(layer.last["blk_max"].cpu(), layer.last["blk_sum"].cpu(), c["trig"], c["cs_now"], c["keep"],
+                  c["lse_ref"], c["cs_ref"], c["lse_att"], Tt, cfg.level, cfg.local, c["flags"], None, c["est"], None,
+                  0.0, False, 0, None, 0.0, topp_margin=tm)
+    ok = ~(tm < 2e-6).view(1, 8, 4).any(-1)
+    assert ok.float().mean() >= 0.75 and bool(c["trig"][0, 6])
+    assert torch.equal(s["keep"].cpu()[ok], c["keep"][ok])
+    okq = ok.repeat_interleave(4, dim=1)
+    assert torch.allclose(s["lse_att"].cpu()[okq], c["lse_att"][okq], rtol=1e-5, atol=1e-5)
     assert K.ext().device_status() == 0

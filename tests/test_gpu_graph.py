@@ -9,6 +9,7 @@ import math
 import pytest
 import torch
 
+import oracle
 from kvskip_b200 import kvskip as K
 from kvskip_b200 import synth
 from kvskip_b200.graph import StepGraph
@@ -38,6 +39,14 @@ def test_dense_with_device_length_matches_by_value(T, splits):
     assert torch.equal(a["blk_max"], b["blk_max"][..., :nb]) and torch.equal(a["blk_sum"], b["blk_sum"][..., :nb])
     assert (b["blk_max"][..., nb:] == float("-inf")).all() and (b["blk_sum"][..., nb:] == 0).all()
     assert torch.isfinite(b["out_f32"]).all()
+    if splits == 4 and T in (65, 1000, 1500):
+        # and against the CPU oracle directly (double precision, the first T tokens only)
+        ref = oracle.decode_f64(q.cpu(), k[:, :, :T].cpu(), v[:, :, :T].cpu(), scale, stats=True)
+        err = float((b["out_f32"].double().cpu() - ref["out"]).norm() / ref["out"].norm())
+        assert err < 5e-5, err
+        assert float((b["out"].double().cpu() - ref["out"]).norm() / ref["out"].norm()) < 2e-3
+        assert torch.allclose(b["lse"].double().cpu(), ref["lse"], rtol=0, atol=2e-4)
+        assert torch.allclose(b["blk_max"][..., :nb].double().cpu(), ref["blk_max"], rtol=0, atol=2e-5)
     # the plain dense kernel (no statistics) too
     c = K.decode(q, k, v, scale, out_f32=True, num_splits=splits, t_dev=t_dev)
     d = K.decode(q, k[:, :, :T], v[:, :, :T], scale, out_f32=True, num_splits=splits)
@@ -65,6 +74,13 @@ def test_masked_with_device_length_matches_by_value(T):
         assert torch.equal(a["out_f32"], b["out_f32"]) and torch.equal(a["lse"], b["lse"])
         assert torch.equal(a["blk_max"], b["blk_max"][..., :nb]) and torch.equal(a["blk_sum"], b["blk_sum"][..., :nb])
         assert (b["blk_max"][..., nb:] == float("-inf")).all() and (b["blk_sum"][..., nb:] == 0).all()
+    # the device-length launch against the CPU oracle over the same block lists
+    bi, bc = synth.keep_to_plan(keep)
+    ref = oracle.decode_f64(q.cpu(), k[:, :, :T].cpu(), v[:, :, :T].cpu(), scale, bi, bc)
+    live = bc.repeat_interleave(4, dim=1) > 0
+    err = float((b["out_f32"].double().cpu() - ref["out"])[live].norm() / ref["out"][live].norm())
+    assert err < 5e-5, err
+    assert torch.allclose(b["lse"].double().cpu()[live], ref["lse"][live], rtol=0, atol=2e-4)
 
 
 def test_exact_path_refuses_device_length():

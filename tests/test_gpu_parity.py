@@ -261,11 +261,15 @@ PLAN_OUT = ("csum", "age", "cs_now", "trig", "block_idx", "block_cnt", "est")
 UPD_OUT = ("keep", "lse_ref", "cs_ref", "lse_att", "calib", "aix")
 
 
-@pytest.mark.parametrize("T,kind,calib_on", [(4096, 2, True), (4137, 0, True), (8192 + 3, 1, False), (199, 2, True)])
-def test_plan_update_single_step_vs_oracle(T, kind, calib_on):
+@pytest.mark.parametrize("T,kind,calib_on,B", [(4096, 2, True, 2), (4137, 0, True, 2), (8192 + 3, 1, False, 2),
+                                               (199, 2, True, 2), (32768 + 70, 2, True, 1), (64000 + 9, 1, True, 1),
+                                               (80000, 2, True, 1), (96000 + 5, 0, True, 1), (128000 - 3, 2, True, 1)])
+def test_plan_update_single_step_vs_oracle(T, kind, calib_on, B, path):
     """One plan and one update call on random state: integer outputs identical to the CPU
-    restatement, float outputs equal up to the GPU's approximate exp/log."""
-    B = 2
+    restatement, float outputs equal up to the GPU's approximate exp/log.  The longer rows (514 to
+    2000 blocks) go through every register width of update's top-p bisection."""
+    if T > 10000 and path == "exact":
+        pytest.skip("the planner kernels do not depend on the attention path: long rows once")
     NBC = math.ceil(T / 64) + 64
     nb = math.ceil(T / 64)
     q, k, v, scale, st = _planner_state(40 + kind, B, T, NBC, DEV)
@@ -536,6 +540,114 @@ def test_decode_exchange_four_ranks_emulated(path):
             assert torch.equal(theirs[par, 0], parts[0])
             assert (bufs[r][n_float:].view(torch.int32).view(R, N)[0] == seq).all()
     assert K.ext().device_status() == 0
+
+
+def test_decode_exchange_short_and_empty_lists_emulated(path):
+    """The one-launch sequence-sharded step with block lists, as rank 0 of two, in the regime where
+    the kernel cuts lists into pieces of at least 24 blocks (more CTAs than SMs): a head whose local
+    list is short and a head with no local block at all must still store their rows to the peer,
+    flag them and take part in the merge.  The peer's triples and flags are placed beforehand so
+    that no kernel waits for another; the result equals pack -> merge of the two partials."""
+    if path == "exact":
+        pytest.skip("the exchange inside the kernel exists on the tensor-core path")
+    from kvskip_b200 import shard
+    R, B, splits = 2, 8, 4                                  # 8 x 8 heads x 4 splits = 256 CTAs > 148 SMs
+    q, k, v, scale, keep = synth.sink_body_case(14, T=8192, B=B, stored_frac=0.6)
+    qc, kc, vc = cuda(q, k, v)
+    nb = keep.shape[-1]
+    lo, hi = shard.block_range(nb, 0, R)
+    keep0 = shard.shard_plan(keep, 0, R).clone()
+    keep0[0, 1] = False
+    keep0[0, 1, :5] = True                                  # a short list: one piece
+    keep0[1, 2] = False                                     # nothing to read on this rank
+    keep0[2, 3] = False
+    keep0[2, 3, 7] = True                                   # a single block
+    assert int(keep0.sum(-1).max()) > 24
+    plan0 = K.make_plan(keep0.to(DEV))
+    plan1 = K.make_plan(shard.shard_plan(keep, 1, R).to(DEV))
+    lo1, hi1 = shard.block_range(nb, 1, R)
+    parts = [shard.local_partial(qc, kc[:, :, lo * 64:hi * 64], vc[:, :, lo * 64:hi * 64], scale, plan=plan0,
+                                 num_splits=splits),
+             shard.local_partial(qc, kc[:, :, lo1 * 64:hi1 * 64], vc[:, :, lo1 * 64:hi1 * 64], scale, plan=plan1)]
+    want = shard.merge_partials(torch.stack(parts), B, 32)
+    N, D, W = B * 32, 128, 130
+    n_float = 2 * R * N * W
+    bufs = [torch.zeros(n_float + R * N, dtype=torch.float32, device=DEV) for _ in range(R)]
+    bp = [b_.data_ptr() for b_ in bufs]
+    fp = [b_.data_ptr() + 4 * n_float for b_ in bufs]
+    for seq in (1, 2):
+        par = seq & 1
+        bufs[0][:n_float].view(2, R, N, W)[par, 1] = parts[1]
+        bufs[0][n_float:].view(torch.int32).view(R, N)[1] = seq
+        out, lse, _, _, o32, _ = K.ext().decode_exchange(qc, kc[:, :, lo * 64:hi * 64], vc[:, :, lo * 64:hi * 64], scale,
+                                                         plan0.block_idx, plan0.block_cnt, splits, bp, fp, 0, seq)
+        assert torch.equal(o32.view(B, 32, D), want["out_f32"]) and torch.equal(lse.view(B, 32), want["lse"])
+        # every row of rank 0, the short and the empty heads included, reached the peer with its flag
+        assert torch.equal(bufs[1][:n_float].view(2, R, N, W)[par, 0], parts[0])
+        assert (bufs[1][n_float:].view(torch.int32).view(R, N)[0] == seq).all()
+    assert K.ext().device_status() == 0
+    # against the CPU oracle on the whole sequence with the combined lists
+    full = torch.cat([keep0, shard.shard_plan(keep, 1, R)], dim=-1)
+    bi, bc = synth.keep_to_plan(full)
+    ref = oracle.decode_f64(q, k, v, scale, bi, bc)
+    assert rel_err(want["out_f32"], ref["out"]) < TOL_F32
+
+
+def test_exchange_wait_runs_out_and_reports(path):
+    """Failure detection on the device, without faulting anything: rank 0 of two runs the exchange
+    while nothing ever sets rank 1's flags.  With the poll limit lowered ("spin_limit") the kernel
+    gives up after about a millisecond, sets the status word to 0x500 + peer (0x510 + peer from the
+    attention kernel's own exchange), returns, and the context stays usable: the same call with the
+    peer's rows and flags in place is clean and correct."""
+    if path == "exact":
+        pytest.skip("one path is enough: the exchange kernels do not depend on it")
+    from kvskip_b200 import shard
+    ext = K.ext()
+    R, N, D, W = 2, 64, 128, 130
+    n_float = 2 * R * N * W
+    bufs = [torch.zeros(n_float + R * N, dtype=torch.float32, device=DEV) for _ in range(R)]
+    bp = [b_.data_ptr() for b_ in bufs]
+    fp = [b_.data_ptr() + 4 * n_float for b_ in bufs]
+    torch.manual_seed(3)
+    o = torch.randn(N, D, device=DEV)
+    lse = torch.randn(N, device=DEV)
+    peer = torch.randn(N, W, device=DEV)
+    peer[:, D + 1] = 1.0
+    assert ext.device_status() == 0
+    ext.set_option("spin_limit", 4096)
+    try:
+        assert ext.get_option("spin_limit") == 4096
+        ext.exchange_merge(o, lse, bp, fp, 0, 1)                      # rank 1 never arrives
+        assert ext.device_status() == 0x501
+        assert ext.device_status() == 0                               # reading clears the word
+        with pytest.raises(K.DeviceWaitError) as ei:
+            ext.exchange_merge(o, lse, bp, fp, 0, 2)
+            K.check_status("exchange")
+        assert ei.value.code == 0x501
+        # the peer's rows and flags in place: clean, and equal to pack -> merge
+        seq = 3
+        bufs[0][:n_float].view(2, R, N, W)[seq & 1, 1] = peer
+        bufs[0][n_float:].view(torch.int32).view(R, N)[1] = seq
+        out, o32, l2 = ext.exchange_merge(o, lse, bp, fp, 0, seq)
+        want = ext.merge_packed(torch.stack([ext.pack_partial(o, lse), peer]).contiguous())
+        assert ext.device_status() == 0
+        assert torch.equal(o32, want[1]) and torch.equal(l2, want[2])
+        # the same through the attention kernel's own exchange
+        q, k, v, scale, _ = synth.sink_body_case(15, T=4096, B=2)
+        qc, kc, vc = cuda(q, k, v)
+        ext.decode_exchange(qc, kc, vc, scale, None, None, 4, bp, fp, 0, 4)
+        assert ext.device_status() == 0x511
+        local = shard.local_partial(qc, kc, vc, scale, num_splits=4)
+        seq = 5
+        bufs[0][:n_float].view(2, R, N, W)[seq & 1, 1] = peer
+        bufs[0][n_float:].view(torch.int32).view(R, N)[1] = seq
+        _, lse5, _, _, o5, _ = ext.decode_exchange(qc, kc, vc, scale, None, None, 4, bp, fp, 0, seq)
+        want = ext.merge_packed(torch.stack([local, peer]).contiguous())
+        assert ext.device_status() == 0
+        assert torch.equal(o5.view(N, D), want[1]) and torch.equal(lse5.view(N), want[2])
+    finally:
+        ext.set_option("spin_limit", 0)
+    assert ext.get_option("spin_limit") == 1 << 21
 
 
 def _xchg_rank(rank, world, port, ret):

@@ -76,3 +76,48 @@ def test_sequence_sharded_two_gloo_ranks(T):
     mp.spawn(_rank, args=(2, port, T, ret), nprocs=2, join=True)
     assert ret["dense"] < 1e-6 and ret["masked"] < 1e-6, dict(ret)
     assert ret["dense_lse"] < 1e-5 and ret["masked_lse"] < 1e-5, dict(ret)
+
+
+def _rank_missing_peer(rank, world, port, ret):
+    """Rank 1 never joins the exchange of the step (a host-side failure: it stays alive but skips
+    the collective); rank 0 must get an error from the step instead of waiting for ever."""
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    try:
+        q, k, v, scale, _ = synth.sink_body_case(78, T=512, B=1)
+        lo, hi = shard.block_range(8, rank, world)
+        kl, vl = k[:, :, lo * 64:hi * 64], v[:, :, lo * 64:hi * 64]
+        be = OracleBackend()
+        good = shard.decode_sequence_sharded(q, kl, vl, scale, backend=be)       # a step both ranks take
+        ret[f"good{rank}"] = bool(torch.isfinite(good["out_f32"]).all())
+        if rank == 0:
+            t0 = time.time()
+            try:
+                shard.decode_sequence_sharded(q, kl, vl, scale, backend=be)      # rank 1 is not coming
+                ret["raised"] = "nothing"
+            except shard.ExchangeError as e:
+                ret["raised"] = "ExchangeError"
+                ret["message"] = str(e)
+            ret["waited_s"] = time.time() - t0
+        else:
+            time.sleep(6.0)          # alive, between steps, no collective in flight
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:  # noqa: BLE001  (the group of the rank that saw the timeout is already broken)
+            pass
+
+
+def test_missing_rank_ends_the_exchange_with_an_error():
+    """Failure detection on the host: a rank that skips the all-gather makes the other rank's step
+    end with shard.ExchangeError after the process group's (short) timeout."""
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 31500 + os.getpid() % 2000
+    mp.spawn(_rank_missing_peer, args=(2, port, ret), nprocs=2, join=True)
+    assert ret["good0"] and ret["good1"]
+    assert ret["raised"] == "ExchangeError", dict(ret)
+    assert "rank 0 of 2" in ret["message"]
+    assert ret["waited_s"] < 30
