@@ -171,6 +171,12 @@ int kvskip_launch_update(const kvskip_update_params* p, void* stream);
  * Replaces kvskip::launch_read (kernels/kvskip.h:120; kernels/kvskip_kernel.cu:738-740). */
 int kvskip_launch_read(const void* x, int64_t bytes, uint32_t* out, int blocks, void* stream);
 
+/* The same probe through the copy engine (no counterpart in the reference): every CTA streams
+ * 32 KB pieces of x with bulk copies into a shared-memory ring, as the attention kernels load K/V
+ * blocks, and discards them.  Reads floor(bytes / 32768) whole pieces; x 16-byte aligned.  One CTA
+ * holds 192 KB of shared memory, so `blocks` = the number of SMs is the natural grid. */
+int kvskip_launch_read_bulk(const void* x, int64_t bytes, uint32_t* out, int blocks, void* stream);
+
 /* Dynamic shared memory of one decode CTA.  Replaces kvskip::max_smem_bytes
  * (kernels/kvskip.h:119; kernels/kvskip_kernel.cu:742-745). */
 int kvskip_max_smem_bytes(int D, int stages, int load_v);

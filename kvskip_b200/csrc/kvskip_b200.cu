@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdarg>
 #include <atomic>
 #include <cstdio>
@@ -17,6 +18,7 @@
 #include "common.cuh"
 #include "decode_exact.cuh"
 #include "decode_tc.cuh"
+#include "decode_tcq.cuh"
 #include "planner.cuh"
 #include "vskip.cuh"
 #include "vskip_tc.cuh"
@@ -169,6 +171,10 @@ constexpr int kMergeRegions = 64;
 constexpr int kMaxDevices = 64;
 __device__ int g_split_done[kMergeRegion * kMergeRegions];
 std::atomic<int> g_half_cta{1};
+// Block lists on more CTAs than SMs: 1 = one persistent CTA per SM pulling pieces from a queue
+// (decode_tcq.cuh), 0 = one CTA per piece (decode_tc.cuh).  Same bits either way.
+std::atomic<int> g_queue{1};
+std::atomic<int> g_min_blocks{24};     // shortest piece a block list is cut into when there are more CTAs than SMs
 // Polls (of about 100 ns) a kernel spends on a peer's flag before it gives up: about 2 s by default.
 // The "spin_limit" option lowers it, so that a missing peer is reported in microseconds (tests of the
 // failure path; a host that prefers a fast error over a long wait).
@@ -253,7 +259,21 @@ int launch_tc(const kvskip_params& p, const DynArgs& dyn, cudaStream_t stream) {
   // rest differ in length, the full-size CTA measured faster.
   const bool multi_wave =
       !MASKED && total >= 4 * static_cast<int64_t>(sms) && g_half_cta.load(std::memory_order_relaxed);
-  const int min_blocks = (total > sms) ? 24 : 1;
+  const int min_blocks = (total > sms) ? g_min_blocks.load(std::memory_order_relaxed) : 1;
+  if constexpr (MASKED && LOAD_V) {
+    // more pieces than SMs: persistent CTAs fed from a queue (the last counter of the stream's
+    // region is the queue head)
+    if (total > sms && done != nullptr && dyn.xa.R == 0 && p.B * p.Hkv < kMergeRegion &&
+        g_queue.load(std::memory_order_relaxed)) {
+      auto kernel = kvb::decode_tcq_kernel<MASKED, STATS>;
+      if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), kvb::TcqCfg::kSmemBytes)) return rc;
+      const int ctas = static_cast<int>(std::min<int64_t>(sms, total));
+      KVB_CUDA(launch_overlapped(kernel, dim3(ctas), dim3(kvb::TcqCfg::kThreads), kvb::TcqCfg::kSmemBytes, stream, p,
+                                 maps, done, done + (kMergeRegion - 1), min_blocks, dyn.t_dev, dyn.pages,
+                                 dyn.max_pages));
+      return KVSKIP_OK;
+    }
+  }
   if (int rc = multi_wave ? launch_tc_nc<3, MASKED, STATS, LOAD_V>(p, maps, done, min_blocks, dyn, stream)
                           : launch_tc_nc<6, MASKED, STATS, LOAD_V>(p, maps, done, min_blocks, dyn, stream))
     return rc;
@@ -526,6 +546,15 @@ int kvskip_set_option(const char* name, int value) {
     g_use_pdl.store(value ? 1 : 0, std::memory_order_relaxed);
     return KVSKIP_OK;
   }
+  if (!std::strcmp(name, "queue")) {
+    g_queue.store(value ? 1 : 0, std::memory_order_relaxed);
+    return KVSKIP_OK;
+  }
+  if (!std::strcmp(name, "min_blocks")) {
+    if (value < 1 || value > 4096) return fail(KVSKIP_E_ARG, "min_blocks: 1..4096");
+    g_min_blocks.store(value, std::memory_order_relaxed);
+    return KVSKIP_OK;
+  }
   if (!std::strcmp(name, "spin_limit")) {   // 0 restores the default
     if (value < 0) return fail(KVSKIP_E_ARG, "spin_limit: polls >= 1, or 0 for the default");
     g_xchg_spin.store(value ? value : kDefaultSpin, std::memory_order_relaxed);
@@ -539,6 +568,8 @@ int kvskip_get_option(const char* name) {
   if (name && !std::strcmp(name, "pdl")) return g_use_pdl.load(std::memory_order_relaxed);
   if (name && !std::strcmp(name, "half_cta")) return g_half_cta.load(std::memory_order_relaxed);
   if (name && !std::strcmp(name, "spin_limit")) return g_xchg_spin.load(std::memory_order_relaxed);
+  if (name && !std::strcmp(name, "queue")) return g_queue.load(std::memory_order_relaxed);
+  if (name && !std::strcmp(name, "min_blocks")) return g_min_blocks.load(std::memory_order_relaxed);
   return fail(KVSKIP_E_ARG, "unknown option");
 }
 
@@ -654,6 +685,16 @@ int kvskip_launch_read(const void* x, int64_t bytes, uint32_t* out, int blocks, 
   if (!x || !out || bytes % 16 || blocks < 1) return fail(KVSKIP_E_ARG, "read: x, out, bytes %% 16 == 0, blocks >= 1");
   kvb::read_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const uint4*>(x),
                                                                           bytes / 16, out);
+  KVB_CUDA(cudaGetLastError());
+  return KVSKIP_OK;
+}
+
+int kvskip_launch_read_bulk(const void* x, int64_t bytes, uint32_t* out, int blocks, void* stream) {
+  if (!x || !out || blocks < 1 || bytes < kvb::RB_PIECE || reinterpret_cast<uintptr_t>(x) % 16)
+    return fail(KVSKIP_E_ARG, "read_bulk: x 16-byte aligned, at least %d bytes, blocks >= 1", kvb::RB_PIECE);
+  if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::read_bulk_kernel), kvb::RB_SMEM)) return rc;
+  kvb::read_bulk_kernel<<<blocks, 64, kvb::RB_SMEM, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned char*>(x), bytes / kvb::RB_PIECE, out);
   KVB_CUDA(cudaGetLastError());
   return KVSKIP_OK;
 }

@@ -477,9 +477,14 @@ std::vector<at::Tensor> refresh_step(const at::Tensor& q, const at::Tensor& k, c
   return {r[0], r[1], r[2], r[3]};
 }
 
-void read_bw(const at::Tensor& x, at::Tensor& out, int64_t blocks) {
+void read_bw(const at::Tensor& x, at::Tensor& out, int64_t blocks, bool bulk) {
   TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.nbytes() % 16 == 0, "x: contiguous CUDA, 16-byte multiple");
   const c10::cuda::CUDAGuard guard(x.device());
+  if (bulk) {
+    raise_on(kvskip_launch_read_bulk(x.data_ptr(), static_cast<int64_t>(x.nbytes()),
+                                     reinterpret_cast<uint32_t*>(out.data_ptr()), static_cast<int>(blocks), cur_stream()));
+    return;
+  }
   raise_on(kvskip_launch_read(x.data_ptr(), static_cast<int64_t>(x.nbytes()), reinterpret_cast<uint32_t*>(out.data_ptr()),
                               static_cast<int>(blocks), cur_stream()));
 }
@@ -630,7 +635,8 @@ int64_t device_status() {
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
-  m.def("read_bw", &read_bw, "streaming read of x (bandwidth ceiling)");
+  m.def("read_bw", &read_bw, "streaming read of x (bandwidth ceiling); bulk: through the copy engine",
+        py::arg("x"), py::arg("out"), py::arg("blocks"), py::arg("bulk") = false);
   m.def("plan", &plan, "refresh planner: decision and block lists (before the pass)",
         py::arg("q"), py::arg("k"), py::arg("csum"), py::arg("lse_ref"), py::arg("cs_ref"), py::arg("keep"),
         py::arg("lse_att"), py::arg("age"), py::arg("flags"), py::arg("cs_now"), py::arg("trig"),

@@ -392,6 +392,52 @@ __global__ void __launch_bounds__(D) sum_splits_kernel(const kvskip_params p) {
   if (p.out_f32) p.out_f32[hq * D + d] = acc;
 }
 
+// Streaming read through the copy engine: the ceiling of what the attention kernels' own loads can
+// reach.  Every CTA pulls 32 KB pieces (piece c, c + grid, ...) with 1-D bulk copies into a ring of
+// RB_STAGES stages; a consumer warp touches one word per lane of a piece and frees the stage.
+// Nothing else is done with the data.  Bytes beyond the last whole piece are left out (the caller
+// counts whole pieces).  Waits are bounded like everywhere else.
+constexpr int RB_PIECE = 32768;
+constexpr int RB_STAGES = 6;
+constexpr int RB_SMEM = RB_STAGES * RB_PIECE + 2 * RB_STAGES * 8 + 128;
+__global__ void __launch_bounds__(64) read_bulk_kernel(const unsigned char* __restrict__ x, int64_t pieces,
+                                                       uint32_t* out) {
+  extern __shared__ unsigned char rb_raw[];
+  unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(rb_raw) + 127) & ~uintptr_t(127));
+  uint64_t* full = reinterpret_cast<uint64_t*>(ring + RB_STAGES * RB_PIECE);
+  uint64_t* empty = full + RB_STAGES;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    for (int s = 0; s < RB_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  const int64_t first = blockIdx.x, step = gridDim.x;
+  const int64_t n = first < pieces ? (pieces - first + step - 1) / step : 0;
+  if (warp == 0) {
+    if (lane == 0)
+      for (int64_t i = 0; i < n; ++i) {
+        const int s = static_cast<int>(i % RB_STAGES);
+        if (i >= RB_STAGES && !mbar_wait(&empty[s], ((i / RB_STAGES) - 1) & 1, 0x600u + s)) break;
+        mbar_expect_tx(&full[s], RB_PIECE);
+        bulk_load_1d(ring + s * RB_PIECE, x + (first + i * step) * RB_PIECE, RB_PIECE, &full[s]);
+      }
+  } else {
+    uint32_t fold = 0;
+    for (int64_t i = 0; i < n; ++i) {
+      const int s = static_cast<int>(i % RB_STAGES);
+      if (!mbar_wait(&full[s], (i / RB_STAGES) & 1, 0x610u + s)) break;
+      fold ^= *reinterpret_cast<const uint32_t*>(ring + s * RB_PIECE + lane * 1024);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+    }
+    if (fold == 0x9e3779b9u) out[0] = fold;   // keeps the reads alive; practically never true
+  }
+}
+
 // Streaming read: 16-byte loads, grid-stride, four independent loads in flight per thread.
 __global__ void __launch_bounds__(256) read_kernel(const uint4* __restrict__ x, int64_t n16, uint32_t* out) {
   uint32_t fold = 0;
