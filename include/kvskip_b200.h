@@ -291,6 +291,11 @@ int kvskip_launch_append(uint16_t* k, uint16_t* v, int64_t sb, int64_t sh, int64
  *   "pdl"          1 (default): the attention and planner kernels are launched with programmatic
  *                  stream serialisation, so their set-up overlaps the tail of the previous kernel
  *                  on the stream (they wait for it before reading memory); 0: plain launches.
+ *   "queue"        1 (default): a decode launch with block lists, V loaded, 32 to 1024 (batch, kv head)
+ *                  pairs and more pieces than SMs runs as one persistent CTA per SM pulling (head,
+ *                  piece) items from a device-side queue; 0: one CTA per piece.  Same bits either way.
+ *   "min_blocks"   shortest piece (in 64-token blocks) a block list is cut into when the launch has
+ *                  more CTAs than SMs; default 24.
  *   "spin_limit"   polls (about 100 ns each) a kernel of the sequence-sharded exchange spends on a
  *                  peer's flag before it gives up, sets the status word (0x500 + peer from
  *                  kvskip_launch_exchange_merge, 0x510 + peer from kvskip_launch_decode_xchg),

@@ -25,6 +25,21 @@
 
 namespace kvb {
 
+// Development aid, compiled out by default: with -DKVB_TIMELINE every CTA records %globaltimer stamps
+// and counts (entry, first item, first data, last block consumed, exit; items, blocks, skipped ids)
+// into g_timeline, which kvskip_debug_timeline() copies out.
+#ifdef KVB_TIMELINE
+__device__ unsigned long long g_timeline[256 * 16];
+__device__ __forceinline__ unsigned long long tl_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define KVB_TL(slot, value) g_timeline[blockIdx.x * 16 + (slot)] = (value)
+#else
+#define KVB_TL(slot, value) ((void)0)
+#endif
+
 struct TcqItem {
   int b, h;
   int i0, n;          // list positions [i0, i0 + n) (dense: blocks)
@@ -42,8 +57,12 @@ struct TcqCfg {
   static constexpr int kStageAcc = 2 * kConsumers * 4 * 128 * 4;               // [2][6][4][128] floats
   static constexpr int kStageMl = 2 * 2 * kConsumers * 4 * 4;                  // sM, sL: [2][6][4] floats each
   static constexpr int kBars = (2 * kStages + 2 * kQueueDepth + 4) * 8;
-  static constexpr int kSmemBytes =
-      kStages * kStageBytes + kStageAcc + kStageMl + kQueueDepth * static_cast<int>(sizeof(TcqItem)) + kBars + 1024;
+  static constexpr int kMaxHeads = 1024;                                       // (batch, kv head) pairs of a launch
+  static constexpr int kTable = (2 * kMaxHeads + 16) * 4;                      // item prefix sums + scan scratch
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStageAcc + kStageMl +
+                                    kQueueDepth * static_cast<int>(sizeof(TcqItem)) + kBars + kTable + 1024;
+  static_assert(kMaxHeads % kThreads == 0, "heads are dealt to threads in equal runs");
+  static_assert(kSmemBytes <= 232448, "one CTA per SM: at most 227 KB of shared memory");
 };
 
 template <bool MASKED, bool STATS>
@@ -66,9 +85,17 @@ decode_tcq_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, i
   uint64_t* iempty = ifull + QD;                                                 // [QD]
   uint64_t* done = iempty + QD;                                                  // [2] staging written by the consumers
   uint64_t* freeb = done + 2;                                                    // [2] staging read by the merger
+  int* pfx = reinterpret_cast<int*>(freeb + 2);                                  // [2][kMaxHeads] item prefix sums
+  int* wsum = pfx + 2 * TcqCfg::kMaxHeads;                                       // [16] scan scratch
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
+#ifdef KVB_TIMELINE
+    KVB_TL(0, tl_now());
+    unsigned int smid;
+    asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+    KVB_TL(9, smid);
+#endif
     tma_prefetch_desc(&maps.k);
     tma_prefetch_desc(&maps.v);
     for (int s = 0; s < S; ++s) {
@@ -92,27 +119,83 @@ decode_tcq_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, i
   const int T = t_dev ? max(1, min(*t_dev, p.T)) : p.T;
   const int BH = p.B * p.Hkv;
 
+  // ---- item table: every CTA computes the same one.  Items are (head, piece) pairs; the heads whose
+  // pieces are long (lists longer than num_splits * min_blocks: the refreshing heads) come first,
+  // then the others, so that the work left for the end of the launch comes in short pieces.
+  // pfx[0][bh], pfx[1][bh]: inclusive prefix sums of the piece counts of the long / the other heads.
+  auto pieces_of = [&](int n_items) {
+    int S_use = p.num_splits;
+    if (min_blocks > 1) S_use = max(1, min(p.num_splits, (n_items + min_blocks - 1) / min_blocks));
+    return S_use;
+  };
+  const int long_len = p.num_splits * max(min_blocks, 1);
+  {
+    constexpr int PER = TcqCfg::kMaxHeads / TcqCfg::kThreads;      // heads per thread
+    int cl[PER], cs[PER], sl = 0, ss = 0;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int bh = tid * PER + j;
+      cl[j] = cs[j] = 0;
+      if (bh < BH) {
+        const int n_items = MASKED ? p.block_cnt[bh] : (T + TILE - 1) / TILE;
+        const int c = pieces_of(n_items);
+        if (n_items > long_len) cl[j] = c; else cs[j] = c;
+      }
+      sl += cl[j];
+      ss += cs[j];
+    }
+    int il = sl, is = ss;                                           // inclusive scan over the threads
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int tl = __shfl_up_sync(0xffffffffu, il, o), ts = __shfl_up_sync(0xffffffffu, is, o);
+      if (lane >= o) { il += tl; is += ts; }
+    }
+    if (lane == 31) { wsum[warp] = il; wsum[8 + warp] = is; }
+    __syncthreads();
+    int ol = 0, os = 0;
+    for (int w = 0; w < warp; ++w) { ol += wsum[w]; os += wsum[8 + w]; }
+    int rl = ol + il - sl, rs = os + is - ss;                       // exclusive offsets of this thread's first head
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int bh = tid * PER + j;
+      rl += cl[j];
+      rs += cs[j];
+      if (bh < BH) { pfx[bh] = rl; pfx[TcqCfg::kMaxHeads + bh] = rs; }
+    }
+    __syncthreads();
+  }
+
   if (warp == NC) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
-      const int total = p.num_splits * BH;               // ids: piece-major, highest piece first
+      const int total_long = pfx[BH - 1], total = total_long + pfx[TcqCfg::kMaxHeads + BH - 1];
       const int last_fetch = total + static_cast<int>(gridDim.x) - 1;
       int gi = 0, it = 0;
       int id = atomicAdd(queue, 1);
       bool ok = true;
+#ifdef KVB_TIMELINE
+      KVB_TL(1, tl_now());
+#endif
       while (ok) {
         if (id >= total) {
           if (id == last_fetch) *queue = 0;              // every CTA has made its final fetch: ready for the next launch
           break;
         }
-        const int piece = p.num_splits - 1 - id / BH, bh = id % BH;
-        const int n_items = MASKED ? p.block_cnt[bh] : (T + TILE - 1) / TILE;
-        int S_use = p.num_splits;
-        if (min_blocks > 1) S_use = max(1, min(p.num_splits, (n_items + min_blocks - 1) / min_blocks));
-        if (piece >= S_use) {
-          id = atomicAdd(queue, 1);
-          continue;
+        // item id -> (head, piece): the first head whose inclusive prefix exceeds the index
+        const int* pf = id < total_long ? pfx : pfx + TcqCfg::kMaxHeads;
+        const int k = id < total_long ? id : id - total_long;
+        int lo = 0, hi = BH - 1;
+        while (lo < hi) {
+          const int mid = (lo + hi) >> 1;
+          if (pf[mid] > k) hi = mid; else lo = mid + 1;
         }
+        const int bh = lo;
+        const int n_items = MASKED ? p.block_cnt[bh] : (T + TILE - 1) / TILE;
+        const int S_use = pieces_of(n_items);
+        const int piece = k - (pf[bh] - S_use);
+#ifdef KVB_TIMELINE
+        if (it == 0) KVB_TL(2, tl_now());
+#endif
         const int per = (n_items + S_use - 1) / S_use;
         const int i0 = min(n_items, piece * per);
         const int n = min(n_items, i0 + per) - i0;
@@ -140,6 +223,11 @@ decode_tcq_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, i
         ++it;
         id = next;
       }
+#ifdef KVB_TIMELINE
+      KVB_TL(3, tl_now());
+      KVB_TL(6, static_cast<unsigned long long>(it));
+      KVB_TL(7, static_cast<unsigned long long>(gi));
+#endif
       // the end of this CTA's item stream, for the consumers and the merger
       const int qi = it % QD;
       if (it < QD || mbar_wait(&iempty[qi], ((it / QD) - 1) & 1, 0x228u + qi)) {
@@ -191,9 +279,15 @@ decode_tcq_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, i
           fence_proxy_async_smem();
           __syncwarp();
         }
+#ifdef KVB_TIMELINE
+        if (g2 == 0 && lane == 0) KVB_TL(4, tl_now());
+#endif
         tc_block<STATS, true>(p, kbase, bq, blk, hq0, lane, T, m_run, l_run, acc);
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
+#ifdef KVB_TIMELINE
+        if (lane == 0) g_timeline[blockIdx.x * 16 + 10 + (warp % 6 == 0 ? 0 : 1)] = tl_now();   // last block done (warp 0 / others)
+#endif
       }
       if (!ok) break;
       gi += d.n;
@@ -303,32 +397,69 @@ decode_tcq_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, i
       last = __shfl_sync(0xffffffffu, last, 0);
       if (!last) continue;
       __threadfence();
-      // merge of the head's pieces in ascending order (the arithmetic of merge_kernel)
-#pragma unroll 1
-      for (int g = 0; g < G; ++g) {
-        const int64_t hq = hq0 + g;
-        const float* ml = p.part_ml + hq * p.num_splits * 2;
-        float m = -INFINITY;
-        for (int s2 = 0; s2 < d.S_use; ++s2) m = fmaxf(m, __ldcg(ml + 2 * s2));
-        const float mu = (m == -INFINITY) ? 0.f : m;
-        float l = 0.f, a[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int s2 = 0; s2 < d.S_use; ++s2) {
-          const float w = ex2(__ldcg(ml + 2 * s2) - mu);
-          l += __ldcg(ml + 2 * s2 + 1) * w;
-          const float* pa = p.part_acc + (hq * p.num_splits + s2) * D;
+      // merge of the head's pieces in ascending order (the arithmetic of merge_kernel): the four
+      // query heads together, the partials of four pieces requested before any of them is used
+      // (64 independent loads per lane: one warp must pull the whole head through)
+      {
+        const float* ml = p.part_ml + hq0 * p.num_splits * 2;          // [G][num_splits][2]
+        const float* pa = p.part_acc + hq0 * p.num_splits * D;         // [G][num_splits][D]
+        const int Su = d.S_use, ns = p.num_splits;
+        float m[G], mu[G], l[G], a[G][4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) a[j] += __ldcg(pa + lane + 32 * j) * w;
+        for (int g = 0; g < G; ++g) {
+          m[g] = -INFINITY;
+          l[g] = 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) a[g][j] = 0.f;
+        }
+        for (int s2 = 0; s2 < Su; ++s2)
+#pragma unroll
+          for (int g = 0; g < G; ++g) m[g] = fmaxf(m[g], __ldcg(ml + (g * ns + s2) * 2));
+#pragma unroll
+        for (int g = 0; g < G; ++g) mu[g] = (m[g] == -INFINITY) ? 0.f : m[g];
+        for (int s0 = 0; s0 < Su; s0 += 4) {
+          float w[4][G], pl[4][G], x[4][G][4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int s2 = min(s0 + u, Su - 1);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+              w[u][g] = __ldcg(ml + (g * ns + s2) * 2);
+              pl[u][g] = __ldcg(ml + (g * ns + s2) * 2 + 1);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) x[u][g][j] = __ldcg(pa + (static_cast<int64_t>(g) * ns + s2) * D + lane + 32 * j);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (s0 + u < Su) {
+#pragma unroll
+              for (int g = 0; g < G; ++g) {
+                const float ww = ex2(w[u][g] - mu[g]);
+                l[g] += pl[u][g] * ww;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) a[g][j] += x[u][g][j] * ww;
+              }
+            }
+          }
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float o32 = l > 0.f ? a[j] / l : 0.f;
-          reinterpret_cast<__nv_bfloat16*>(p.out)[hq * D + lane + 32 * j] = __float2bfloat16(o32);
-          if (p.out_f32) p.out_f32[hq * D + lane + 32 * j] = o32;
+        for (int g = 0; g < G; ++g) {
+          const int64_t hq = hq0 + g;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float o32 = l[g] > 0.f ? a[g][j] / l[g] : 0.f;
+            reinterpret_cast<__nv_bfloat16*>(p.out)[hq * D + lane + 32 * j] = __float2bfloat16(o32);
+            if (p.out_f32) p.out_f32[hq * D + lane + 32 * j] = o32;
+          }
+          if (lane == 0 && p.lse) p.lse[hq] = l[g] > 0.f ? (m[g] + log2f(l[g])) * LN2 : -INFINITY;
         }
-        if (lane == 0 && p.lse) p.lse[hq] = l > 0.f ? (m + log2f(l)) * LN2 : -INFINITY;
       }
       if (lane == 0) split_done[d.b * p.Hkv + d.h] = 0;
     }
+#ifdef KVB_TIMELINE
+    if (lane == 0) KVB_TL(5, tl_now());
+#endif
   }
 }
 

@@ -263,8 +263,10 @@ int launch_tc(const kvskip_params& p, const DynArgs& dyn, cudaStream_t stream) {
   if constexpr (MASKED && LOAD_V) {
     // more pieces than SMs: persistent CTAs fed from a queue (the last counter of the stream's
     // region is the queue head)
-    if (total > sms && done != nullptr && dyn.xa.R == 0 && p.B * p.Hkv < kMergeRegion &&
-        g_queue.load(std::memory_order_relaxed)) {
+    // (from 32 heads on: below that the pieces of a launch are fewer than the SMs and a CTA per piece
+    // starts sooner than the queue)
+    if (total > sms && done != nullptr && dyn.xa.R == 0 && p.B * p.Hkv >= 32 &&
+        p.B * p.Hkv <= kvb::TcqCfg::kMaxHeads && g_queue.load(std::memory_order_relaxed)) {
       auto kernel = kvb::decode_tcq_kernel<MASKED, STATS>;
       if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), kvb::TcqCfg::kSmemBytes)) return rc;
       const int ctas = static_cast<int>(std::min<int64_t>(sms, total));
@@ -848,6 +850,15 @@ int kvskip_launch_advance(int* t_dev, int delta, void* stream) {
   KVB_CUDA(cudaGetLastError());
   return KVSKIP_OK;
 }
+
+#ifdef KVB_TIMELINE
+// development builds only: the per-CTA stamps of the last queue-kernel launch (see decode_tcq.cuh)
+int kvskip_debug_timeline(unsigned long long* dst, int n) {
+  KVB_CUDA(cudaDeviceSynchronize());
+  KVB_CUDA(cudaMemcpyFromSymbol(dst, kvb::g_timeline, sizeof(unsigned long long) * std::min(n, 256 * 16)));
+  return KVSKIP_OK;
+}
+#endif
 
 int kvskip_device_status(void* stream, unsigned int* status) {
   if (!status) return fail(KVSKIP_E_ARG, "null status pointer");

@@ -130,11 +130,21 @@ def make_plan(keep: torch.Tensor, sync: bool = True) -> Plan:
     return Plan(order, cnt, int(cnt.max()) if sync else nb, nb)
 
 
+QUEUE_MIN_HEADS = 32      # (batch, kv head) pairs from which block lists go to the persistent queue kernel
+
+
 def splits_for_unsynced_plan(bh: int, nb: int) -> int:
-    """Split count for a block list whose true lengths are not known on the host (sized for nb).
-    The tensor-core kernel cuts every list into pieces of >= 24 blocks and lets surplus CTAs leave
-    at once, so at small batch it pays to provision enough splits for a head that reads every block
-    to spread over many SMs; at larger batch the grid is several waves anyway."""
+    """Split count (pieces provisioned per head) for a block list whose true lengths are not known
+    on the host (sized for nb).  The tensor-core kernels cut every list into pieces of at least 24
+    blocks, so a short list uses few of the provisioned pieces.
+      * from 32 (batch, kv head) pairs on, the pieces are pulled from a queue by one persistent CTA
+        per SM: 12 pieces per head measured best (a head that reads everything is cut into 12 long
+        pieces, which are handed out first; more pieces make the merge of a head the tail of the
+        launch);
+      * below that every piece is a CTA of its own: enough splits for a head that reads every block
+        to spread over many SMs."""
+    if bh >= QUEUE_MIN_HEADS and ext().get_option("queue"):
+        return max(1, min(12, -(-nb // 24)))
     base = num_splits_for(bh, nb)
     if bh * base <= 2 * num_sms():
         return min(64, max(base, -(-nb // 24)))

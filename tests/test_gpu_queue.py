@@ -45,8 +45,8 @@ def both(fn):
     return a, b
 
 
-@pytest.mark.parametrize("B,T,splits,min_blocks", [(8, 8192 + 13, 9, 24), (8, 8192 + 13, 20, 6), (2, 16384, 64, 24),
-                                                    (3, 4096 + 1, 16, 4), (16, 2048, 5, 2)])
+@pytest.mark.parametrize("B,T,splits,min_blocks", [(8, 8192 + 13, 9, 24), (8, 8192 + 13, 20, 6), (4, 16384, 64, 24),
+                                                    (5, 4096 + 1, 16, 4), (16, 2048, 5, 2)])
 @pytest.mark.parametrize("stats", [False, True])
 def test_queue_kernel_equals_piece_kernel(B, T, splits, min_blocks, stats):
     q, k, v, scale = synth.dense_case(300 + B, B, T)
