@@ -23,7 +23,7 @@
 //     operand, 32 ldmatrix.trans + 64 MMA for the output.
 //   * epilogue: the consumers' states are merged through shared memory in warp order, then
 //     written as the final output (one split) or as this split's partial (max, sum, acc).
-// Only D = 128, G = 4.  Scores differ from the exact-order path in the last bits (the tensor
+// D = 128 and D = 64 (half-size stages, two per consumer warp), G = 4.  Scores differ from the exact-order path in the last bits (the tensor
 // core's accumulation order); outputs and block log-sum-exps stay within the 2e-3 tolerance.
 #pragma once
 #include "common.cuh"
@@ -43,12 +43,15 @@ constexpr int TC_HALF_BYTES = TILE * 64 * 2;        // one TMA box: 64 tokens x 
 // has more CTAs than SMs, so that while one CTA of an SM sets up, drains or merges, the other one
 // streams -- the fixed cost of a CTA (about 6 us: launch, first TMA round trip, merge, fence and
 // counter) is as long as streaming 9 blocks, and block lists of a refresh step are short.
-template <int NC, bool LOAD_V>
+// D = 64 (one 64-dim half per tensor): stages are half as large and twice as many, two per consumer.
+template <int NC, bool LOAD_V, int D = 128>
 struct TcCfg {
+  static_assert(D == 64 || D == 128, "head dims with a tensor-core path");
+  static constexpr int kHalves = D / 64;                            // 64-dim TMA boxes per tensor and block
   static constexpr int kThreads = (NC + 1) * 32;
-  static constexpr int kStageBytes = TC_HALF_BYTES * (LOAD_V ? 4 : 2);
-  static constexpr int kStages = LOAD_V ? NC : 2 * NC;
-  static constexpr int kRedBytes = NC * 4 * 128 * 4;               // epilogue staging, aliases the ring
+  static constexpr int kStageBytes = TC_HALF_BYTES * kHalves * (LOAD_V ? 2 : 1);
+  static constexpr int kStages = (LOAD_V ? NC : 2 * NC) * (2 / kHalves);
+  static constexpr int kRedBytes = NC * 4 * D * 4;                  // epilogue staging, aliases the ring
   static constexpr int kAuxBytes = NC * 8 * 4 + 2 * kStages * 8;
   static_assert(kStages % NC == 0, "a stage must always be consumed by the same warp");
   static_assert(kRedBytes <= kStages * kStageBytes, "epilogue staging fits in the ring");
@@ -94,10 +97,11 @@ __device__ __forceinline__ float quadcol_sum(float v) {
 
 // ---- one 64-token block for one consumer warp: scores, online softmax (+ statistics), output.
 // kbase: shared-memory address of the stage (K halves, then V halves); state in m_run / l_run / acc.
-template <bool STATS, bool LOAD_V>
-__device__ __forceinline__ void tc_block(const kvskip_params& p, const uint32_t kbase, const uint32_t (&bq)[8][2],
+template <bool STATS, bool LOAD_V, int D = 128>
+__device__ __forceinline__ void tc_block(const kvskip_params& p, const uint32_t kbase, const uint32_t (&bq)[D / 16][2],
                                          const int blk, const int64_t hq0, const int lane, const int T,
-                                         float (&m_run)[2], float (&l_run)[2], float (&acc)[8][4]) {
+                                         float (&m_run)[2], float (&l_run)[2], float (&acc)[D / 16][4]) {
+  constexpr int KS = D / 16;                   // 16-dim steps of the score product = 16-dim tiles of the output
   const int lrow = lane & 7, lmat = lane >> 3;
   const bool col_ok = (lane & 3) < 2;          // this thread's two columns are real heads
   const int head0 = 2 * (lane & 3);
@@ -109,7 +113,7 @@ __device__ __forceinline__ void tc_block(const kvskip_params& p, const uint32_t 
 #pragma unroll
     for (int c = 0; c < 4; ++c) sc[mt][c] = 0.f;
 #pragma unroll
-  for (int ks = 0; ks < 8; ++ks) {
+  for (int ks = 0; ks < KS; ++ks) {
     const uint32_t hbase = kbase + (ks >> 2) * TC_HALF_BYTES;
     const int chunk = (ks & 3) * 2 + (lmat >> 1);
 #pragma unroll
@@ -187,12 +191,12 @@ __device__ __forceinline__ void tc_block(const kvskip_params& p, const uint32_t 
     // ---- O^T = alpha * O^T + V^T P^T
     if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-      for (int mt = 0; mt < 8; ++mt) {
+      for (int mt = 0; mt < KS; ++mt) {
         acc[mt][0] *= alpha[0]; acc[mt][1] *= alpha[1];
         acc[mt][2] *= alpha[0]; acc[mt][3] *= alpha[1];
       }
     }
-    const uint32_t vbase = kbase + 2 * TC_HALF_BYTES;
+    const uint32_t vbase = kbase + (D / 64) * TC_HALF_BYTES;
 #pragma unroll
     for (int kt = 0; kt < 4; ++kt) {
       // P of tokens kt*16..+15 as high + low bf16 parts, transposed into the B layout
@@ -203,7 +207,7 @@ __device__ __forceinline__ void tc_block(const kvskip_params& p, const uint32_t 
       const uint32_t bh0 = movm_t(h0), bh1 = movm_t(h1), bl0 = movm_t(l0), bl1 = movm_t(l1);
       const int tok = kt * 16 + (lmat >> 1) * 8 + lrow;
 #pragma unroll
-      for (int mt = 0; mt < 8; ++mt) {
+      for (int mt = 0; mt < KS; ++mt) {
         const int dchunk = mt * 2 + (lmat & 1);
         uint32_t a[4];
         ldsm_x4_t(a, vbase + (dchunk >> 3) * TC_HALF_BYTES + tok * 128 + (((dchunk & 7) ^ lrow) << 4));
@@ -216,12 +220,13 @@ __device__ __forceinline__ void tc_block(const kvskip_params& p, const uint32_t 
 
 // Q^T as the B operand of the score MMA: column n = lane/4 is a head (4..7 are zero padding),
 // rows k = 2*(lane%4)+{0,1} (+8) of each 16-dim step
+template <int KS>
 __device__ __forceinline__ void tc_load_q(const kvskip_params& p, const int b, const int h, const int lane,
-                                          uint32_t (&bq)[8][2]) {
+                                          uint32_t (&bq)[KS][2]) {
   const int head = lane >> 2;
   const uint16_t* qp = p.q + b * p.q_sb + (h * 4 + (head & 3)) * p.q_sh + 2 * (lane & 3);
 #pragma unroll
-  for (int ks = 0; ks < 8; ++ks) {
+  for (int ks = 0; ks < KS; ++ks) {
     bq[ks][0] = head < 4 ? *reinterpret_cast<const uint32_t*>(qp + ks * 16) : 0u;
     bq[ks][1] = head < 4 ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8) : 0u;
   }
@@ -323,13 +328,13 @@ __device__ __forceinline__ void xchg_finish(const kvskip_params& p, const XchgAr
   }
 }
 
-template <int NC, bool MASKED, bool STATS, bool LOAD_V>
+template <int NC, bool MASKED, bool STATS, bool LOAD_V, int D = 128>
 __global__ void __launch_bounds__((NC + 1) * 32, NC <= 3 ? 2 : 1)
 decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* __restrict__ split_done,
                  const int min_blocks, const int* __restrict__ t_dev, const int32_t* __restrict__ pages,
                  const int max_pages, const XchgArgs xa) {
-  using Cfg = TcCfg<NC, LOAD_V>;
-  constexpr int G = 4, D = 128;
+  using Cfg = TcCfg<NC, LOAD_V, D>;
+  constexpr int G = 4, KS = D / 16, HV = D / 64;   // HV: 64-dim halves per tensor and block
   constexpr int S = Cfg::kStages;
   constexpr int TC_THREADS = Cfg::kThreads;   // shadows the 6-consumer constant inside this kernel
 
@@ -387,9 +392,9 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
   // per-thread state of a consumer: two heads (columns 2*(lane&3), +1 of the 8-wide N axis)
   float m_run[2] = {-INFINITY, -INFINITY};
   float l_run[2] = {0.f, 0.f};            // thread-partial sums, reduced across lanes in the epilogue
-  float acc[8][4];                        // O^T fragments: 8 tiles of 16 dims x 8 heads
+  float acc[KS][4];                       // O^T fragments: D/16 tiles of 16 dims x 8 heads
 #pragma unroll
-  for (int mt = 0; mt < 8; ++mt)
+  for (int mt = 0; mt < KS; ++mt)
 #pragma unroll
     for (int c = 0; c < 4; ++c) acc[mt][c] = 0.f;
 
@@ -407,18 +412,19 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
         const int bp = pages ? pages[static_cast<int64_t>(b) * max_pages + blk] : b;
         unsigned char* dst = ring + s * Cfg::kStageBytes;
         mbar_expect_tx(&full[s], Cfg::kStageBytes);
-        tma_load_4d(dst, &maps.k, &full[s], 0, t0, h, bp);
-        tma_load_4d(dst + TC_HALF_BYTES, &maps.k, &full[s], 64, t0, h, bp);
+#pragma unroll
+        for (int hv = 0; hv < HV; ++hv) tma_load_4d(dst + hv * TC_HALF_BYTES, &maps.k, &full[s], 64 * hv, t0, h, bp);
         if constexpr (LOAD_V) {
-          tma_load_4d(dst + 2 * TC_HALF_BYTES, &maps.v, &full[s], 0, t0, h, bp);
-          tma_load_4d(dst + 3 * TC_HALF_BYTES, &maps.v, &full[s], 64, t0, h, bp);
+#pragma unroll
+          for (int hv = 0; hv < HV; ++hv)
+            tma_load_4d(dst + (HV + hv) * TC_HALF_BYTES, &maps.v, &full[s], 64 * hv, t0, h, bp);
         }
       }
     }
   } else {
     // ------------------------------------------------------------------ consumers
-    uint32_t bq[8][2];
-    tc_load_q(p, b, h, lane, bq);
+    uint32_t bq[KS][2];
+    tc_load_q<KS>(p, b, h, lane, bq);
     const int64_t hq0 = static_cast<int64_t>(b) * p.Hq + h * G;
     const int head0 = 2 * (lane & 3);
 
@@ -435,17 +441,17 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
         // is moot).
         if ((t_dev != nullptr || pages != nullptr) && blk * TILE + TILE > T) {
           const int r0 = T - blk * TILE;
-          unsigned char* vst = ring + s * Cfg::kStageBytes + 2 * TC_HALF_BYTES;
+          unsigned char* vst = ring + s * Cfg::kStageBytes + HV * TC_HALF_BYTES;
           for (int o = r0 * 128 + lane * 16; o < TILE * 128; o += 32 * 16) {
-            *reinterpret_cast<uint4*>(vst + o) = make_uint4(0u, 0u, 0u, 0u);
-            *reinterpret_cast<uint4*>(vst + TC_HALF_BYTES + o) = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+            for (int hv = 0; hv < HV; ++hv) *reinterpret_cast<uint4*>(vst + hv * TC_HALF_BYTES + o) = make_uint4(0u, 0u, 0u, 0u);
           }
           fence_proxy_async_smem();   // ordered before the next bulk load into this stage
           __syncwarp();
         }
       }
 
-      tc_block<STATS, LOAD_V>(p, kbase, bq, blk, hq0, lane, T, m_run, l_run, acc);
+      tc_block<STATS, LOAD_V, D>(p, kbase, bq, blk, hq0, lane, T, m_run, l_run, acc);
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);
     }
@@ -480,13 +486,13 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
   }
   __syncthreads();   // every block has been consumed: the ring is free for the merge of the warps
 
-  const bool xchg = LOAD_V && xa.R > 0;
+  const bool xchg = LOAD_V && D == 128 && xa.R > 0;   // the cross-GPU exchange exists for D = 128
   if constexpr (LOAD_V) {
     float* red = reinterpret_cast<float*>(ring);   // [NC][G][D]
     if (warp < NC && (lane & 3) < 2) {
       const int head0 = 2 * (lane & 3);
 #pragma unroll
-      for (int mt = 0; mt < 8; ++mt)
+      for (int mt = 0; mt < KS; ++mt)
 #pragma unroll
         for (int c = 0; c < 4; ++c)
           red[(warp * G + head0 + (c & 1)) * D + mt * 16 + (lane >> 2) + (c >> 1) * 8] = acc[mt][c];
@@ -511,7 +517,7 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
         if (!xchg) {
           reinterpret_cast<__nv_bfloat16*>(p.out)[hq * D + d] = __float2bfloat16(o32);
           if (p.out_f32) p.out_f32[hq * D + d] = o32;
-        } else {   // a head this rank reads in one piece (a short or empty list): its row goes to the peers from here
+        } else if constexpr (D == 128) {   // a head this rank reads in one piece (a short or empty list): its row goes to the peers from here
           xchg_store(xa, hq, d, o32, l > 0.f ? (M + log2f(l)) * LN2 : -INFINITY);
         }
       } else {
@@ -539,7 +545,8 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
   // finished splits and is put back to zero by the CTA that merges.
   if constexpr (LOAD_V) {
     if (S_use == 1) {
-      if (xchg) xchg_finish<TC_THREADS>(p, xa, b, h, tid);
+      if constexpr (D == 128)
+        if (xchg) xchg_finish<TC_THREADS>(p, xa, b, h, tid);
     } else if (split_done != nullptr) {
       __shared__ int s_last;
       __threadfence();            // this CTA's partials are visible device-wide before it is counted
@@ -568,11 +575,12 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
             reinterpret_cast<__nv_bfloat16*>(p.out)[hq * D + d] = __float2bfloat16(o32);
             if (p.out_f32) p.out_f32[hq * D + d] = o32;
             if (d == 0 && p.lse) p.lse[hq] = lse_nat;
-          } else {
+          } else if constexpr (D == 128) {
             xchg_store(xa, hq, d, o32, lse_nat);
           }
         }
-        if (xchg) xchg_finish<TC_THREADS>(p, xa, b, h, tid);
+        if constexpr (D == 128)
+          if (xchg) xchg_finish<TC_THREADS>(p, xa, b, h, tid);
         if (tid == 0) split_done[b * p.Hkv + h] = 0;
       }
     }

@@ -250,7 +250,7 @@ decode_tcq_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, i
       const int32_t* list = MASKED ? p.block_idx + static_cast<int64_t>(b * p.Hkv + h) * p.max_blocks : nullptr;
       const int64_t hq0 = static_cast<int64_t>(b) * p.Hq + h * G;
       uint32_t bq[8][2];
-      tc_load_q(p, b, h, lane, bq);
+      tc_load_q<8>(p, b, h, lane, bq);
       float m_run[2] = {-INFINITY, -INFINITY};
       float l_run[2] = {0.f, 0.f};
       float acc[8][4];

@@ -216,26 +216,26 @@ struct DynArgs {
   kvb::XchgArgs xa{};               // R > 0: cross-GPU exchange inside the kernel (sequence shards)
 };
 
-template <int NC, bool MASKED, bool STATS, bool LOAD_V>
+template <int NC, bool MASKED, bool STATS, bool LOAD_V, int D>
 int launch_tc_nc(const kvskip_params& p, const kvb::TmaMaps& maps, int* done, int min_blocks, const DynArgs& dyn,
                  cudaStream_t stream) {
-  using Cfg = kvb::TcCfg<NC, LOAD_V>;
-  auto kernel = kvb::decode_tc_kernel<NC, MASKED, STATS, LOAD_V>;
+  using Cfg = kvb::TcCfg<NC, LOAD_V, D>;
+  auto kernel = kvb::decode_tc_kernel<NC, MASKED, STATS, LOAD_V, D>;
   if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes)) return rc;
   KVB_CUDA(launch_overlapped(kernel, dim3(p.num_splits, p.Hkv, p.B), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, p,
                              maps, done, min_blocks, dyn.t_dev, dyn.pages, dyn.max_pages, dyn.xa));
   return KVSKIP_OK;
 }
 
-template <bool MASKED, bool STATS, bool LOAD_V>
+template <bool MASKED, bool STATS, bool LOAD_V, int D = 128>
 int launch_tc(const kvskip_params& p, const DynArgs& dyn, cudaStream_t stream) {
   kvb::TmaMaps maps;
   // contiguous cache: (D, T, Hkv, B); paged cache: (D, 64, Hkv, pages) over the pool
   const int map_b = dyn.pages ? dyn.num_pages : p.B, map_t = dyn.pages ? KVSKIP_TILE : p.T;
-  if (int rc = make_kv_map(&maps.k, p.k, p.k_sb, p.k_sh, p.k_st, map_b, p.Hkv, map_t, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+  if (int rc = make_kv_map(&maps.k, p.k, p.k_sb, p.k_sh, p.k_st, map_b, p.Hkv, map_t, D, 64, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
   if (LOAD_V) {
-    if (int rc = make_kv_map(&maps.v, p.v, p.v_sb, p.v_sh, p.v_st, map_b, p.Hkv, map_t, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+    if (int rc = make_kv_map(&maps.v, p.v, p.v_sb, p.v_sh, p.v_st, map_b, p.Hkv, map_t, D, 64, CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
   } else {
     maps.v = maps.k;
@@ -260,7 +260,7 @@ int launch_tc(const kvskip_params& p, const DynArgs& dyn, cudaStream_t stream) {
   const bool multi_wave =
       !MASKED && total >= 4 * static_cast<int64_t>(sms) && g_half_cta.load(std::memory_order_relaxed);
   const int min_blocks = (total > sms) ? g_min_blocks.load(std::memory_order_relaxed) : 1;
-  if constexpr (MASKED && LOAD_V) {
+  if constexpr (MASKED && LOAD_V && D == 128) {
     // more pieces than SMs: persistent CTAs fed from a queue (the last counter of the stream's
     // region is the queue head)
     // (from 32 heads on: below that the pieces of a launch are fewer than the SMs and a CTA per piece
@@ -276,11 +276,11 @@ int launch_tc(const kvskip_params& p, const DynArgs& dyn, cudaStream_t stream) {
       return KVSKIP_OK;
     }
   }
-  if (int rc = multi_wave ? launch_tc_nc<3, MASKED, STATS, LOAD_V>(p, maps, done, min_blocks, dyn, stream)
-                          : launch_tc_nc<6, MASKED, STATS, LOAD_V>(p, maps, done, min_blocks, dyn, stream))
+  if (int rc = multi_wave ? launch_tc_nc<3, MASKED, STATS, LOAD_V, D>(p, maps, done, min_blocks, dyn, stream)
+                          : launch_tc_nc<6, MASKED, STATS, LOAD_V, D>(p, maps, done, min_blocks, dyn, stream))
     return rc;
   if (LOAD_V && p.num_splits > 1 && done == nullptr) {
-    kvb::merge_kernel<128><<<p.B * p.Hq, 128, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits,
+    kvb::merge_kernel<D><<<p.B * p.Hq, D, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits,
                                                           static_cast<int64_t>(p.B) * p.Hq, true, p.out, p.out_f32,
                                                           p.lse);
     KVB_CUDA(cudaGetLastError());
@@ -288,13 +288,14 @@ int launch_tc(const kvskip_params& p, const DynArgs& dyn, cudaStream_t stream) {
   return KVSKIP_OK;
 }
 
+template <int D>
 int dispatch_tc(const kvskip_params& p, bool masked, bool stats, bool load_v, const DynArgs& dyn, cudaStream_t s) {
-  if (!masked && !stats && load_v) return launch_tc<false, false, true>(p, dyn, s);
-  if (!masked && stats && load_v) return launch_tc<false, true, true>(p, dyn, s);
-  if (!masked && stats && !load_v) return launch_tc<false, true, false>(p, dyn, s);
-  if (masked && !stats && load_v) return launch_tc<true, false, true>(p, dyn, s);
-  if (masked && stats && load_v) return launch_tc<true, true, true>(p, dyn, s);
-  if (masked && stats && !load_v) return launch_tc<true, true, false>(p, dyn, s);
+  if (!masked && !stats && load_v) return launch_tc<false, false, true, D>(p, dyn, s);
+  if (!masked && stats && load_v) return launch_tc<false, true, true, D>(p, dyn, s);
+  if (!masked && stats && !load_v) return launch_tc<false, true, false, D>(p, dyn, s);
+  if (masked && !stats && load_v) return launch_tc<true, false, true, D>(p, dyn, s);
+  if (masked && stats && load_v) return launch_tc<true, true, true, D>(p, dyn, s);
+  if (masked && stats && !load_v) return launch_tc<true, true, false, D>(p, dyn, s);
   return fail(KVSKIP_E_ARG, "kvskip: unsupported flag combination (load_v=false needs stats=true)");
 }
 
@@ -425,11 +426,16 @@ int decode_impl(const kvskip_params* p, int D, int G, int stages, int masked, in
     return fail(KVSKIP_E_ARG, "num_splits > 1 needs part_acc / part_ml scratch");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int path = g_decode_path.load(std::memory_order_relaxed);
-  if (D == 128 && path != 1) return dispatch_tc(*p, masked, stats, load_v, dyn, s);
+  // the tensor-core kernel: D = 128, and D = 64 except with write_p (the fp16 P of the two-pass
+  // V-skip is written by the D = 128 instantiation and by the exact-order kernels only)
+  if (path != 1 && D == 128) return dispatch_tc<128>(*p, masked, stats, load_v, dyn, s);
+  if (path != 1 && D == 64 && !p->p_out) {
+    if (dyn.xa.R > 0) return fail(KVSKIP_E_ARG, "the exchange inside the kernel exists for D = 128");
+    return dispatch_tc<64>(*p, masked, stats, load_v, dyn, s);
+  }
   if (dyn.t_dev || dyn.pages)
-    return fail(KVSKIP_E_ARG,
-                "a device-resident length or a paged cache needs the tensor-core path (D = 128, decode_path != 1)");
-  if (path == 2) return fail(KVSKIP_E_ARG, "the tensor-core path exists for D = 128 only");
+    return fail(KVSKIP_E_ARG, "a device-resident length or a paged cache needs the tensor-core path (decode_path != 1)");
+  if (path == 2) return fail(KVSKIP_E_ARG, "the tensor-core path does not write P for D = 64");
   return D == 128 ? dispatch_exact<128>(*p, masked, stats, load_v, s) : dispatch_exact<64>(*p, masked, stats, load_v, s);
 }
 }  // namespace

@@ -177,7 +177,8 @@ def decode(q, k, v, scale: float, *, plan: Plan | None = None, stats: bool = Fal
     if num_splits is None:
         n_items = math.ceil(T / TILE) if plan is None else plan.max_cnt
         # the tensor-core kernel owns an SM; three CTAs of the exact-order kernel share one
-        per_sm = 1 if (q.shape[-1] == 128 and ext().get_option("decode_path") != 1) else 3
+        tc = q.shape[-1] == 128 or (q.shape[-1] == 64 and not write_p)
+        per_sm = 1 if (tc and ext().get_option("decode_path") != 1) else 3
         if plan is not None and per_sm == 1 and plan.max_cnt == plan.nb and load_v:
             num_splits = splits_for_unsynced_plan(B * Hkv, n_items)
         else:

@@ -143,3 +143,57 @@ def test_long_context_planner_beyond_3072_blocks(path):
     okq = ok.repeat_interleave(4, dim=1)
     assert torch.allclose(s["lse_att"].cpu()[okq], c["lse_att"][okq], rtol=1e-5, atol=1e-5)
     assert K.ext().device_status() == 0
+
+
+@pytest.mark.parametrize("T,B,splits", [(1000, 2, None), (33, 2, 3), (4096 + 17, 1, 7), (65, 3, 1), (20000, 4, None)])
+def test_head_dim_64_on_the_tensor_core_path(T, B, splits, path):
+    """D = 64 (half-size stages, two per consumer warp): dense, statistics, statistics only, block
+    lists, device-resident length and paged cache against the CPU oracle."""
+    if path == "exact":
+        pytest.skip("this test is about the tensor-core instantiation")
+    from kvskip_b200.cache import PagedKV
+    q, k, v, scale = synth.sink_case(60 + T, B, T, D=64)
+    qc, kc, vc = q.to(DEV), k.to(DEV), v.to(DEV)
+    nb = math.ceil(T / 64)
+    ref = oracle.decode_f64(q, k, v, scale, stats=True)
+    r = K.decode(qc, kc, vc, scale, stats=True, out_f32=True, num_splits=splits)
+    assert rel_err(r["out"], ref["out"]) < TOL_BF16 and rel_err(r["out_f32"], ref["out"]) < TOL_F32
+    assert torch.allclose(r["lse"].double().cpu(), ref["lse"], rtol=0, atol=2e-4)
+    assert torch.allclose(r["blk_max"].double().cpu(), ref["blk_max"], rtol=0, atol=1e-4)      # nats; scores reach +-30
+    assert torch.allclose(r["blk_sum"].double().cpu(), ref["blk_sum"], rtol=2e-4, atol=1e-6)
+    so = K.decode(qc, kc, vc, scale, stats=True, load_v=False, num_splits=splits)
+    assert torch.equal(so["blk_max"], r["blk_max"]) and torch.equal(so["blk_sum"], r["blk_sum"])
+    d = K.decode(qc, kc, vc, scale, out_f32=True, num_splits=splits)
+    assert rel_err(d["out_f32"], ref["out"]) < TOL_F32
+    # block lists (one empty)
+    keep = torch.rand(B, 8, nb, generator=torch.Generator().manual_seed(T)) < 0.5
+    keep[..., 0] = True
+    keep[..., -1] = True
+    keep[B - 1, 5] = False
+    bi, bc = synth.keep_to_plan(keep)
+    refm = oracle.decode_f64(q, k, v, scale, bi, bc)
+    m = K.decode(qc, kc, vc, scale, plan=K.make_plan(keep.to(DEV)), stats=True, out_f32=True, num_splits=splits)
+    live = bc.repeat_interleave(4, dim=1) > 0
+    assert float((m["out_f32"].double().cpu() - refm["out"])[live].norm() / refm["out"][live].norm()) < TOL_F32
+    assert torch.isinf(m["lse"].cpu()[~live]).all()
+    assert torch.equal(torch.isfinite(m["blk_max"]).cpu(), keep.repeat_interleave(4, dim=1))
+    # device-resident length (cache tail poisoned) and paged cache: same bits as the plain launch
+    cap = nb * 64 + 128
+    kbig = torch.full((B, 8, cap, 64), float("nan"), dtype=torch.bfloat16, device=DEV)
+    vbig = torch.full((B, 8, cap, 64), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kbig[:, :, :T], vbig[:, :, :T] = kc, vc
+    t_dev = torch.tensor([T], dtype=torch.int32, device=DEV)
+    ns = d["num_splits"]
+    dd = K.decode(qc, kbig, vbig, scale, out_f32=True, num_splits=ns, t_dev=t_dev)
+    assert torch.equal(dd["out_f32"], d["out_f32"]) and torch.equal(dd["lse"], d["lse"])
+    pg = PagedKV(B * (cap // 64) + 3, B, 8, 64, cap, DEV, order="shuffled", seed=T)
+    pg.k.fill_(float("nan"))
+    pg.v.fill_(float("nan"))
+    pg.write(kc, vc)
+    if T % 64:
+        last = pg.table[:, nb - 1].long()
+        pg.k[last, :, T % 64:] = float("nan")
+        pg.v[last, :, T % 64:] = float("nan")
+    dp = K.decode(qc, pg.k, pg.v, scale, out_f32=True, num_splits=ns, page_table=pg.table, seq_len=T)
+    assert torch.equal(dp["out_f32"], d["out_f32"]) and torch.equal(dp["lse"], d["lse"])
+    assert K.ext().device_status() == 0
