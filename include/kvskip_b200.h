@@ -242,6 +242,15 @@ int kvskip_launch_update_dyn(const kvskip_update_params* p, const int* t_dev, vo
 int kvskip_launch_index_blocks_dyn(const int64_t* ids, int64_t ids_stride, int n, int T_bound, const int* t_dev,
                                    uint8_t* out, int NBC, void* stream);
 int kvskip_launch_advance(int* t_dev, int delta, void* stream);
+/* The V-skip entry points with the length on the device (tensor-core path, D = 128): the single
+ * pass, the second pass of the two-pass form, and the selection between its passes (T_bound sizes
+ * the rows of blk_max / blk_sum / keep / block_idx / weight: ceil(T_bound / 64) blocks; entries of
+ * keep and weight beyond the current length are written as zero). */
+int kvskip_launch_vskip1_dyn(const kvskip_params* p, int D, int G, const int* t_dev, void* stream);
+int kvskip_launch_pv_dyn(const kvskip_params* p, int D, int G, const int* t_dev, void* stream);
+int kvskip_launch_select_dyn(const float* blk_max, const float* blk_sum, int B, int Hkv, int T_bound, const int* t_dev,
+                             int rule, float value, int local, uint8_t* keep, int32_t* block_idx, int32_t* block_cnt,
+                             float* weight, void* stream);
 
 /* Block selection between the two passes of the two-pass V-skip, in one launch (the reference's
  * caller does it with torch ops: kernels/kvskip.py:122-147 select_blocks, :165-177, :70-85

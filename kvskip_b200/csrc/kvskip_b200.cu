@@ -346,7 +346,7 @@ int launch_vskip1_tc(const kvskip_params& p, const DynArgs& dyn, cudaStream_t st
   if (p.num_splits > 1)
     if (int rc = split_done_region(p.B * p.Hkv, stream, &done)) return rc;
   KVB_CUDA(launch_overlapped(kernel, dim3(p.num_splits, p.Hkv, p.B), dim3(kvb::TC_THREADS),
-                             kvb::Vs1TcCfg::kSmemBytes, stream, p, maps, done, dyn.pages, dyn.max_pages));
+                             kvb::Vs1TcCfg::kSmemBytes, stream, p, maps, done, dyn.pages, dyn.max_pages, dyn.t_dev));
   if (p.num_splits > 1 && done == nullptr) {
     kvb::merge_kernel<128><<<p.B * p.Hq, 128, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits,
                                                           static_cast<int64_t>(p.B) * p.Hq, true, p.out, p.out_f32,
@@ -356,7 +356,7 @@ int launch_vskip1_tc(const kvskip_params& p, const DynArgs& dyn, cudaStream_t st
   return KVSKIP_OK;
 }
 
-int launch_pv_tc(const kvskip_params& p, cudaStream_t stream) {
+int launch_pv_tc(const kvskip_params& p, const int* t_dev, cudaStream_t stream) {
   auto kernel = kvb::pv_tc_kernel;
   if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), kvb::PvTcCfg::kSmemBytes)) return rc;
   kvb::TmaMaps maps;
@@ -367,7 +367,7 @@ int launch_pv_tc(const kvskip_params& p, cudaStream_t stream) {
   if (p.num_splits > 1)
     if (int rc = split_done_region(p.B * p.Hkv, stream, &done)) return rc;
   KVB_CUDA(launch_overlapped(kernel, dim3(p.num_splits, p.Hkv, p.B), dim3(kvb::TC_THREADS), kvb::PvTcCfg::kSmemBytes,
-                             stream, p, maps, done));
+                             stream, p, maps, done, t_dev));
   if (p.num_splits > 1 && done == nullptr) {
     kvb::sum_splits_kernel<128><<<p.B * p.Hq, 128, 0, stream>>>(p);
     KVB_CUDA(cudaGetLastError());
@@ -590,6 +590,18 @@ int kvskip_launch_vskip1(const kvskip_params* p, int D, int G, void* stream) {
   return D == 128 ? launch_vskip1_t<128>(*p, s) : launch_vskip1_t<64>(*p, s);
 }
 
+int kvskip_launch_vskip1_dyn(const kvskip_params* p, int D, int G, const int* t_dev, void* stream) {
+  if (int rc = check_common(p, D, G)) return rc;
+  if (!t_dev) return fail(KVSKIP_E_ARG, "t_dev is null");
+  if (!p->out || !p->lse) return fail(KVSKIP_E_ARG, "out and lse are required");
+  if (p->num_splits > 1 && (!p->part_ml || !p->part_acc)) return fail(KVSKIP_E_ARG, "num_splits > 1 needs scratch");
+  if (D != 128 || g_decode_path.load(std::memory_order_relaxed) == 1)
+    return fail(KVSKIP_E_ARG, "a device-resident length needs the tensor-core path (D = 128, decode_path != 1)");
+  DynArgs dyn;
+  dyn.t_dev = t_dev;
+  return launch_vskip1_tc(*p, dyn, static_cast<cudaStream_t>(stream));
+}
+
 int kvskip_launch_vskip1_paged(const kvskip_params* p, int D, int G, const int32_t* page_table, int max_pages,
                                int num_pages, void* stream) {
   if (int rc = check_common(p, D, G)) return rc;
@@ -606,14 +618,24 @@ int kvskip_launch_vskip1_paged(const kvskip_params* p, int D, int G, const int32
   return launch_vskip1_tc(*p, dyn, static_cast<cudaStream_t>(stream));
 }
 
-int kvskip_launch_pv(const kvskip_params* p, int D, int G, void* stream) {
+namespace {
+int pv_impl(const kvskip_params* p, int D, int G, const int* t_dev, void* stream) {
   if (int rc = check_common(p, D, G)) return rc;
   if (!p->p_in || !p->blk_scale || !p->block_idx || !p->block_cnt || !p->out)
     return fail(KVSKIP_E_ARG, "pv needs p_in, blk_scale, block_idx, block_cnt, out");
   if (p->num_splits > 1 && !p->part_acc) return fail(KVSKIP_E_ARG, "num_splits > 1 needs part_acc scratch");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (D == 128 && g_decode_path.load(std::memory_order_relaxed) != 1) return launch_pv_tc(*p, s);
+  if (D == 128 && g_decode_path.load(std::memory_order_relaxed) != 1) return launch_pv_tc(*p, t_dev, s);
+  if (t_dev) return fail(KVSKIP_E_ARG, "a device-resident length needs the tensor-core path (D = 128, decode_path != 1)");
   return D == 128 ? launch_pv_t<128>(*p, s) : launch_pv_t<64>(*p, s);
+}
+}  // namespace
+
+int kvskip_launch_pv(const kvskip_params* p, int D, int G, void* stream) { return pv_impl(p, D, G, nullptr, stream); }
+
+int kvskip_launch_pv_dyn(const kvskip_params* p, int D, int G, const int* t_dev, void* stream) {
+  if (!t_dev) return fail(KVSKIP_E_ARG, "t_dev is null");
+  return pv_impl(p, D, G, t_dev, stream);
 }
 
 namespace {
@@ -833,9 +855,10 @@ int kvskip_launch_append(uint16_t* k, uint16_t* v, int64_t sb, int64_t sh, int64
   return KVSKIP_OK;
 }
 
-int kvskip_launch_select(const float* blk_max, const float* blk_sum, int B, int Hkv, int nb, int rule, float value,
-                         int local, uint8_t* keep, int32_t* block_idx, int32_t* block_cnt, float* weight,
-                         void* stream) {
+namespace {
+int select_impl(const float* blk_max, const float* blk_sum, int B, int Hkv, int nb, int rule, float value, int local,
+                uint8_t* keep, int32_t* block_idx, int32_t* block_cnt, float* weight, const int* t_dev, int T_bound,
+                void* stream) {
   if (!blk_max || !blk_sum || !keep || !block_idx || !block_cnt || !weight || B < 1 || Hkv < 1 || nb < 1)
     return fail(KVSKIP_E_ARG, "select: bad arguments");
   if (rule != 0 && rule != 1) return fail(KVSKIP_E_ARG, "select: rule 0 (top-p) or 1 (tau)");
@@ -846,8 +869,24 @@ int kvskip_launch_select(const float* blk_max, const float* blk_sum, int B, int 
     if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::select_kernel), 220 * 1024)) return rc;
   KVB_CUDA(launch_overlapped(kvb::select_kernel, dim3(Hkv, B), dim3(kvb::PL_THREADS), smem,
                              static_cast<cudaStream_t>(stream), blk_max, blk_sum, nb, Hkv, rule, value, local, keep,
-                             block_idx, block_cnt, weight));
+                             block_idx, block_cnt, weight, t_dev, T_bound));
   return KVSKIP_OK;
+}
+}  // namespace
+
+int kvskip_launch_select(const float* blk_max, const float* blk_sum, int B, int Hkv, int nb, int rule, float value,
+                         int local, uint8_t* keep, int32_t* block_idx, int32_t* block_cnt, float* weight,
+                         void* stream) {
+  return select_impl(blk_max, blk_sum, B, Hkv, nb, rule, value, local, keep, block_idx, block_cnt, weight, nullptr, 0,
+                     stream);
+}
+
+int kvskip_launch_select_dyn(const float* blk_max, const float* blk_sum, int B, int Hkv, int T_bound, const int* t_dev,
+                             int rule, float value, int local, uint8_t* keep, int32_t* block_idx, int32_t* block_cnt,
+                             float* weight, void* stream) {
+  if (!t_dev || T_bound < 1) return fail(KVSKIP_E_ARG, "select: t_dev and T_bound >= 1");
+  return select_impl(blk_max, blk_sum, B, Hkv, (T_bound + KVSKIP_TILE - 1) / KVSKIP_TILE, rule, value, local, keep,
+                     block_idx, block_cnt, weight, t_dev, T_bound, stream);
 }
 
 int kvskip_launch_advance(int* t_dev, int delta, void* stream) {

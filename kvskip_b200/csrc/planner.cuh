@@ -486,31 +486,35 @@ __global__ void __launch_bounds__(256) index_blocks_kernel(const int64_t* __rest
 // keep u8 [B,Hkv,nb], the ascending block list and its length, and for the second pass the
 // weights exp(blk_max - lse_kept) [B,Hkv,nb,4] (0 on blocks not kept), lse_kept = log-sum-exp of
 // x over the kept set.
+// With a device-resident length (t_dev != nullptr, T_bound its bound) nbs = ceil(T_bound / 64) stays
+// the row stride of every array and the selection runs over the blocks of the current length.
 __global__ void __launch_bounds__(PL_THREADS) select_kernel(const float* __restrict__ blk_max,
-                                                            const float* __restrict__ blk_sum, const int nb,
+                                                            const float* __restrict__ blk_sum, const int nbs,
                                                             const int Hkv, const int rule, const float value,
                                                             const int local, uint8_t* __restrict__ keep,
                                                             int32_t* __restrict__ block_idx,
                                                             int32_t* __restrict__ block_cnt,
-                                                            float* __restrict__ weight) {
+                                                            float* __restrict__ weight,
+                                                            const int* __restrict__ t_dev, const int T_bound) {
   const int h = blockIdx.x, b = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int64_t bh = static_cast<int64_t>(b) * Hkv + h;
   const int64_t hrow = bh * PL_G + warp;
   extern __shared__ float sel_smem[];
-  float* x = sel_smem + warp * nb;
-  float* ey = sel_smem + (PL_G + warp) * nb;
-  uint8_t* skeep = reinterpret_cast<uint8_t*>(sel_smem + 2 * PL_G * nb);
+  float* x = sel_smem + warp * nbs;
+  float* ey = sel_smem + (PL_G + warp) * nbs;
+  uint8_t* skeep = reinterpret_cast<uint8_t*>(sel_smem + 2 * PL_G * nbs);
   __shared__ int scan[PL_THREADS];
   pdl_wait_prior();          // the statistics come from the kernel before this one
   pdl_launch_dependents();
+  const int nb = t_dev ? (max(1, min(*t_dev, T_bound)) + TILE - 1) / TILE : nbs;   // blocks of the current length
 
   const bool in_regs = nb <= 64 * 32;     // the bisection keeps its values in registers: ey[] is free
   float mx = -INFINITY;
 #pragma unroll 16
   for (int i = lane; i < nb; i += 32) {
-    const float bm = blk_max[hrow * nb + i];
-    const float val = bm + __logf(blk_sum[hrow * nb + i]);
+    const float bm = blk_max[hrow * nbs + i];
+    const float val = bm + __logf(blk_sum[hrow * nbs + i]);
     x[i] = val;
     if (in_regs) ey[i] = bm;              // block maxima for the weights, no second trip to global memory
     mx = fmaxf(mx, val);
@@ -542,10 +546,11 @@ __global__ void __launch_bounds__(PL_THREADS) select_kernel(const float* __restr
   const float S = warp_sum(s2 > 0.f ? s2 * __expf(m2 - M) : 0.f);
   const float lse_kept = M + __logf(S);
   for (int i = lane; i < nb; i += 32)
-    weight[(bh * nb + i) * PL_G + warp] =
-        skeep[i] ? __expf((in_regs ? ey[i] : blk_max[hrow * nb + i]) - lse_kept) : 0.f;
-  for (int i = tid; i < nb; i += PL_THREADS) keep[bh * nb + i] = skeep[i];
-  pl_compact(nb, block_idx + bh * nb, block_cnt + bh, scan, [&](int i) { return skeep[i] != 0; });
+    weight[(bh * nbs + i) * PL_G + warp] =
+        skeep[i] ? __expf((in_regs ? ey[i] : blk_max[hrow * nbs + i]) - lse_kept) : 0.f;
+  for (int i = tid; i < nbs; i += PL_THREADS) keep[bh * nbs + i] = i < nb ? skeep[i] : 0;
+  for (int i = nb + lane; i < nbs; i += 32) weight[(bh * nbs + i) * PL_G + warp] = 0.f;
+  pl_compact(nb, block_idx + bh * nbs, block_cnt + bh, scan, [&](int i) { return skeep[i] != 0; });
 }
 
 // The new token's K and V rows into the cache: grid (Hkv, B) x D/8 threads, 16 bytes per thread

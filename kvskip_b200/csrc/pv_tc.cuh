@@ -18,7 +18,8 @@ namespace kvb {
 using PvTcCfg = TcCfg<TC_CONSUMERS, false>;   // 12 stages of one V block (16 KB)
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
-pv_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* __restrict__ split_done) {
+pv_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* __restrict__ split_done,
+             const int* __restrict__ t_dev) {
   using Cfg = PvTcCfg;
   constexpr int G = 4, D = 128, NC = TC_CONSUMERS;
   constexpr int S = Cfg::kStages;
@@ -44,6 +45,7 @@ pv_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* _
   pdl_wait_prior();          // P, the block weights and the list come from earlier work on the stream
   pdl_launch_dependents();
 
+  const int T = t_dev ? max(1, min(*t_dev, p.T)) : p.T;   // device-resident length: p.T is its bound
   const int n_items = p.block_cnt[b * p.Hkv + h];
   const int32_t* list = p.block_idx + static_cast<int64_t>(b * p.Hkv + h) * p.max_blocks;
   const int per = (n_items + p.num_splits - 1) / p.num_splits;
@@ -94,8 +96,8 @@ pv_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* _
             if (head < G) {
               const __half2 hh = *reinterpret_cast<const __half2*>(pin + t0 + tok);
               // P beyond T is not defined (the statistics pass never wrote it): those weights are zero
-              w0 = (t0 + tok < p.T) ? __half2float(__low2half(hh)) * f : 0.f;
-              w1 = (t0 + tok + 1 < p.T) ? __half2float(__high2half(hh)) * f : 0.f;
+              w0 = (t0 + tok < T) ? __half2float(__low2half(hh)) * f : 0.f;
+              w1 = (t0 + tok + 1 < T) ? __half2float(__high2half(hh)) * f : 0.f;
             }
             const uint32_t hi = pack_bf16(w0, w1);
             bhi[kt][e] = hi;
@@ -104,6 +106,17 @@ pv_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* _
       }
       if (!mbar_wait(&full[s], (i / S) & 1, 0x430u + s)) break;
       const uint32_t vbase = smem_u32(ring + s * Cfg::kStageBytes);
+      if (t_dev != nullptr && t0 + TILE > T) {
+        // device-resident length: the map reaches past T, where the cache holds anything (their
+        // weights are zero, but 0 x NaN is not): clear those rows of both halves
+        unsigned char* vst = ring + s * Cfg::kStageBytes;
+        for (int o = (T - t0) * 128 + lane * 16; o < TILE * 128; o += 32 * 16) {
+          *reinterpret_cast<uint4*>(vst + o) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(vst + TC_HALF_BYTES + o) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        fence_proxy_async_smem();   // ordered before the next bulk load into this stage
+        __syncwarp();
+      }
 #pragma unroll
       for (int kt = 0; kt < 4; ++kt) {
         const int tok = kt * 16 + (lmat >> 1) * 8 + lrow;

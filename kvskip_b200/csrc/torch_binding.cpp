@@ -226,7 +226,7 @@ std::vector<at::Tensor> decode_exchange(const at::Tensor& q, const at::Tensor& k
 // Two-pass V-skip, second pass: [out bf16, out_f32 or undefined]
 std::vector<at::Tensor> pv(const at::Tensor& P, const at::Tensor& v, const at::Tensor& blk_scale,
                            const at::Tensor& block_idx, const at::Tensor& block_cnt, int64_t num_splits,
-                           bool want_f32) {
+                           bool want_f32, const c10::optional<at::Tensor>& t_dev) {
   need_kv(v, "v");
   TORCH_CHECK(P.is_cuda() && P.scalar_type() == at::kHalf && P.dim() == 3 && P.is_contiguous(), "P: fp16 [B, Hq, t_pad]");
   TORCH_CHECK(blk_scale.is_cuda() && blk_scale.scalar_type() == at::kFloat && blk_scale.dim() == 4 &&
@@ -264,7 +264,10 @@ std::vector<at::Tensor> pv(const at::Tensor& P, const at::Tensor& v, const at::T
   p.t_pad = nb * KVSKIP_TILE;
   p.p_in = u16(P);
   p.blk_scale = blk_scale.data_ptr<float>();
-  raise_on(kvskip_launch_pv(&p, static_cast<int>(D), static_cast<int>(G), cur_stream()));
+  if (const int* td = tdev_ptr(t_dev))
+    raise_on(kvskip_launch_pv_dyn(&p, static_cast<int>(D), static_cast<int>(G), td, cur_stream()));
+  else
+    raise_on(kvskip_launch_pv(&p, static_cast<int>(D), static_cast<int>(G), cur_stream()));
   return {out, out32};
 }
 
@@ -272,10 +275,12 @@ std::vector<at::Tensor> pv(const at::Tensor& P, const at::Tensor& v, const at::T
 std::vector<at::Tensor> vskip1(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double scale,
                                double tau, int64_t local, int64_t num_splits, bool want_f32, bool count,
                                const c10::optional<at::Tensor>& lse_prev,
-                               const c10::optional<at::Tensor>& page_table, int64_t seq_len) {
+                               const c10::optional<at::Tensor>& page_table, int64_t seq_len,
+                               const c10::optional<at::Tensor>& t_dev) {
   need_q(q);
   need_kv(k, "k");
   need_kv(v, "v");
+  TORCH_CHECK(!(t_dev.has_value() && page_table.has_value()), "vskip1: a device-resident length or a paged cache, not both");
   TORCH_CHECK(tau > 0.0 && local >= 0 && num_splits >= 1, "tau > 0, local >= 0, num_splits >= 1");
   const c10::cuda::CUDAGuard guard(q.device());
   const int64_t B = q.size(0), Hq = q.size(1), D = q.size(2), Hkv = k.size(1);
@@ -318,6 +323,8 @@ std::vector<at::Tensor> vskip1(const at::Tensor& q, const at::Tensor& k, const a
   if (pg.table)
     raise_on(kvskip_launch_vskip1_paged(&p, static_cast<int>(D), static_cast<int>(Hq / Hkv), pg.table, pg.max_pages,
                                         pg.num_pages, cur_stream()));
+  else if (const int* td = tdev_ptr(t_dev))
+    raise_on(kvskip_launch_vskip1_dyn(&p, static_cast<int>(D), static_cast<int>(Hq / Hkv), td, cur_stream()));
   else
     raise_on(kvskip_launch_vskip1(&p, static_cast<int>(D), static_cast<int>(Hq / Hkv), cur_stream()));
   return {out, lse, out32, vcount};
@@ -593,7 +600,7 @@ void append(at::Tensor& k, at::Tensor& v, const at::Tensor& k_new, const at::Ten
 
 // Block selection of the two-pass V-skip on the device: [keep u8 [B,Hkv,nb], block_idx, block_cnt, weight [B,Hkv,nb,4]]
 std::vector<at::Tensor> select_dev(const at::Tensor& blk_max, const at::Tensor& blk_sum, int64_t rule, double value,
-                               int64_t local) {
+                               int64_t local, const c10::optional<at::Tensor>& t_dev, int64_t T_bound) {
   need_f32(blk_max, "blk_max"); need_f32(blk_sum, "blk_sum");
   TORCH_CHECK(blk_max.dim() == 3 && blk_max.sizes() == blk_sum.sizes() && blk_max.size(1) % 4 == 0,
               "blk_max, blk_sum: fp32 [B, 4*Hkv, nb]");
@@ -603,6 +610,14 @@ std::vector<at::Tensor> select_dev(const at::Tensor& blk_max, const at::Tensor& 
   at::Tensor bi = at::empty({B, Hkv, nb}, blk_max.options().dtype(at::kInt));
   at::Tensor bc = at::empty({B, Hkv}, blk_max.options().dtype(at::kInt));
   at::Tensor w = at::empty({B, Hkv, nb, 4}, blk_max.options());
+  if (const int* td = tdev_ptr(t_dev)) {
+    TORCH_CHECK((T_bound + KVSKIP_TILE - 1) / KVSKIP_TILE == nb, "select: T_bound must match the rows of blk_max");
+    raise_on(kvskip_launch_select_dyn(blk_max.data_ptr<float>(), blk_sum.data_ptr<float>(), static_cast<int>(B),
+                                      static_cast<int>(Hkv), static_cast<int>(T_bound), td, static_cast<int>(rule),
+                                      static_cast<float>(value), static_cast<int>(local), keep.data_ptr<uint8_t>(),
+                                      bi.data_ptr<int32_t>(), bc.data_ptr<int32_t>(), w.data_ptr<float>(), cur_stream()));
+    return {keep, bi, bc, w};
+  }
   raise_on(kvskip_launch_select(blk_max.data_ptr<float>(), blk_sum.data_ptr<float>(), static_cast<int>(B),
                                 static_cast<int>(Hkv), static_cast<int>(nb), static_cast<int>(rule),
                                 static_cast<float>(value), static_cast<int>(local), keep.data_ptr<uint8_t>(),
@@ -655,14 +670,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("vskip1", &vskip1, "single-pass V-skip", py::arg("q"), py::arg("k"), py::arg("v"), py::arg("scale"),
         py::arg("tau"), py::arg("local") = 2, py::arg("num_splits") = 1, py::arg("want_f32") = false,
         py::arg("count") = false, py::arg("lse_prev") = py::none(), py::arg("page_table") = py::none(),
-        py::arg("seq_len") = 0);
+        py::arg("seq_len") = 0, py::arg("t_dev") = py::none());
   m.def("decode", &decode, "split-K decode attention", py::arg("q"), py::arg("k"), py::arg("v"), py::arg("scale"),
         py::arg("block_idx") = py::none(), py::arg("block_cnt") = py::none(), py::arg("stats") = false,
         py::arg("load_v") = true, py::arg("num_splits") = 1, py::arg("stages") = 2, py::arg("want_f32") = false,
         py::arg("write_p") = false, py::arg("t_dev") = py::none(), py::arg("page_table") = py::none(),
         py::arg("seq_len") = 0);
   m.def("pv", &pv, "two-pass V-skip, pass 2", py::arg("P"), py::arg("v"), py::arg("blk_scale"), py::arg("block_idx"),
-        py::arg("block_cnt"), py::arg("num_splits") = 1, py::arg("want_f32") = false);
+        py::arg("block_cnt"), py::arg("num_splits") = 1, py::arg("want_f32") = false, py::arg("t_dev") = py::none());
   m.def("refresh_step", &refresh_step, "plan -> masked+stats attention -> update for one layer, one call",
         py::arg("q"), py::arg("k"), py::arg("v"), py::arg("csum"), py::arg("lse_ref"), py::arg("cs_ref"),
         py::arg("keep"), py::arg("lse_att"), py::arg("age"), py::arg("flags"), py::arg("cs_now"), py::arg("trig"),
@@ -688,7 +703,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("v"), py::arg("k_new"), py::arg("v_new"), py::arg("T"), py::arg("t_dev") = py::none(),
         py::arg("page_table") = py::none());
   m.def("select", &select_dev, "two-pass V-skip: block selection, list and second-pass weights in one launch",
-        py::arg("blk_max"), py::arg("blk_sum"), py::arg("rule"), py::arg("value"), py::arg("local") = 2);
+        py::arg("blk_max"), py::arg("blk_sum"), py::arg("rule"), py::arg("value"), py::arg("local") = 2,
+        py::arg("t_dev") = py::none(), py::arg("T_bound") = 0);
   m.def("advance", &advance, "device-resident sequence length += delta, in stream order", py::arg("t_dev"),
         py::arg("delta") = 1);
   m.def("set_option", &set_option, "process-wide option, e.g. (\"decode_path\", 1) for the exact-order kernels",

@@ -22,7 +22,7 @@ struct Vs1TcCfg {
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
 vskip1_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* __restrict__ split_done,
-                 const int32_t* __restrict__ pages, const int max_pages) {
+                 const int32_t* __restrict__ pages, const int max_pages, const int* __restrict__ t_dev) {
   constexpr int G = 4, D = 128;
   constexpr int NC = TC_CONSUMERS;
   extern __shared__ unsigned char smem_raw[];
@@ -39,10 +39,6 @@ vskip1_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
 
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int nb = (p.T + TILE - 1) / TILE;
-  const int per = (nb + p.num_splits - 1) / p.num_splits;
-  const int i0 = min(nb, split * per);
-  const int n = min(nb, i0 + per) - i0;
   const bool sink_rule = p.lse_prev == nullptr;
 
   if (tid == 0) {
@@ -59,6 +55,12 @@ vskip1_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
   __syncthreads();
   pdl_wait_prior();          // nothing written by the previous kernel on the stream is read above
   pdl_launch_dependents();
+  // the length: p.T, or the value at t_dev (p.T is then the bound the grid and the maps were sized for)
+  const int T = t_dev ? max(1, min(*t_dev, p.T)) : p.T;
+  const int nb = (T + TILE - 1) / TILE;
+  const int per = (nb + p.num_splits - 1) / p.num_splits;
+  const int i0 = min(nb, split * per);
+  const int n = min(nb, i0 + per) - i0;
   // contiguous cache: rows blk*64.. of sequence b; paged cache (pages != nullptr): the whole page
   // the table names for block blk -- the maps then run over the page pool
   auto row_of = [&](int blk) { return pages ? 0 : blk * TILE; };
@@ -98,13 +100,13 @@ vskip1_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
         mma_bf16(sc[mt], a, bq[ks][0], bq[ks][1]);
       }
     }
-    const bool ragged = t0 + TILE > p.T;
+    const bool ragged = t0 + TILE > T;
 #pragma unroll
     for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         float v = sc[mt][c] * p.scale_log2;
-        if (ragged && t0 + mt * 16 + (lane >> 2) + (c >> 1) * 8 >= p.T) v = -INFINITY;
+        if (ragged && t0 + mt * 16 + (lane >> 2) + (c >> 1) * 8 >= T) v = -INFINITY;
         sc[mt][c] = v;
       }
   };
@@ -186,7 +188,7 @@ vskip1_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
 
     auto retire = [&]() {           // acc = alpha * acc + V^T P^T for the pending block
       if (!mbar_wait(&vfull[warp], vphase ^ 1u, 0x360u + warp)) { ok = false; return; }
-      if (pages != nullptr && pend_rows < TILE) {
+      if ((pages != nullptr || t_dev != nullptr) && pend_rows < TILE) {
         // paged cache: the rows of the last page past the sequence hold stale data; their weights
         // are zero but 0 x NaN is not, so clear them (whole 128-byte rows of both halves)
         unsigned char* vb = bufV + warp * Vs1TcCfg::kVBytes;
@@ -275,7 +277,7 @@ vskip1_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
         }
         vphase ^= 1u;                                        // retire() waits for parity vphase ^ 1
         pending = true;
-        pend_rows = min(TILE, p.T - blk * TILE);             // rows of the block that hold tokens
+        pend_rows = min(TILE, T - blk * TILE);               // rows of the block that hold tokens
         ++loaded;
       }
     }

@@ -228,30 +228,36 @@ def select_blocks(logw: torch.Tensor, G: int, rule: str, value: float, local: in
     return per_head.view(B, Hq // G, G, nb).any(2) | always_keep(nb, local, logw.device)
 
 
-def pv(P, v, blk_scale, plan: Plan, num_splits: int | None = None, out_f32: bool = False):
+def pv(P, v, blk_scale, plan: Plan, num_splits: int | None = None, out_f32: bool = False,
+       t_dev: torch.Tensor | None = None):
     if num_splits is None:
         num_splits = num_splits_for(v.shape[0] * v.shape[1], plan.max_cnt)
-    return ext().pv(P, v, blk_scale, plan.block_idx, plan.block_cnt, int(num_splits), out_f32)
+    return ext().pv(P, v, blk_scale, plan.block_idx, plan.block_cnt, int(num_splits), out_f32, t_dev)
 
 
 def vskip_two_pass(q, k, v, scale: float, rule: str = "topp", value: float = 0.99, local: int = 2,
-                   sync: bool = True, out_f32: bool = False, device_select: bool = True) -> dict:
+                   sync: bool = True, out_f32: bool = False, device_select: bool = True,
+                   t_dev: torch.Tensor | None = None) -> dict:
     """Two-pass V-skip: a statistics pass over all of K that also writes P = exp(s - block max) in
     fp16, block selection per GQA union, then a pass over P and V of the selected blocks.
     device_select (not in the reference): the selection between the passes runs as one kernel;
-    False gives the reference's torch formulation (sort + cumulative sum)."""
+    False gives the reference's torch formulation (sort + cumulative sum).
+    t_dev (not in the reference): the length is read on the device by all three launches (k, v are
+    views of the whole provisioned cache, sync must be False): for captured decode steps."""
     q = _q3(q)
     B, Hq, _ = q.shape
     Hkv = k.shape[1]
     G = Hq // Hkv
-    first = decode(q, k, v, scale, stats=True, load_v=False, write_p=True)
+    if t_dev is not None and (sync or not device_select or G != 4):
+        raise ValueError("vskip_two_pass with t_dev: sync=False, device_select=True, G = 4")
+    first = decode(q, k, v, scale, stats=True, load_v=False, write_p=True, t_dev=t_dev)
     if device_select and G == 4 and rule in ("topp", "tau"):
         # selection, block list and second-pass weights in one launch instead of a dozen torch ops
         keep8, bi, bc, weight = ext().select(first["blk_max"], first["blk_sum"], 0 if rule == "topp" else 1,
-                                             float(value), int(local))
+                                             float(value), int(local), t_dev, int(k.shape[2]) if t_dev is not None else 0)
         nb = keep8.shape[-1]
         plan = Plan(bi, bc, int(bc.max()) if sync else nb, nb)
-        out, o32 = pv(first["p"], v, weight, plan, out_f32=out_f32)
+        out, o32 = pv(first["p"], v, weight, plan, out_f32=out_f32, t_dev=t_dev)
         keep = keep8.bool()
         res = {"out": out, "keep": keep, "kept_frac": keep.float().mean().item() if sync else None}
         if out_f32:
@@ -272,13 +278,16 @@ def vskip_two_pass(q, k, v, scale: float, rule: str = "topp", value: float = 0.9
 
 def vskip_one_pass(q, k, v, scale: float, tau: float = 1e-4, local: int = 2, num_splits: int | None = None,
                    out_f32: bool = False, count: bool = False, lse_prev: torch.Tensor | None = None,
-                   sync: bool = True, page_table: torch.Tensor | None = None, seq_len: int | None = None) -> dict:
+                   sync: bool = True, page_table: torch.Tensor | None = None, seq_len: int | None = None,
+                   t_dev: torch.Tensor | None = None) -> dict:
     """Single-pass V-skip: K is read once; the V block of a tile is read only if some query head of
     the group gives the block an estimated weight >= tau.  The normaliser estimate is `lse_prev`
     (per query head, e.g. the "lse" this function returned one step earlier); without it every
     CTA uses the sink block's log-sum-exp, a lower bound that keeps every block the exact rule
     keeps.  count=True adds "v_tiles" [B, Hkv] (and "kept_frac" when sync).
-    page_table with seq_len (not in the reference): k and v are page pools, as in `decode`."""
+    page_table with seq_len (not in the reference): k and v are page pools, as in `decode`.
+    t_dev (not in the reference): the length is read on the device (k, v views of the whole
+    provisioned cache; count with sync=False only): for captured decode steps."""
     q = _q3(q)
     B, Hkv, T = q.shape[0], k.shape[1], k.shape[2]
     if page_table is not None:
@@ -289,7 +298,7 @@ def vskip_one_pass(q, k, v, scale: float, tau: float = 1e-4, local: int = 2, num
     if num_splits is None:
         num_splits = num_splits_for(B * Hkv, nb)
     out, lse, o32, cnt = ext().vskip1(q, k, v, float(scale), float(tau), int(local), int(num_splits),
-                                      out_f32, count, lse_prev, page_table, int(seq_len or 0))
+                                      out_f32, count, lse_prev, page_table, int(seq_len or 0), t_dev)
     _auto_check("vskip_one_pass")
     res = {"out": out, "lse": lse, "num_splits": num_splits}
     if out_f32:

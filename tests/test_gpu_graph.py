@@ -177,3 +177,67 @@ def test_planner_loop_replayed_from_a_graph_matches_launches(name, overlap):
     assert g.replays == steps - 2                        # first step on the host, one eager step
     assert g.captures == (1 if name == "plain" else 2)
     assert K.ext().device_status() == 0
+
+
+@pytest.mark.parametrize("T", [65, 1000, 1471])
+def test_vskip_variants_with_device_length_match_by_value(T):
+    """Single-pass V-skip (both normaliser rules) and the two-pass form (statistics + P pass,
+    selection, P.V pass) with the length read on the device from views of the whole cache, whose
+    tail holds NaN: same bits as the by-value launches on views of the current length."""
+    cap = 1536
+    q, k, v, scale, _ = synth.body_union_case(900 + T, cap)
+    q, k, v = q.to(DEV), _poison_tail(k.to(DEV), T), _poison_tail(v.to(DEV), T)
+    t_dev = torch.tensor([T], dtype=torch.int32, device=DEV)
+    nb = math.ceil(T / 64)
+    kv, vv = k[:, :, :T], v[:, :, :T]
+    lse = K.decode(q, kv, vv, scale)["lse"]
+    for prev in (None, lse):
+        a = K.vskip_one_pass(q, kv, vv, scale, tau=1e-3, out_f32=True, count=True, lse_prev=prev, num_splits=3)
+        b = K.vskip_one_pass(q, k, v, scale, tau=1e-3, out_f32=True, count=True, lse_prev=prev, num_splits=3,
+                             sync=False, t_dev=t_dev)
+        assert torch.equal(a["out_f32"], b["out_f32"]) and torch.equal(a["lse"], b["lse"])
+        assert torch.equal(a["v_tiles"], b["v_tiles"]) and torch.isfinite(b["out_f32"]).all()
+    for rule, value in (("topp", 0.95), ("tau", 1e-3)):
+        a = K.vskip_two_pass(q, kv, vv, scale, rule, value, sync=False, out_f32=True)
+        b = K.vskip_two_pass(q, k, v, scale, rule, value, sync=False, out_f32=True, t_dev=t_dev)
+        # the split counts are sized from the bound here and from the length there: same sums in another order
+        assert torch.isfinite(b["out_f32"]).all()
+        assert float((a["out_f32"] - b["out_f32"]).norm() / a["out_f32"].norm()) < 2e-6
+        assert torch.equal(a["keep"], b["keep"][..., :nb]) and not b["keep"][..., nb:].any()
+    ref = oracle.vskip1_f64(q.cpu(), kv.cpu(), vv.cpu(), scale, tau=1e-3, lse_prev=lse.cpu())
+    border = (ref["margin"].abs() < 1e-3).sum(-1)
+    got = K.vskip_one_pass(q, k, v, scale, tau=1e-3, out_f32=True, count=True, lse_prev=lse, sync=False, t_dev=t_dev)
+    assert ((got["v_tiles"].cpu() - ref["v_tiles"]).abs() <= border).all()
+    if int(border.sum()) == 0:
+        assert float((got["out_f32"].double().cpu() - ref["out"]).norm() / ref["out"].norm()) < 5e-5
+
+
+def test_single_pass_vskip_replayed_from_a_graph():
+    """The vskip1 decode mode as a captured step: append, advance, V-skip with the previous step's
+    normaliser, replayed while the cache grows; equal to the same steps issued one by one."""
+    T0, steps, cap = 700, 12, 1024
+    q, k, v, scale, _ = synth.body_union_case(77, cap)
+    q, k, v = q.to(DEV), k.to(DEV), v.to(DEV)
+    eager, prev = [], None
+    for t in range(steps):
+        T = T0 + t + 1
+        r = K.vskip_one_pass(q, k[:, :, :T], v[:, :, :T], scale, tau=1e-4, lse_prev=prev, num_splits=4)
+        prev = r["lse"]
+        eager.append((r["out"].clone(), r["lse"].clone()))
+    t_dev = torch.tensor([T0], dtype=torch.int32, device=DEV)
+    prev_buf = torch.empty_like(prev)
+    prev_buf.copy_(K.vskip_one_pass(q, k[:, :, :T0 + 1], v[:, :, :T0 + 1], scale, tau=1e-4, num_splits=4)["lse"])
+    K.ext().advance(t_dev, 1)                                  # step 0 done eagerly (no previous normaliser)
+
+    def launch():
+        K.ext().advance(t_dev, 1)
+        r = K.vskip_one_pass(q, k, v, scale, tau=1e-4, lse_prev=prev_buf, num_splits=4, sync=False, t_dev=t_dev)
+        prev_buf.copy_(r["lse"])
+        return r["out"], r["lse"]
+
+    g = StepGraph(launch, eager=1)
+    for t in range(1, steps):
+        out, lse = g.step()
+        assert torch.equal(out, eager[t][0]) and torch.equal(lse, eager[t][1]), t
+    assert g.captures == 1 and g.replays >= steps - 2
+    assert K.ext().device_status() == 0
