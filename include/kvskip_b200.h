@@ -197,23 +197,27 @@ int kvskip_launch_merge_packed(const float* parts, int R, int64_t N, int D, uint
 
 /* Sequence shards, exchange and merge fused in one kernel over peer memory (no collective call).
  * Every rank (one process per GPU, R <= 8) passes its normalised local result (out_f32 [N,D],
- * lse [N]), the R peer-visible addresses of the ranks' exchange buffers (each 2*R*N*(D+2) floats)
- * and flag arrays (each R*N uint32, zero before the first step), its rank, and a step number seq
- * that is the same on every rank and grows by one per call (starting at 1).  Each row is stored
- * into every rank's buffer with plain stores over NVLink, flagged, awaited and merged in ascending
- * rank order; results equal kvskip_launch_merge_packed on the all-gathered buffers bit for bit.
- * The wait is bounded (about a second); on expiry the device status word is set.  All ranks must
- * call it for the same step: a rank that does not shows up as that timeout, not as a hang. */
+ * lse [N]), the R peer-visible addresses of the ranks' exchange buffers, its rank, and a step
+ * number seq that is the same on every rank and grows by one per call (starting at 1).
+ * An exchange buffer holds 2*R*N*(D+2) words of 8 bytes (8-byte aligned, zero before the first
+ * step): a word is (fp32 value, step number), written with one 8-byte store, so the flag travels
+ * with the data and a reader polls the word itself -- no fence, no flag array, one NVLink crossing.
+ * peer_flags is not used and may be null (kept for callers of the earlier flag-array protocol).
+ * Each row is stored into every rank's buffer with plain stores over NVLink, awaited word by word
+ * and merged in ascending rank order; results equal kvskip_launch_merge_packed on the all-gathered
+ * buffers bit for bit.  The wait is bounded ("spin_limit" option, about two seconds by default); on
+ * expiry the device status word is set and the missing rank counts as having read nothing.  All
+ * ranks must call it for the same step: a rank that does not shows up as that timeout, not as a hang. */
 int kvskip_launch_exchange_merge(const float* out_f32, const float* lse, float* const* peer_bufs,
                                  unsigned int* const* peer_flags, int rank, int R, int64_t N, int D, unsigned int seq,
                                  uint16_t* out, float* res_f32, float* res_lse, void* stream);
 
 /* Sequence shards, everything in one kernel: kvskip_launch_decode whose split merge also does the
  * exchange of kvskip_launch_exchange_merge -- the CTA that merges the splits of a (batch, kv head)
- * stores the result as a packed triple into every rank's buffer (plain peer stores), flags its
- * rows, waits (bounded, status word 0x510 + peer) for the peers' flags and merges the R triples in
+ * stores the result as a packed triple into every rank's buffer (plain peer stores of (value, step)
+ * words), waits (bounded, status word 0x510 + peer) for the peers' words and merges the R triples in
  * ascending rank order; p->out / out_f32 / lse receive the result over the whole sequence.  Same
- * buffers, flags, seq convention and bits as kvskip_launch_exchange_merge (N = B * Hq rows).
+ * buffers, seq convention and bits as kvskip_launch_exchange_merge (N = B * Hq rows).
  * Needs num_splits > 1, D = 128 and at most half as many (batch, kv head) pairs as SMs. */
 int kvskip_launch_decode_xchg(const kvskip_params* p, int D, int G, int stages, int masked, int stats,
                               float* const* peer_bufs, unsigned int* const* peer_flags, int rank, int R,

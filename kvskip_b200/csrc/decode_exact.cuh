@@ -355,21 +355,45 @@ __global__ void __launch_bounds__(D) merge_packed_kernel(const float* __restrict
 }
 
 // ---- sequence shards, exchange and merge in one kernel over peer memory ----------------------
-// One process per GPU.  Every rank owns a symmetric buffer [2][R][N][D+2] floats and a flag array
-// [R][N] (uint32), and knows the peers' addresses of both.  Row `row` of this rank's result is
-// packed and stored straight into slot [seq & 1][rank][row] of EVERY rank's buffer (plain stores
-// over NVLink), followed by a system-scope fence and the per-row flag flags[rank][row] = seq on
-// every rank; the same CTA then waits until all R flags of its row on ITS OWN array hold `seq` and
-// merges the R triples from its own buffer in ascending rank order (the arithmetic of
-// merge_packed_kernel, so the bits equal the all-gather path).  Two buffer sets alternate by the
-// parity of seq: a rank can be at most one step ahead of a peer, because finishing a step needs
-// the peer's flags of that step.  The wait is bounded (`spin` polls of about 100 ns each); on expiry
-// the status word is set to 0x500 + peer and the row is written from whatever arrived.
+// One process per GPU.  Every rank owns a symmetric buffer of 8-byte words [2][R][N][D+2] and
+// knows the peers' addresses of theirs.  A word is (value bits, step number): the flag travels with
+// the data in one 8-byte store, which arrives whole, so no fence, no separate flag array and no
+// second round trip are needed -- a reader polls the word itself until it carries the step number
+// it waits for.  Row `row` of this rank's result is packed as [acc(D) | m | l] (acc = out,
+// m = lse / ln 2, l = 1) and stored word by word into slot [seq & 1][rank][row] of EVERY rank's
+// buffer (plain 8-byte stores, over NVLink for the peers); the same CTA then reads the R triples
+// of its row from ITS OWN buffer, waiting for each word, and merges them in ascending rank order
+// (the arithmetic of merge_packed_kernel, so the bits equal the all-gather path).  Two buffer sets
+// alternate by the parity of seq: a rank can be at most one step ahead of a peer, because
+// finishing a step needs the peer's words of that step.  Every wait is bounded (`spin` polls); on
+// expiry the status word is set to 0x500 + peer and that peer counts as having read nothing.
 constexpr int XCHG_MAX_RANKS = 8;
 struct XchgPeers {
-  float* buf[XCHG_MAX_RANKS];
-  unsigned int* flags[XCHG_MAX_RANKS];
+  float* buf[XCHG_MAX_RANKS];            // 8-byte words; declared float* for the C ABI's sake
+  unsigned int* flags[XCHG_MAX_RANKS];   // unused (kept so that the parameter block keeps its shape)
 };
+
+__device__ __forceinline__ void ll_store(float* buf, const int64_t word, const float val, const unsigned int seq) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(reinterpret_cast<uint2*>(buf) + word),
+               "r"(__float_as_uint(val)), "r"(seq)
+               : "memory");
+}
+// Waits until the word carries `seq`; false (and val = 0) after `spin` polls.
+__device__ __forceinline__ bool ll_load(const float* buf, const int64_t word, const unsigned int seq,
+                                        const unsigned int spin, float& val) {
+  const uint2* w = reinterpret_cast<const uint2*>(buf) + word;
+  for (unsigned int it = 0; it < spin; ++it) {
+    unsigned int x, y;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(x), "=r"(y) : "l"(w) : "memory");
+    if (y == seq) {
+      val = __uint_as_float(x);
+      return true;
+    }
+    if (it > 256) __nanosleep(64);
+  }
+  val = 0.f;
+  return false;
+}
 
 template <int D>
 __global__ void __launch_bounds__(D) exchange_merge_kernel(const float* __restrict__ out_f32,
@@ -381,7 +405,8 @@ __global__ void __launch_bounds__(D) exchange_merge_kernel(const float* __restri
   const int64_t row = blockIdx.x;
   const int d = threadIdx.x;
   pdl_wait_prior();
-  const int64_t slot = ((static_cast<int64_t>(seq & 1u) * R + rank) * N + row) * W;
+  const int64_t par = static_cast<int64_t>(seq & 1u) * R;
+  const int64_t slot = ((par + rank) * N + row) * W;
   const float val = out_f32[row * D + d];
   float mval = 0.f, lval = 0.f;
   if (d == 0) {
@@ -390,49 +415,33 @@ __global__ void __launch_bounds__(D) exchange_merge_kernel(const float* __restri
     lval = x == -INFINITY ? 0.f : 1.f;
   }
   for (int r = 0; r < R; ++r) {
-    float* dst = peers.buf[r] + slot;
-    dst[d] = val;
+    ll_store(peers.buf[r], slot + d, val, seq);
     if (d == 0) {
-      dst[D] = mval;
-      dst[D + 1] = lval;
+      ll_store(peers.buf[r], slot + D, mval, seq);
+      ll_store(peers.buf[r], slot + D + 1, lval, seq);
     }
   }
-  __threadfence_system();
-  __syncthreads();
-  if (d < R) {
-    volatile unsigned int* f = peers.flags[d] + static_cast<int64_t>(rank) * N + row;
-    *f = seq;
-  }
-  // wait for the R flags of this row on this rank's own array
-  __shared__ int s_ok;
-  if (d == 0) s_ok = 1;
-  __syncthreads();
-  if (d < R) {
-    const volatile unsigned int* f = peers.flags[rank] + static_cast<int64_t>(d) * N + row;
-    bool got = false;
-    for (uint32_t it = 0; it < spin; ++it) {
-      // ">= seq" in wrap-safe form: a peer that has already gone on to its next step has
-      // overwritten this flag with the next value, which still says that step `seq` arrived
-      if (static_cast<int>(*f - seq) >= 0) { got = true; break; }
-      __nanosleep(100);
-    }
-    if (!got) {
-      s_ok = 0;
-      atomicCAS(&g_status, 0u, 0x500u + d);
-    }
-  }
-  __threadfence_system();
-  __syncthreads();
-  const float* mine = peers.buf[rank] + (static_cast<int64_t>(seq & 1u) * R) * N * W;
+  // the R triples of this row from this rank's own buffer
+  const float* mine = peers.buf[rank];
+  float mr[XCHG_MAX_RANKS], lr[XCHG_MAX_RANKS], ar[XCHG_MAX_RANKS];
   float m = -INFINITY;
-  for (int r = 0; r < R; ++r) m = fmaxf(m, __ldcg(mine + (static_cast<int64_t>(r) * N + row) * W + D));
+  for (int r = 0; r < R; ++r) {
+    const int64_t w0 = ((par + r) * N + row) * W;
+    const bool ok = ll_load(mine, w0 + D, seq, spin, mr[r]) & ll_load(mine, w0 + D + 1, seq, spin, lr[r]) &
+                    ll_load(mine, w0 + d, seq, spin, ar[r]);
+    if (!ok) {
+      atomicCAS(&g_status, 0u, 0x500u + r);
+      mr[r] = -INFINITY;
+      lr[r] = ar[r] = 0.f;
+    }
+    m = fmaxf(m, mr[r]);
+  }
   const float mu = (m == -INFINITY) ? 0.f : m;
   float l = 0.f, acc = 0.f;
   for (int r = 0; r < R; ++r) {
-    const float* pr = mine + (static_cast<int64_t>(r) * N + row) * W;
-    const float w = ex2(__ldcg(pr + D) - mu);
-    l += __ldcg(pr + D + 1) * w;
-    acc += __ldcg(pr + d) * w;
+    const float w = ex2(mr[r] - mu);
+    l += lr[r] * w;
+    acc += ar[r] * w;
   }
   const float o32 = l > 0.f ? acc / l : 0.f;
   if (out) reinterpret_cast<__nv_bfloat16*>(out)[row * D + d] = __float2bfloat16(o32);

@@ -251,9 +251,10 @@ __device__ __forceinline__ void tc_fill_gap(const kvskip_params& p, const int32_
 // Sequence shards: the cross-GPU exchange inside the attention kernel.  With R > 0 the CTA that
 // merges the splits of a (batch, kv head) does not write the result but stores it, as the packed
 // triple (acc = out, m = lse / ln 2, l = 1) of exchange_merge_kernel, into every rank's buffer
-// over NVLink (plain peer stores), flags its four rows, waits -- bounded -- for the peers' flags
-// on its own rank's array and merges the R triples in ascending rank order.  Same buffers, slots,
-// flags and arithmetic as exchange_merge_kernel, so the two give the same bits.
+// over NVLink (plain peer stores of (value, step number) words), then reads the R triples of its
+// rows from its own rank's buffer, waiting -- bounded -- for each word, and merges them in
+// ascending rank order.  Same buffers, slots and arithmetic as exchange_merge_kernel, so the two
+// give the same bits.
 struct XchgArgs {
   XchgPeers peers;
   int rank;
@@ -264,62 +265,55 @@ struct XchgArgs {
 };
 
 // One element of this rank's packed row (acc = out, then m = lse / ln 2 and l = 1) into every
-// rank's buffer: plain stores, to peer memory over NVLink for r != rank.
+// rank's buffer as (value, step number) words: plain 8-byte stores, to peer memory over NVLink for
+// r != rank.
 __device__ __forceinline__ void xchg_store(const XchgArgs& xa, const int64_t hq, const int d, const float o32,
                                            const float lse_nat) {
   constexpr int D = 128, XW = D + 2;
   const int64_t slot = ((static_cast<int64_t>(xa.seq & 1u) * xa.R + xa.rank) * xa.N + hq) * XW;
   for (int r = 0; r < xa.R; ++r) {
-    float* dst = xa.peers.buf[r] + slot;
-    dst[d] = o32;
+    ll_store(xa.peers.buf[r], slot + d, o32, xa.seq);
     if (d == 0) {
-      dst[D] = lse_nat == -INFINITY ? -INFINITY : lse_nat * LOG2E;
-      dst[D + 1] = lse_nat == -INFINITY ? 0.f : 1.f;
+      ll_store(xa.peers.buf[r], slot + D, lse_nat == -INFINITY ? -INFINITY : lse_nat * LOG2E, xa.seq);
+      ll_store(xa.peers.buf[r], slot + D + 1, lse_nat == -INFINITY ? 0.f : 1.f, xa.seq);
     }
   }
 }
 
-// After the four rows of (batch b, kv head h) were stored with xchg_store by this CTA: make them
-// visible system-wide, flag them on every rank, wait -- bounded -- for the peers' flags of the same
-// rows on this rank's own array, and merge the R triples in ascending rank order (the arithmetic of
-// merge_packed_kernel).  Called by every thread of the CTA.
+// After the four rows of (batch b, kv head h) were stored with xchg_store by this CTA: read the R
+// triples of those rows from this rank's own buffer, waiting -- bounded -- for every word to carry
+// this step's number, and merge them in ascending rank order (the arithmetic of
+// merge_packed_kernel).  No fence and no flag: the step number travels inside every word.
+// Called by every thread of the CTA.
 template <int THREADS>
 __device__ __forceinline__ void xchg_finish(const kvskip_params& p, const XchgArgs& xa, const int b, const int h,
                                             const int tid) {
   constexpr int G = 4, D = 128, XW = D + 2;
   const int64_t hq0x = static_cast<int64_t>(b) * p.Hq + h * G;
-  __threadfence_system();       // the rows are visible on every GPU before their flags
-  __syncthreads();
-  if (tid < G * xa.R) {
-    const int g = tid / xa.R, r = tid % xa.R;
-    volatile unsigned int* f = xa.peers.flags[r] + static_cast<int64_t>(xa.rank) * xa.N + hq0x + g;
-    *f = xa.seq;
-  }
-  if (tid < G * xa.R) {         // this rank's copy of the flags of its four rows, one per peer
-    const int g = tid / xa.R, r = tid % xa.R;
-    const volatile unsigned int* f = xa.peers.flags[xa.rank] + static_cast<int64_t>(r) * xa.N + hq0x + g;
-    bool got = false;
-    for (uint32_t it = 0; it < xa.spin; ++it) {
-      if (static_cast<int>(*f - xa.seq) >= 0) { got = true; break; }
-      __nanosleep(100);
-    }
-    if (!got) atomicCAS(&g_status, 0u, 0x510u + r);
-  }
-  __threadfence_system();
-  __syncthreads();
-  const float* mine = xa.peers.buf[xa.rank] + (static_cast<int64_t>(xa.seq & 1u) * xa.R) * xa.N * XW;
+  const float* mine = xa.peers.buf[xa.rank];
+  const int64_t par = static_cast<int64_t>(xa.seq & 1u) * xa.R;
   for (int o = tid; o < G * D; o += THREADS) {
     const int g = o / D, d = o % D;
     const int64_t row = hq0x + g;
+    float mr[XCHG_MAX_RANKS], lr[XCHG_MAX_RANKS], ar[XCHG_MAX_RANKS];
     float m = -INFINITY;
-    for (int r = 0; r < xa.R; ++r) m = fmaxf(m, __ldcg(mine + (static_cast<int64_t>(r) * xa.N + row) * XW + D));
+    for (int r = 0; r < xa.R; ++r) {
+      const int64_t w0 = ((par + r) * xa.N + row) * XW;
+      const bool ok = ll_load(mine, w0 + D, xa.seq, xa.spin, mr[r]) & ll_load(mine, w0 + D + 1, xa.seq, xa.spin, lr[r]) &
+                      ll_load(mine, w0 + d, xa.seq, xa.spin, ar[r]);
+      if (!ok) {
+        atomicCAS(&g_status, 0u, 0x510u + r);
+        mr[r] = -INFINITY;
+        lr[r] = ar[r] = 0.f;
+      }
+      m = fmaxf(m, mr[r]);
+    }
     const float mu = (m == -INFINITY) ? 0.f : m;
     float l = 0.f, acc2 = 0.f;
     for (int r = 0; r < xa.R; ++r) {
-      const float* pr = mine + (static_cast<int64_t>(r) * xa.N + row) * XW;
-      const float w = ex2(__ldcg(pr + D) - mu);
-      l += __ldcg(pr + D + 1) * w;
-      acc2 += __ldcg(pr + d) * w;
+      const float w = ex2(mr[r] - mu);
+      l += lr[r] * w;
+      acc2 += ar[r] * w;
     }
     const float o32 = l > 0.f ? acc2 / l : 0.f;
     reinterpret_cast<__nv_bfloat16*>(p.out)[row * D + d] = __float2bfloat16(o32);

@@ -456,15 +456,16 @@ int kvskip_launch_decode_dyn(const kvskip_params* p, int D, int G, int stages, i
 int kvskip_launch_decode_xchg(const kvskip_params* p, int D, int G, int stages, int masked, int stats,
                               float* const* peer_bufs, unsigned int* const* peer_flags, int rank, int R,
                               unsigned int seq, void* stream) {
-  if (!p || !peer_bufs || !peer_flags) return fail(KVSKIP_E_ARG, "decode_xchg: null argument");
+  if (!p || !peer_bufs) return fail(KVSKIP_E_ARG, "decode_xchg: null argument");
   if (R < 1 || R > kvb::XCHG_MAX_RANKS || rank < 0 || rank >= R)
     return fail(KVSKIP_E_LIMIT, "decode_xchg: 1..%d ranks", kvb::XCHG_MAX_RANKS);
   if (seq == 0) return fail(KVSKIP_E_ARG, "decode_xchg: seq >= 1");
   DynArgs dyn;
   for (int r = 0; r < R; ++r) {
-    if (!peer_bufs[r] || !peer_flags[r]) return fail(KVSKIP_E_ARG, "decode_xchg: null peer pointer");
+    if (!peer_bufs[r] || reinterpret_cast<uintptr_t>(peer_bufs[r]) % 8)
+      return fail(KVSKIP_E_ARG, "decode_xchg: null or misaligned peer buffer");
     dyn.xa.peers.buf[r] = peer_bufs[r];
-    dyn.xa.peers.flags[r] = peer_flags[r];
+    dyn.xa.peers.flags[r] = peer_flags ? peer_flags[r] : nullptr;
   }
   dyn.xa.rank = rank;
   dyn.xa.R = R;
@@ -774,15 +775,16 @@ int kvskip_launch_merge_packed(const float* parts, int R, int64_t N, int D, uint
 int kvskip_launch_exchange_merge(const float* out_f32, const float* lse, float* const* peer_bufs,
                                  unsigned int* const* peer_flags, int rank, int R, int64_t N, int D, unsigned int seq,
                                  uint16_t* out, float* res_f32, float* res_lse, void* stream) {
-  if (!out_f32 || !lse || !peer_bufs || !peer_flags) return fail(KVSKIP_E_ARG, "exchange_merge: null argument");
+  if (!out_f32 || !lse || !peer_bufs) return fail(KVSKIP_E_ARG, "exchange_merge: null argument");
   if (R < 1 || R > kvb::XCHG_MAX_RANKS || rank < 0 || rank >= R)
     return fail(KVSKIP_E_LIMIT, "exchange_merge: 1..%d ranks", kvb::XCHG_MAX_RANKS);
   if (N < 1 || N > 2147483647LL || seq == 0) return fail(KVSKIP_E_ARG, "exchange_merge: N >= 1, seq >= 1");
   kvb::XchgPeers peers{};
   for (int r = 0; r < R; ++r) {
-    if (!peer_bufs[r] || !peer_flags[r]) return fail(KVSKIP_E_ARG, "exchange_merge: null peer pointer");
+    if (!peer_bufs[r] || reinterpret_cast<uintptr_t>(peer_bufs[r]) % 8)
+      return fail(KVSKIP_E_ARG, "exchange_merge: null or misaligned peer buffer");
     peers.buf[r] = peer_bufs[r];
-    peers.flags[r] = peer_flags[r];
+    peers.flags[r] = peer_flags ? peer_flags[r] : nullptr;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (D != 128 && D != 64) return fail(KVSKIP_E_ARG, "kvskip: unsupported head dim");

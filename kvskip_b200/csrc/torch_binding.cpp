@@ -550,7 +550,7 @@ std::vector<at::Tensor> exchange_merge(const at::Tensor& out_f32, const at::Tens
   unsigned int* flags[8];
   for (int64_t r = 0; r < R; ++r) {
     bufs[r] = reinterpret_cast<float*>(buf_ptrs[r]);
-    flags[r] = reinterpret_cast<unsigned int*>(flag_ptrs[r]);
+    flags[r] = reinterpret_cast<unsigned int*>(flag_ptrs[r]);   // unused by the library
   }
   at::Tensor out = at::empty({N, D}, out_f32.options().dtype(at::kBFloat16));
   at::Tensor out32 = at::empty({N, D}, out_f32.options());

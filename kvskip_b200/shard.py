@@ -109,7 +109,7 @@ def merge_partials(parts: torch.Tensor, B: int, Hq: int, backend=None):
 class PeerExchange:
     """Exchange + merge of the per-rank triples in ONE kernel over peer memory, instead of pack ->
     NCCL all-gather -> merge: every rank stores its rows straight into every rank's buffer over
-    NVLink, flags them, waits for its peers' flags (bounded) and merges.  Buffers come from
+    NVLink as (value, step number) words, waits for its peers' words (bounded) and merges.  Buffers come from
     torch's symmetric memory (one allocation per rank, rendezvous once); results equal the
     all-gather path bit for bit.  All ranks must call it once per step, in the same order."""
 
@@ -124,16 +124,17 @@ class PeerExchange:
         if self.world > 8:
             raise ValueError("at most 8 ranks")
         device = device or torch.device("cuda", torch.cuda.current_device())
-        n_float = 2 * self.world * n_rows * (D + 2)
-        self.mem = symm.empty(n_float + self.world * n_rows, dtype=torch.float32, device=device)
+        # 2 buffer sets x R ranks x rows x (D + 2) words of 8 bytes: (fp32 value, step number)
+        n_words = 2 * self.world * n_rows * (D + 2)
+        self.mem = symm.empty(2 * n_words, dtype=torch.float32, device=device)
         self.mem.zero_()
         handle = symm.rendezvous(self.mem, group)
         ptrs = [int(p) for p in handle.buffer_ptrs]
         self.buf_ptrs = ptrs
-        self.flag_ptrs = [p + 4 * n_float for p in ptrs]
+        self.flag_ptrs = [0 for _ in ptrs]         # the flag travels inside every word: no flag arrays
         self.n_rows, self.D, self.seq = n_rows, D, 0
         torch.cuda.synchronize(device)
-        dist.barrier(group)                       # every rank's flags are zero before anyone writes
+        dist.barrier(group)                       # every rank's buffer is zero before anyone writes
 
     def check(self) -> None:
         """Synchronise and raise kvskip.DeviceWaitError if a wait for a peer's rows ran out in one

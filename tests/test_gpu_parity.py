@@ -460,13 +460,31 @@ def test_sequence_shards_emulated_on_one_gpu(R):
     assert rel_err(got["out_f32"], one["out_f32"].double().cpu()) < 2e-5
 
 
+def xchg_buffers(R, N, W=130):
+    """R exchange buffers of 2*R*N*W words of 8 bytes (value bits, step number), zeroed; returns
+    the tensors (int32 view [2,R,N,W,2]) and their addresses."""
+    bufs = [torch.zeros(2, R, N, W, 2, dtype=torch.int32, device=DEV) for _ in range(R)]
+    return bufs, [b_.data_ptr() for b_ in bufs]
+
+
+def xchg_place(buf, par, r, triple, seq):
+    """A rank's packed rows [N, W] as (value, step) words in slot [par][r] of a buffer."""
+    buf[par, r, :, :, 0] = triple.contiguous().view(torch.int32)
+    buf[par, r, :, :, 1] = seq
+
+
+def xchg_rows(buf, par, r):
+    """(values [N, W] as fp32, steps [N, W]) of slot [par][r]."""
+    return buf[par, r, :, :, 0].contiguous().view(torch.float32), buf[par, r, :, :, 1]
+
+
 def test_exchange_merge_single_rank():
     """The fused exchange kernel with one rank (its own buffer is the only peer): the merge of one
     triple is the identity, step numbers alternate the buffer set, nothing times out."""
     torch.manual_seed(5)
     N, D = 32, 128
-    buf = torch.zeros(2 * N * (D + 2) + N, dtype=torch.float32, device=DEV)
-    bp, fp = [buf.data_ptr()], [buf.data_ptr() + 4 * 2 * N * (D + 2)]
+    bufs, bp = xchg_buffers(1, N)          # (keep the tensors alive: the kernels get their addresses)
+    fp = [0]
     for seq in (1, 2, 3):
         o = torch.randn(N, D, device=DEV)
         lse = torch.randn(N, device=DEV) * 3
@@ -487,8 +505,8 @@ def test_decode_exchange_single_rank(path):
     q, k, v, scale, keep = synth.sink_body_case(8, T=8192 + 13, B=2)
     qc, kc, vc = cuda(q, k, v)
     N, D = 2 * 32, 128
-    buf = torch.zeros(2 * N * (D + 2) + N, dtype=torch.float32, device=DEV)
-    bp, fp = [buf.data_ptr()], [buf.data_ptr() + 4 * 2 * N * (D + 2)]
+    bufs, bp = xchg_buffers(1, N)          # (keep the tensors alive: the kernels get their addresses)
+    fp = [0]
     plan = K.make_plan(keep.to(DEV))
     for seq, pl in ((1, None), (2, plan), (3, None)):
         bi, bc = (None, None) if pl is None else (pl.block_idx, pl.block_cnt)
@@ -514,10 +532,8 @@ def test_decode_exchange_four_ranks_emulated(path):
     qc, kc, vc = cuda(q, k, v)
     nb = keep.shape[-1]
     N, D, W = B * 32, 128, 130
-    n_float = 2 * R * N * W
-    bufs = [torch.zeros(n_float + R * N, dtype=torch.float32, device=DEV) for _ in range(R)]
-    bp = [b_.data_ptr() for b_ in bufs]
-    fp = [b_.data_ptr() + 4 * n_float for b_ in bufs]
+    bufs, bp = xchg_buffers(R, N)
+    fp = [0] * R
     parts = []
     for r in range(R):
         lo, hi = shard.block_range(nb, r, R)
@@ -525,20 +541,16 @@ def test_decode_exchange_four_ranks_emulated(path):
     want = shard.merge_partials(torch.stack(parts), B, 32)
     for seq in (1, 2):
         par = seq & 1
-        mine = bufs[0][:n_float].view(2, R, N, W)
-        flags = bufs[0][n_float:].view(torch.int32).view(R, N)
         for r in range(1, R):
-            mine[par, r] = parts[r]
-            flags[r] = seq
+            xchg_place(bufs[0], par, r, parts[r], seq)
         lo, hi = shard.block_range(nb, 0, R)
         out, lse, _, _, o32, _ = K.ext().decode_exchange(qc, kc[:, :, lo * 64:hi * 64], vc[:, :, lo * 64:hi * 64], scale,
                                                          None, None, 5, bp, fp, 0, seq)
         assert torch.equal(o32.view(B, 32, D), want["out_f32"]) and torch.equal(lse.view(B, 32), want["lse"])
-        # rank 0's own triple reached every peer's buffer, with its flags
+        # rank 0's own triple reached every peer's buffer, every word carrying the step number
         for r in range(1, R):
-            theirs = bufs[r][:n_float].view(2, R, N, W)
-            assert torch.equal(theirs[par, 0], parts[0])
-            assert (bufs[r][n_float:].view(torch.int32).view(R, N)[0] == seq).all()
+            vals, steps = xchg_rows(bufs[r], par, 0)
+            assert torch.equal(vals, parts[0]) and (steps == seq).all()
     assert K.ext().device_status() == 0
 
 
@@ -571,20 +583,18 @@ def test_decode_exchange_short_and_empty_lists_emulated(path):
              shard.local_partial(qc, kc[:, :, lo1 * 64:hi1 * 64], vc[:, :, lo1 * 64:hi1 * 64], scale, plan=plan1)]
     want = shard.merge_partials(torch.stack(parts), B, 32)
     N, D, W = B * 32, 128, 130
-    n_float = 2 * R * N * W
-    bufs = [torch.zeros(n_float + R * N, dtype=torch.float32, device=DEV) for _ in range(R)]
-    bp = [b_.data_ptr() for b_ in bufs]
-    fp = [b_.data_ptr() + 4 * n_float for b_ in bufs]
+    bufs, bp = xchg_buffers(R, N)
+    fp = [0] * R
     for seq in (1, 2):
         par = seq & 1
-        bufs[0][:n_float].view(2, R, N, W)[par, 1] = parts[1]
-        bufs[0][n_float:].view(torch.int32).view(R, N)[1] = seq
+        xchg_place(bufs[0], par, 1, parts[1], seq)
         out, lse, _, _, o32, _ = K.ext().decode_exchange(qc, kc[:, :, lo * 64:hi * 64], vc[:, :, lo * 64:hi * 64], scale,
                                                          plan0.block_idx, plan0.block_cnt, splits, bp, fp, 0, seq)
         assert torch.equal(o32.view(B, 32, D), want["out_f32"]) and torch.equal(lse.view(B, 32), want["lse"])
-        # every row of rank 0, the short and the empty heads included, reached the peer with its flag
-        assert torch.equal(bufs[1][:n_float].view(2, R, N, W)[par, 0], parts[0])
-        assert (bufs[1][n_float:].view(torch.int32).view(R, N)[0] == seq).all()
+        # every row of rank 0, the short and the empty heads included, reached the peer, every word
+        # carrying the step number
+        vals, steps = xchg_rows(bufs[1], par, 0)
+        assert torch.equal(vals, parts[0]) and (steps == seq).all()
     assert K.ext().device_status() == 0
     # against the CPU oracle on the whole sequence with the combined lists
     full = torch.cat([keep0, shard.shard_plan(keep, 1, R)], dim=-1)
@@ -595,7 +605,7 @@ def test_decode_exchange_short_and_empty_lists_emulated(path):
 
 def test_exchange_wait_runs_out_and_reports(path):
     """Failure detection on the device, without faulting anything: rank 0 of two runs the exchange
-    while nothing ever sets rank 1's flags.  With the poll limit lowered ("spin_limit") the kernel
+    while rank 1's words never arrive.  With the poll limit lowered ("spin_limit") the kernel
     gives up after about a millisecond, sets the status word to 0x500 + peer (0x510 + peer from the
     attention kernel's own exchange), returns, and the context stays usable: the same call with the
     peer's rows and flags in place is clean and correct."""
@@ -604,10 +614,8 @@ def test_exchange_wait_runs_out_and_reports(path):
     from kvskip_b200 import shard
     ext = K.ext()
     R, N, D, W = 2, 64, 128, 130
-    n_float = 2 * R * N * W
-    bufs = [torch.zeros(n_float + R * N, dtype=torch.float32, device=DEV) for _ in range(R)]
-    bp = [b_.data_ptr() for b_ in bufs]
-    fp = [b_.data_ptr() + 4 * n_float for b_ in bufs]
+    bufs, bp = xchg_buffers(R, N)
+    fp = [0] * R
     torch.manual_seed(3)
     o = torch.randn(N, D, device=DEV)
     lse = torch.randn(N, device=DEV)
@@ -626,8 +634,7 @@ def test_exchange_wait_runs_out_and_reports(path):
         assert ei.value.code == 0x501
         # the peer's rows and flags in place: clean, and equal to pack -> merge
         seq = 3
-        bufs[0][:n_float].view(2, R, N, W)[seq & 1, 1] = peer
-        bufs[0][n_float:].view(torch.int32).view(R, N)[1] = seq
+        xchg_place(bufs[0], seq & 1, 1, peer, seq)
         out, o32, l2 = ext.exchange_merge(o, lse, bp, fp, 0, seq)
         want = ext.merge_packed(torch.stack([ext.pack_partial(o, lse), peer]).contiguous())
         assert ext.device_status() == 0
@@ -639,8 +646,7 @@ def test_exchange_wait_runs_out_and_reports(path):
         assert ext.device_status() == 0x511
         local = shard.local_partial(qc, kc, vc, scale, num_splits=4)
         seq = 5
-        bufs[0][:n_float].view(2, R, N, W)[seq & 1, 1] = peer
-        bufs[0][n_float:].view(torch.int32).view(R, N)[1] = seq
+        xchg_place(bufs[0], seq & 1, 1, peer, seq)
         _, lse5, _, _, o5, _ = ext.decode_exchange(qc, kc, vc, scale, None, None, 4, bp, fp, 0, seq)
         want = ext.merge_packed(torch.stack([local, peer]).contiguous())
         assert ext.device_status() == 0
