@@ -570,9 +570,9 @@ def _planner_cases(dev, peak, K, synth, RefreshConfig, RefreshLayer, cases, targ
     planner_case(32, 1, 32768, 128, 8, "planner loop: 32 layers x 128 steps, batch 1, 32k context, layer 0 dense, "
                                        "peak calibration, auto index")
     planner_case(8, 8, 32768, 64, 8, "planner loop: 8 layers x 64 steps, batch 8, 32k context")
-    planner_case(5, 1, 65536, 64, 8, "planner loop: 5 layers x 64 steps, batch 1, 64k context", target=True)
-    planner_case(4, 8, 65536, 48, 8, "planner loop: 4 layers x 48 steps, batch 8, 64k context", target=True)
-    planner_case(3, 16, 65536, 40, 8, "planner loop: 3 layers x 40 steps, batch 16, 64k context", target=True)
+    planner_case(9, 1, 65536, 64, 8, "planner loop: 9 layers x 64 steps, batch 1, 64k context", target=True)
+    planner_case(9, 8, 65536, 48, 8, "planner loop: 9 layers x 48 steps, batch 8, 64k context", target=True)
+    planner_case(7, 16, 65536, 40, 8, "planner loop: 7 layers x 40 steps, batch 16, 64k context", target=True)
 
 
 def multi_gpu_cases(dev, rank, world, peak):

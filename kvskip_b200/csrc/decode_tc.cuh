@@ -264,6 +264,60 @@ struct XchgArgs {
   unsigned int spin;     // polls of a peer's flag before the wait gives up (status word 0x510 + peer)
 };
 
+// Merge of the S pieces of one (query head, output element) on the tensor-core path: global max,
+// then the rescaled sums in FOUR interleaved chains (pieces s = k mod 4 in ascending order, combined
+// as (c0 + c1) + (c2 + c3)): four independent chains of loads and additions instead of one, which
+// matters when the CTA that merges is the tail of the launch (a head cut into 43 pieces).  Every
+// in-kernel merge of this path and tc_merge_kernel use this order, so they give the same bits.
+// ml: (m, l) pairs of the pieces; acc: this element of piece 0, pieces `stride` floats apart.
+__device__ __forceinline__ void tc_merge_pieces(const float* ml, const float* acc, const int stride, const int S,
+                                                float& m_out, float& l_out, float& a_out) {
+  float m = -INFINITY;
+  for (int s = 0; s < S; ++s) m = fmaxf(m, __ldcg(ml + 2 * s));
+  const float mu = (m == -INFINITY) ? 0.f : m;
+  float l[4] = {0.f, 0.f, 0.f, 0.f}, a[4] = {0.f, 0.f, 0.f, 0.f};
+  int s = 0;
+  for (; s + 4 <= S; s += 4) {
+    float w[4], pl[4], x[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      w[u] = __ldcg(ml + 2 * (s + u));
+      pl[u] = __ldcg(ml + 2 * (s + u) + 1);
+      x[u] = __ldcg(acc + static_cast<int64_t>(s + u) * stride);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float ww = ex2(w[u] - mu);
+      l[u] += pl[u] * ww;
+      a[u] += x[u] * ww;
+    }
+  }
+  for (int u = 0; s < S; ++s, ++u) {
+    const float ww = ex2(__ldcg(ml + 2 * s) - mu);
+    l[u] += __ldcg(ml + 2 * s + 1) * ww;
+    a[u] += __ldcg(acc + static_cast<int64_t>(s) * stride) * ww;
+  }
+  m_out = m;
+  l_out = (l[0] + l[1]) + (l[2] + l[3]);
+  a_out = (a[0] + a[1]) + (a[2] + a[3]);
+}
+
+// The same merge as a kernel of its own (the fallback when a launch cannot use the device counters):
+// one CTA per (b, query head), one thread per dim; part_acc [rows][S][D], part_ml [rows][S][2].
+template <int D>
+__global__ void __launch_bounds__(D) tc_merge_kernel(const float* __restrict__ part_acc,
+                                                     const float* __restrict__ part_ml, int S, uint16_t* out,
+                                                     float* out_f32, float* lse) {
+  const int64_t row = blockIdx.x;
+  const int d = threadIdx.x;
+  float m, l, a;
+  tc_merge_pieces(part_ml + row * S * 2, part_acc + row * S * D + d, D, S, m, l, a);
+  const float o32 = l > 0.f ? a / l : 0.f;
+  if (out) reinterpret_cast<__nv_bfloat16*>(out)[row * D + d] = __float2bfloat16(o32);
+  if (out_f32) out_f32[row * D + d] = o32;
+  if (d == 0 && lse) lse[row] = l > 0.f ? (m + log2f(l)) * LN2 : -INFINITY;
+}
+
 // One element of this rank's packed row (acc = out, then m = lse / ln 2 and l = 1) into every
 // rank's buffer as (value, step number) words: plain 8-byte stores, to peer memory over NVLink for
 // r != rank.
@@ -554,15 +608,8 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
           const int g = o / D, d = o % D;
           const int64_t hq = static_cast<int64_t>(b) * p.Hq + h * G + g;
           const float* ml = p.part_ml + hq * p.num_splits * 2;
-          float m = -INFINITY;
-          for (int s2 = 0; s2 < S2; ++s2) m = fmaxf(m, __ldcg(ml + 2 * s2));
-          const float mu = (m == -INFINITY) ? 0.f : m;
-          float l = 0.f, a = 0.f;
-          for (int s2 = 0; s2 < S2; ++s2) {
-            const float w = ex2(__ldcg(ml + 2 * s2) - mu);
-            l += __ldcg(ml + 2 * s2 + 1) * w;
-            a += __ldcg(p.part_acc + (hq * p.num_splits + s2) * D + d) * w;
-          }
+          float m, l, a;
+          tc_merge_pieces(ml, p.part_acc + hq * p.num_splits * D + d, D, S2, m, l, a);
           const float o32 = l > 0.f ? a / l : 0.f;
           const float lse_nat = l > 0.f ? (m + log2f(l)) * LN2 : -INFINITY;
           if (!xchg) {

@@ -16,7 +16,7 @@
 // and min_blocks: a list is cut into the same pieces, block i of a piece is folded by "virtual
 // warp" i mod 6 in the same order (the physical warp is rotated so that ring stage s is always
 // consumed by warp s: an mbarrier wait names a phase by parity only), the six states merge in
-// virtual-warp order, a head's pieces merge in ascending order.  Which SM processes which piece
+// virtual-warp order, a head's pieces merge in the same order (tc_merge_pieces).  Which SM processes which piece
 // depends on timing; what is computed does not.
 //
 // Warps: 0..5 consumers, 6 producer (one lane), 7 merger.  D = 128, G = 4, V always loaded.
@@ -397,63 +397,23 @@ decode_tcq_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, i
       last = __shfl_sync(0xffffffffu, last, 0);
       if (!last) continue;
       __threadfence();
-      // merge of the head's pieces in ascending order (the arithmetic of merge_kernel): the four
-      // query heads together, the partials of four pieces requested before any of them is used
-      // (64 independent loads per lane: one warp must pull the whole head through)
-      {
-        const float* ml = p.part_ml + hq0 * p.num_splits * 2;          // [G][num_splits][2]
-        const float* pa = p.part_acc + hq0 * p.num_splits * D;         // [G][num_splits][D]
-        const int Su = d.S_use, ns = p.num_splits;
-        float m[G], mu[G], l[G], a[G][4];
+      // merge of the head's pieces (tc_merge_pieces: four interleaved chains per output element, the
+      // order every merge of the tensor-core path uses); a lane owns 4 elements of each query head
+#pragma unroll 1
+      for (int g = 0; g < G; ++g) {
+        const int64_t hq = hq0 + g;
+        const float* ml = p.part_ml + hq * p.num_splits * 2;
+        float m[4], l[4], a[4];
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-          m[g] = -INFINITY;
-          l[g] = 0.f;
+        for (int j = 0; j < 4; ++j)
+          tc_merge_pieces(ml, p.part_acc + hq * p.num_splits * D + lane + 32 * j, D, d.S_use, m[j], l[j], a[j]);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) a[g][j] = 0.f;
+        for (int j = 0; j < 4; ++j) {
+          const float o32 = l[j] > 0.f ? a[j] / l[j] : 0.f;
+          reinterpret_cast<__nv_bfloat16*>(p.out)[hq * D + lane + 32 * j] = __float2bfloat16(o32);
+          if (p.out_f32) p.out_f32[hq * D + lane + 32 * j] = o32;
         }
-        for (int s2 = 0; s2 < Su; ++s2)
-#pragma unroll
-          for (int g = 0; g < G; ++g) m[g] = fmaxf(m[g], __ldcg(ml + (g * ns + s2) * 2));
-#pragma unroll
-        for (int g = 0; g < G; ++g) mu[g] = (m[g] == -INFINITY) ? 0.f : m[g];
-        for (int s0 = 0; s0 < Su; s0 += 4) {
-          float w[4][G], pl[4][G], x[4][G][4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int s2 = min(s0 + u, Su - 1);
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-              w[u][g] = __ldcg(ml + (g * ns + s2) * 2);
-              pl[u][g] = __ldcg(ml + (g * ns + s2) * 2 + 1);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) x[u][g][j] = __ldcg(pa + (static_cast<int64_t>(g) * ns + s2) * D + lane + 32 * j);
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            if (s0 + u < Su) {
-#pragma unroll
-              for (int g = 0; g < G; ++g) {
-                const float ww = ex2(w[u][g] - mu[g]);
-                l[g] += pl[u][g] * ww;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) a[g][j] += x[u][g][j] * ww;
-              }
-            }
-          }
-        }
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-          const int64_t hq = hq0 + g;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float o32 = l[g] > 0.f ? a[g][j] / l[g] : 0.f;
-            reinterpret_cast<__nv_bfloat16*>(p.out)[hq * D + lane + 32 * j] = __float2bfloat16(o32);
-            if (p.out_f32) p.out_f32[hq * D + lane + 32 * j] = o32;
-          }
-          if (lane == 0 && p.lse) p.lse[hq] = l[g] > 0.f ? (m[g] + log2f(l[g])) * LN2 : -INFINITY;
-        }
+        if (lane == 0 && p.lse) p.lse[hq] = l[0] > 0.f ? (m[0] + log2f(l[0])) * LN2 : -INFINITY;
       }
       if (lane == 0) split_done[d.b * p.Hkv + d.h] = 0;
     }

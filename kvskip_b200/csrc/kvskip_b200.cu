@@ -279,10 +279,8 @@ int launch_tc(const kvskip_params& p, const DynArgs& dyn, cudaStream_t stream) {
   if (int rc = multi_wave ? launch_tc_nc<3, MASKED, STATS, LOAD_V, D>(p, maps, done, min_blocks, dyn, stream)
                           : launch_tc_nc<6, MASKED, STATS, LOAD_V, D>(p, maps, done, min_blocks, dyn, stream))
     return rc;
-  if (LOAD_V && p.num_splits > 1 && done == nullptr) {
-    kvb::merge_kernel<D><<<p.B * p.Hq, D, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits,
-                                                          static_cast<int64_t>(p.B) * p.Hq, true, p.out, p.out_f32,
-                                                          p.lse);
+  if (LOAD_V && p.num_splits > 1 && done == nullptr) {   // no device counters for this launch: merge as a second kernel
+    kvb::tc_merge_kernel<D><<<p.B * p.Hq, D, 0, stream>>>(p.part_acc, p.part_ml, p.num_splits, p.out, p.out_f32, p.lse);
     KVB_CUDA(cudaGetLastError());
   }
   return KVSKIP_OK;
