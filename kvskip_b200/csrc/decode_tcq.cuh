@@ -397,23 +397,62 @@ decode_tcq_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, i
       last = __shfl_sync(0xffffffffu, last, 0);
       if (!last) continue;
       __threadfence();
-      // merge of the head's pieces (tc_merge_pieces: four interleaved chains per output element, the
-      // order every merge of the tensor-core path uses); a lane owns 4 elements of each query head
+      // merge of the head's pieces in the order of tc_merge_pieces (four interleaved chains per output
+      // element: pieces s = u mod 4 ascending, combined (c0 + c1) + (c2 + c3)), written out so that
+      // one warp pulls a query head through in few round trips: the (m, l) pairs and this lane's four
+      // elements of up to 12 pieces are requested before any of them is used.
+      {
+        const int Su = d.S_use, ns = p.num_splits;
+        constexpr int BATCH = 12;                         // pieces in flight: a multiple of 4 (chain u = s mod 4)
 #pragma unroll 1
-      for (int g = 0; g < G; ++g) {
-        const int64_t hq = hq0 + g;
-        const float* ml = p.part_ml + hq * p.num_splits * 2;
-        float m[4], l[4], a[4];
+        for (int g = 0; g < G; ++g) {
+          const int64_t hq = hq0 + g;
+          const float* ml = p.part_ml + hq * ns * 2;
+          const float* pa = p.part_acc + hq * ns * D + lane;
+          float m = -INFINITY;
+          for (int s0 = 0; s0 < Su; s0 += BATCH) {
+            float t[BATCH];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          tc_merge_pieces(ml, p.part_acc + hq * p.num_splits * D + lane + 32 * j, D, d.S_use, m[j], l[j], a[j]);
+            for (int u = 0; u < BATCH; ++u) t[u] = s0 + u < Su ? __ldcg(ml + 2 * (s0 + u)) : -INFINITY;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float o32 = l[j] > 0.f ? a[j] / l[j] : 0.f;
-          reinterpret_cast<__nv_bfloat16*>(p.out)[hq * D + lane + 32 * j] = __float2bfloat16(o32);
-          if (p.out_f32) p.out_f32[hq * D + lane + 32 * j] = o32;
+            for (int u = 0; u < BATCH; ++u) m = fmaxf(m, t[u]);
+          }
+          const float mu = (m == -INFINITY) ? 0.f : m;
+          float l[4] = {0.f, 0.f, 0.f, 0.f}, a[4][4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) a[u][j] = 0.f;
+          for (int s0 = 0; s0 < Su; s0 += BATCH) {
+            float w[BATCH], pl[BATCH], x[BATCH][4];
+#pragma unroll
+            for (int u = 0; u < BATCH; ++u) {
+              const int s2 = min(s0 + u, Su - 1);
+              w[u] = __ldcg(ml + 2 * s2);
+              pl[u] = __ldcg(ml + 2 * s2 + 1);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) x[u][j] = __ldcg(pa + static_cast<int64_t>(s2) * D + 32 * j);
+            }
+#pragma unroll
+            for (int u = 0; u < BATCH; ++u) {
+              if (s0 + u < Su) {
+                const float ww = ex2(w[u] - mu);
+                l[u & 3] += pl[u] * ww;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) a[u & 3][j] += x[u][j] * ww;
+              }
+            }
+          }
+          const float lt = (l[0] + l[1]) + (l[2] + l[3]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float at = (a[0][j] + a[1][j]) + (a[2][j] + a[3][j]);
+            const float o32 = lt > 0.f ? at / lt : 0.f;
+            reinterpret_cast<__nv_bfloat16*>(p.out)[hq * D + lane + 32 * j] = __float2bfloat16(o32);
+            if (p.out_f32) p.out_f32[hq * D + lane + 32 * j] = o32;
+          }
+          if (lane == 0 && p.lse) p.lse[hq] = lt > 0.f ? (m + log2f(lt)) * LN2 : -INFINITY;
         }
-        if (lane == 0 && p.lse) p.lse[hq] = l[0] > 0.f ? (m[0] + log2f(l[0])) * LN2 : -INFINITY;
       }
       if (lane == 0) split_done[d.b * p.Hkv + d.h] = 0;
     }
