@@ -183,6 +183,11 @@ def decode(q, k, v, scale: float, *, plan: Plan | None = None, stats: bool = Fal
             num_splits = splits_for_unsynced_plan(B * Hkv, n_items)
         else:
             num_splits = num_splits_for(B * Hkv, n_items, sms=per_sm * num_sms())
+            if (plan is not None and load_v and q.shape[-1] == 128 and per_sm == 1 and B * Hkv >= QUEUE_MIN_HEADS
+                    and ext().get_option("queue")):
+                # lists of known length on the persistent queue kernel: few, long pieces measured best
+                # (every piece costs the consumers a reload of q and of the list, and the merger a merge)
+                num_splits = min(num_splits, 8)
     bi, bc = (None, None) if plan is None else (plan.block_idx, plan.block_cnt)
     out, lse, bmax, bsum, o32, pbuf = ext().decode(q, k, v, float(scale), bi, bc, stats, load_v,
                                                    int(num_splits), int(stages), out_f32, write_p, t_dev,
