@@ -170,3 +170,55 @@ def test_reference_decode_test_synthetic_edge_block():
     assert len(rows) == 5, rows
     for name, s in rows.items():
         assert s["max"] < 2e-3, (name, s)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["dense", "vskip2", "vskip1", "vskip1sink", "refresh", "refresh_pre", "refresh_fused",
+                                  "replay"])
+def test_reference_attention_forward_every_mode(mode):
+    """`kvskip_attention_forward` of the reference's HF glue (src/kvskip_attn.py:481-511), unmodified,
+    over every mode it dispatches to: eight decode steps on a growing cache.  The dense mode must
+    match the fp64 oracle to the bf16 tolerance; the sparse modes (top-p 0.99 sets, tau 1e-4) stay
+    within a few per cent of dense on the planted data and produce finite outputs of the right
+    shape; the counters of the glue are filled."""
+    import types
+
+    import oracle
+    ka = load_caller("kvskip_attn", "src")
+    dev = torch.device("cuda")
+    steps, T0, B = 8, 4096 + 9, 2
+    walk = synth.planner_walk(31, T0, steps, B=B)
+    q, k, v = walk.q.to(dev), walk.k.to(dev), walk.v.to(dev)
+    c = ka.KVSKIP
+    c.reset()
+    c.mode, c.dense_layers, c.count, c.record = mode, (), True, False
+    c.calib, c.calib_warm, c.calib_kind, c.calib_auto_ix, c.dense_heads, c.index_heads = None, (), "logit", None, (), ()
+    layer = types.SimpleNamespace(layer_idx=3)
+    try:
+        if mode == "replay":          # block lists recorded beforehand: here the sink, the newest and every third block
+            plans = []
+            for t in range(steps):
+                nb = math.ceil((T0 + t + 1) / 64)
+                keep = torch.zeros(B, 8, nb, dtype=torch.bool, device=dev)
+                keep[..., ::3] = True
+                keep[..., 0] = True
+                keep[..., -2:] = True
+                plans.append(K.make_plan(keep, sync=False))
+            c.plans = {3: plans}
+        worst = 0.0
+        for t in range(steps):
+            T = T0 + t + 1
+            out, _ = ka.kvskip_attention_forward(layer, q[t][:, :, None], k[:, :, :T], v[:, :, :T], None,
+                                                 scaling=walk.scale)
+            assert out.shape == (B, 1, 32, 128) and torch.isfinite(out).all()
+            ref = oracle.decode_f64(walk.q[t], walk.k[:, :, :T], walk.v[:, :, :T], walk.scale)["out"]
+            worst = max(worst, float((out[:, 0].double().cpu() - ref).norm() / ref.norm()))
+        limit = {"dense": 2e-3, "vskip1": 5e-3, "vskip1sink": 5e-3, "vskip2": 3e-2, "replay": 1.0}.get(mode, 5e-2)
+        assert worst < limit, (mode, worst)
+        if mode.startswith("refresh"):
+            tot = ka.log_totals()
+            assert 0 < tot["blocks_read"] <= tot["blocks_total"]
+        assert K.ext().device_status() == 0
+    finally:
+        c.reset()
+        c.mode, c.dense_layers, c.plans = "dense", (0,), {}
