@@ -144,5 +144,5 @@ def test_planner_loop_matches_python_planner(golden_dir, name):
     live = [h for h in range(8) if not (VARIANTS[name].get("index_heads") == (h,) and not VARIANTS[name].get("index_union"))]
     assert np.array_equal(s["age"].numpy()[:, live], g[f"{name}_age"][:, live])
     assert np.array_equal(s["aix"].numpy().astype(bool), g[f"{name}_aix"])
-    assert np.allclose(s["calib"].numpy(), g[f"{name}_calib"][-1], atol=2e-3)
-    assert np.allclose(s["lse_att"].numpy(), g[f"{name}_lse_att"], atol=1e-3)
+    assert np.allclose(s["calib"].numpy(), g[f"{name}_calib"][-1], rtol=0, atol=1e-5)
+    assert np.allclose(s["lse_att"].numpy(), g[f"{name}_lse_att"], rtol=0, atol=1e-5)
