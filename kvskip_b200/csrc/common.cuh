@@ -85,6 +85,56 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
   return false;
 }
 
+// ---- thread-block clusters ------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+// The hardware barrier of a cluster, split: every thread of every CTA arrives once and may wait once.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// Address of this CTA's shared-memory location `addr` in the CTA of rank `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_st_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_st_u8(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u8 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+// Arrival on an mbarrier of another CTA of the cluster; orders this thread's earlier stores to that
+// CTA's shared memory before it.
+__device__ __forceinline__ void cluster_mbar_arrive(uint32_t remote_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+}
+// Bounded wait for arrivals from other CTAs of the cluster (acquire at cluster scope).
+__device__ __forceinline__ bool cluster_mbar_wait(uint64_t* bar, uint32_t parity, unsigned int code) {
+  for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  atomicCAS(&g_status, 0u, code);
+  return false;
+}
+
 // ---- TMA ----------------------------------------------------------------------------------
 // 4-D tiled load: coordinates (c0 = dim offset, c1 = token, c2 = kv head, c3 = batch).
 // c0 * 2 bytes must be a multiple of 16 (callers only pass 0 or 64).

@@ -159,6 +159,27 @@ cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// The same with the CTAs along x grouped into clusters of `cluster` (gridDim.x a multiple of it).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_overlapped_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, unsigned cluster, size_t smem,
+                                      cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_use_pdl.load(std::memory_order_relaxed) ? 1 : 0;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = cluster;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Counters of finished splits for the in-kernel merge: zero at load, put back to zero by the CTA
 // that merges.  A region of counters belongs to a (device, stream) pair: launches on one stream run
 // one after the other (a dependent launch touches its counters only after griddepcontrol.wait), so
@@ -174,6 +195,8 @@ std::atomic<int> g_half_cta{1};
 // Block lists on more CTAs than SMs: 1 = one persistent CTA per SM pulling pieces from a queue
 // (decode_tcq.cuh), 0 = one CTA per piece (decode_tc.cuh).  Same bits either way.
 std::atomic<int> g_queue{1};
+std::atomic<int> g_plan_rounds{0};     // 32-block rounds per CTA of `plan` (counter version): 1, 2, 4, 8, or 0 = chosen per launch
+std::atomic<int> g_plan_cluster{-1};   // CTAs per head of `plan` on a cluster: 1, 2, 4, 8; -1 = chosen per launch; 0 = counter version
 std::atomic<int> g_min_blocks{24};     // shortest piece a block list is cut into when there are more CTAs than SMs
 // Polls (of about 100 ns) a kernel spends on a peer's flag before it gives up: about 2 s by default.
 // The "spin_limit" option lowers it, so that a missing peer is reported in microseconds (tests of the
@@ -562,6 +585,18 @@ int kvskip_set_option(const char* name, int value) {
     g_min_blocks.store(value, std::memory_order_relaxed);
     return KVSKIP_OK;
   }
+  if (!std::strcmp(name, "plan_cluster")) {
+    if (value != -1 && value != 0 && value != 1 && value != 2 && value != 4 && value != 8)
+      return fail(KVSKIP_E_ARG, "plan_cluster: 1, 2, 4 or 8 CTAs per head, -1 for the per-launch choice, 0 for the counter version");
+    g_plan_cluster.store(value, std::memory_order_relaxed);
+    return KVSKIP_OK;
+  }
+  if (!std::strcmp(name, "plan_rounds")) {
+    if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8)
+      return fail(KVSKIP_E_ARG, "plan_rounds: 1, 2, 4 or 8, or 0 for the per-launch choice");
+    g_plan_rounds.store(value, std::memory_order_relaxed);
+    return KVSKIP_OK;
+  }
   if (!std::strcmp(name, "spin_limit")) {   // 0 restores the default
     if (value < 0) return fail(KVSKIP_E_ARG, "spin_limit: polls >= 1, or 0 for the default");
     g_xchg_spin.store(value ? value : kDefaultSpin, std::memory_order_relaxed);
@@ -577,6 +612,8 @@ int kvskip_get_option(const char* name) {
   if (name && !std::strcmp(name, "spin_limit")) return g_xchg_spin.load(std::memory_order_relaxed);
   if (name && !std::strcmp(name, "queue")) return g_queue.load(std::memory_order_relaxed);
   if (name && !std::strcmp(name, "min_blocks")) return g_min_blocks.load(std::memory_order_relaxed);
+  if (name && !std::strcmp(name, "plan_rounds")) return g_plan_rounds.load(std::memory_order_relaxed);
+  if (name && !std::strcmp(name, "plan_cluster")) return g_plan_cluster.load(std::memory_order_relaxed);
   return fail(KVSKIP_E_ARG, "unknown option");
 }
 
@@ -646,20 +683,62 @@ int plan_impl(const kvskip_plan_params* p, const DynArgs& dyn, void* stream) {
   if (((p->flags == nullptr)) || !p->csum || !p->keep || !p->block_idx || !p->block_cnt || !p->trig || !p->cs_now)
     return fail(KVSKIP_E_ARG, "plan: missing state tensor");
   if (p->B > 65535 || p->Hkv > 65535) return fail(KVSKIP_E_LIMIT, "B and Hkv are grid dims: at most 65535");
+  int sms = 148;
+  {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  // The cluster version: the CTAs of a head hand their results to the first one through its shared
+  // memory (17 bytes per block of the head).  CTAs per head: as many as keep the launch at about
+  // four CTAs per SM, and no more than the head has 32-block rounds.
+  int cluster = g_plan_cluster.load(std::memory_order_relaxed);
+  const int64_t heads = static_cast<int64_t>(p->B) * p->Hkv;
+  const int csmem = (17 * nb + 15) & ~15;
+  if (cluster != 0 && csmem <= 200 * 1024) {
+    if (cluster < 0) {
+      cluster = 8;
+      while (cluster > 1 && heads * cluster > 4 * static_cast<int64_t>(sms)) cluster /= 2;
+    }
+    while (cluster > 1 && cluster > (nb + kvb::PL_CHUNK - 1) / kvb::PL_CHUNK) cluster /= 2;
+    if (csmem > 40 * 1024)
+      if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::plan_cluster_kernel), 200 * 1024)) return rc;
+    KVB_CUDA(launch_overlapped_cluster(kvb::plan_cluster_kernel, dim3(cluster, p->Hkv, p->B), dim3(kvb::PL_THREADS),
+                                       static_cast<unsigned>(cluster), csmem, static_cast<cudaStream_t>(stream), *p,
+                                       dyn.t_dev, dyn.pages, dyn.max_pages, dyn.num_pages));
+    return KVSKIP_OK;
+  }
   int* done = nullptr;
   if (int rc = split_done_region(p->B * p->Hkv, static_cast<cudaStream_t>(stream), &done)) return rc;
   if (!done)
     return fail(KVSKIP_E_LIMIT, "plan: more than %d (batch, kv head) pairs per call, or more than %d streams used on this device",
                 kMergeRegion, kMergeRegions);
-  const int chunks = (nb + kvb::PL_CHUNK - 1) / kvb::PL_CHUNK;
+  // A CTA computes the centroid scores of 32 * rounds blocks.  With one round a long context at a
+  // large batch is a grid of thousands of short CTAs whose start-up rate bounds the kernel; the
+  // rounds double until the grid is down to about four CTAs per SM.
+  int rounds = g_plan_rounds.load(std::memory_order_relaxed);
+  if (rounds == 0) {
+    const int64_t ctas = static_cast<int64_t>((nb + kvb::PL_CHUNK - 1) / kvb::PL_CHUNK) * p->Hkv * p->B;
+    rounds = 1;
+    while (rounds < 8 && ctas / rounds > 4 * static_cast<int64_t>(sms)) rounds *= 2;
+  }
+  const int chunk = kvb::PL_CHUNK * rounds;
+  const int chunks = (nb + chunk - 1) / chunk;
   const int smem = (nb + 15) & ~15;   // attended flags of one head
   if (smem > 200 * 1024) return fail(KVSKIP_E_LIMIT, "plan: more than %d blocks", 200 * 1024);
-  if (smem > 40 * 1024)
-    if (int rc = ensure_smem(reinterpret_cast<const void*>(kvb::plan_kernel), 200 * 1024)) return rc;
-  KVB_CUDA(launch_overlapped(kvb::plan_kernel, dim3(chunks, p->Hkv, p->B), dim3(kvb::PL_THREADS), smem,
-                             static_cast<cudaStream_t>(stream), *p, done, dyn.t_dev, dyn.pages, dyn.max_pages,
-                             dyn.num_pages));
-  return KVSKIP_OK;
+  auto launch = [&](auto kernel) -> int {
+    if (smem > 40 * 1024)
+      if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), 200 * 1024)) return rc;
+    KVB_CUDA(launch_overlapped(kernel, dim3(chunks, p->Hkv, p->B), dim3(kvb::PL_THREADS), smem,
+                               static_cast<cudaStream_t>(stream), *p, done, dyn.t_dev, dyn.pages, dyn.max_pages,
+                               dyn.num_pages));
+    return KVSKIP_OK;
+  };
+  switch (rounds) {
+    case 1: return launch(kvb::plan_kernel<1>);
+    case 2: return launch(kvb::plan_kernel<2>);
+    case 4: return launch(kvb::plan_kernel<4>);
+    default: return launch(kvb::plan_kernel<8>);
+  }
 }
 }  // namespace
 

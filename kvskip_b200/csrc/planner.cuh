@@ -44,62 +44,136 @@ __device__ __forceinline__ void pl_fold(float& m, float& s, float e) {
   }
 }
 
-// Ascending compaction of the blocks satisfying `pred` into bi[]; count to *cnt.  Chunked scan:
-// thread t owns a contiguous chunk, an inclusive Hillis-Steele scan over the 128 chunk counts
-// gives the offsets.  Must be called by all PL_THREADS threads.
+// Ascending compaction of the blocks satisfying `pred` into bi[]; count to *cnt.  Thread t owns a
+// contiguous chunk; the offsets come from a shuffle scan inside each warp and the four warp totals
+// in `scan`.  Must be called by all PL_THREADS threads.
 template <typename Pred>
 __device__ __forceinline__ void pl_compact(int nb, int* bi, int* cnt, int* scan, Pred pred) {
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int per = (nb + PL_THREADS - 1) / PL_THREADS;
   const int a = min(nb, tid * per), e = min(nb, a + per);
   int c = 0;
   for (int i = a; i < e; ++i) c += pred(i) ? 1 : 0;
-  scan[tid] = c;
-  __syncthreads();
-  for (int o = 1; o < PL_THREADS; o <<= 1) {
-    const int add = tid >= o ? scan[tid - o] : 0;
-    __syncthreads();
-    scan[tid] += add;
-    __syncthreads();
+  int inc = c;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int up = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += up;
   }
-  int off = scan[tid] - c;
+  __syncthreads();           // (scan may still be read by an earlier call)
+  if (lane == 31) scan[warp] = inc;
+  __syncthreads();
+  int off = inc - c, total = 0;
+#pragma unroll
+  for (int w = 0; w < PL_THREADS / 32; ++w) {
+    const int t = scan[w];
+    if (w < warp) off += t;
+    total += t;
+  }
   for (int i = a; i < e; ++i)
     if (pred(i)) bi[off++] = i;
-  if (tid == PL_THREADS - 1) *cnt = scan[PL_THREADS - 1];
+  if (tid == 0) *cnt = total;
 }
 
-constexpr int PL_CHUNK = 32;   // blocks whose centroid scores one CTA computes (4 warps x 8 in flight)
+// The end of `plan` for one (batch, kv head), by the CTA that holds the 128 fold slots (m, s): the
+// slots merge per warp (max, butterfly of rescaled sums), the four groups merge serially in
+// ascending order, the largest miss of the four query heads decides, and the block list is written:
+// every block on a refresh, else the attended ones (att[], one byte per block in shared memory).
+// lse_att (threads 0..3), calib and age (thread 0) were loaded by the caller ahead of time.
+__device__ __forceinline__ void pl_decide_list(const kvskip_plan_params& p, float (&m)[PL_G], float (&s)[PL_G],
+                                               const float lse_att, const float calib, const int age, const int fl,
+                                               const int nb, const int64_t bh, int* bi, const unsigned char* pl_att,
+                                               int* scan, float (*wM)[PL_G], float (*wS)[PL_G], int* s_flag_p) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int& s_flag = *s_flag_p;
+  constexpr int NW = PL_THREADS / 32;
+#pragma unroll
+  for (int g = 0; g < PL_G; ++g) {
+    const float M = warp_max(m[g]);
+    const float S = warp_sum(s[g] > 0.f ? s[g] * __expf(m[g] - M) : 0.f);
+    if (lane == 0) {
+      wM[warp][g] = M;
+      wS[warp][g] = S;
+    }
+  }
+  __syncthreads();
+  if (warp == 0) {   // lane g < 4 merges the four groups of head g in ascending order; the largest miss decides
+    float miss = 0.f;
+    if (lane < PL_G) {
+      const int g = lane;
+      float M = -INFINITY, S = 0.f;
+      for (int w = 0; w < NW; ++w)
+        if (wS[w][g] > 0.f) M = fmaxf(M, wM[w][g]);
+      for (int w = 0; w < NW; ++w)
+        if (wS[w][g] > 0.f) S += wS[w][g] * __expf(wM[w][g] - M);
+      if (S > 0.f) {
+        const float est = M + __logf(S);
+        miss = fmaxf(miss, 1.f / (1.f + __expf(lse_att - est)));
+      }
+    }
+    miss = warp_max(miss);
+    if (lane == 0) {
+      if (p.est) p.est[bh] = miss;
+      float dec = miss;
+      if (p.calib && p.calib_on) dec = p.calib_kind ? miss + calib : 1.f / (1.f + __expf(-(pl_logit(miss) + calib)));
+      const int a = age + 1;
+      const bool tr = dec > p.delta || a >= p.max_age || (fl & 1);
+      p.age[bh] = tr ? 0 : a;
+      p.trig[bh] = tr ? 1 : 0;
+      s_flag = tr ? 1 : 0;
+    }
+  }
+  __syncthreads();
 
-// grid (ceil(nb / PL_CHUNK), Hkv, B).  Every CTA computes the centroid scores of its chunk of
-// blocks and stores them to cs_now; the last CTA of a (batch, kv head) to finish (counted in
-// done[], which it puts back to zero) folds the estimate, decides and writes the block list.
+  // 3. block list of the attention pass
+  if (s_flag) {
+    for (int i = tid; i < nb; i += PL_THREADS) bi[i] = i;
+    if (tid == 0) p.block_cnt[bh] = nb;
+    return;
+  }
+  pl_compact(nb, bi, p.block_cnt + bh, scan, [&](int i) { return pl_att[i] != 0; });
+}
+
+constexpr int PL_CHUNK = 32;   // blocks of one round of a CTA's centroid scores (4 warps x 8 in flight)
+
+// grid (ceil(nb / (32 ROUNDS)), Hkv, B).  Every CTA computes the centroid scores of its chunk of
+// 32 ROUNDS blocks and stores them to cs_now; the last CTA of a (batch, kv head) to finish (counted
+// in done[], which it puts back to zero) folds the estimate, decides and writes the block list.
 // The arithmetic of a score and of the fold is unchanged, only spread over more SMs: one CTA per
-// head reading nb * 512 bytes of key sums is latency-bound at long contexts.
+// head reading nb * 512 bytes of key sums is latency-bound at long contexts.  ROUNDS is chosen by
+// the host so that a launch has a few CTAs per SM: the SMs start a CTA every ~0.4 us each, so a grid
+// of thousands of 3 us CTAs is bound by the rate at which CTAs start, not by their work.
+// A head costs a fixed number of memory round trips, whatever its length: every load of a phase is
+// issued before the first use (no load sits behind a branch on another load's value).
 // With a device-resident length (t_dev != nullptr) p.T is the bound the grid was sized for; CTAs
 // whose chunk lies beyond the current length leave without being counted.
 // With a paged cache (pages != nullptr) p.k is the page pool [pages, Hkv, 64, D] (k_sb = page stride)
 // and the key of the new token is row (T-1) % 64 of page pages[b, (T-1) / 64].
+template <int ROUNDS>
 __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_params p, int* __restrict__ done,
                                                           const int* __restrict__ t_dev,
                                                           const int32_t* __restrict__ pages, const int max_pages,
                                                           const int num_pages) {
+  constexpr int CHUNK = PL_CHUNK * ROUNDS;
   const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int64_t bh = static_cast<int64_t>(b) * p.Hkv + h;
   float* csum = p.csum + bh * p.NBC * PL_D;
   const uint8_t* keep = p.keep + bh * p.NBC;
   int* bi = p.block_idx + bh * p.NBC;
-  __shared__ int scan[PL_THREADS];
+  __shared__ int scan[PL_THREADS / 32];
   __shared__ float wM[PL_THREADS / 32][PL_G], wS[PL_THREADS / 32][PL_G];
   __shared__ int s_flag;
+  extern __shared__ unsigned char pl_att[];   // [nb] attended flags of the head
   pdl_wait_prior();          // the state this kernel reads may come from the previous kernel on the stream
   pdl_launch_dependents();
   const int T = t_dev ? max(1, min(*t_dev, p.T)) : p.T;
   const int nb = (T + TILE - 1) / TILE;
-  const int chunks = (nb + PL_CHUNK - 1) / PL_CHUNK;
+  const int chunks = (nb + CHUNK - 1) / CHUNK;
   if (chunk >= chunks) return;
 
   const int fl = p.flags[h];
+  const bool latched = p.aix && p.aix[bh];
   if (fl & 2) {   // token-index head: index blocks + sink + newest, never refreshes; one CTA does it
     if (chunk != 0) return;
     const uint8_t* ix = p.idx + static_cast<int64_t>(b) * p.NBC;
@@ -107,13 +181,12 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
     if (tid == 0) p.trig[bh] = 0;
     return;
   }
-  const bool uni = (fl & 4) || (p.aix && p.aix[bh]);
-  const uint8_t* ix = uni ? p.idx + static_cast<int64_t>(b) * p.NBC : nullptr;
-  auto attended = [&](int blk) { return keep[blk] || pl_always(blk, nb, p.local) || (uni && ix[blk]); };
+  const bool uni = (fl & 4) || latched;
+  const uint8_t* ix = uni ? p.idx + static_cast<int64_t>(b) * p.NBC : keep;   // (read unconditionally below)
 
-  const int blk0 = chunk * PL_CHUNK;
+  const int blk0 = chunk * CHUNK;
   const int tok_blk = (T - 1) / TILE;
-  if (p.add_token && tok_blk >= blk0 && tok_blk < blk0 + PL_CHUNK) {   // D == 128 == PL_THREADS
+  if (p.add_token && tok_blk >= blk0 && tok_blk < blk0 + CHUNK) {   // D == 128 == PL_THREADS
     int64_t seq = b, row = T - 1;
     if (pages) {
       seq = pages[static_cast<int64_t>(b) * max_pages + tok_blk];
@@ -127,8 +200,8 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
       const __nv_bfloat16* kr = reinterpret_cast<const __nv_bfloat16*>(p.k) + seq * p.k_sb + h * p.k_sh + row * p.k_st;
       csum[static_cast<int64_t>(tok_blk) * PL_D + tid] += __bfloat162float(kr[tid]);
     }
+    __syncthreads();
   }
-  __syncthreads();
 
   // 1. centroid scores of this chunk: a warp per block, lane owns dims 4*lane..4*lane+3
   float qv[PL_G][4];
@@ -139,25 +212,35 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
     for (int e = 0; e < 4; ++e) qv[g][e] = __bfloat162float(qp[e]) * p.scale;
   }
   const int64_t row0 = (static_cast<int64_t>(b) * p.Hq + h * PL_G) * p.NBC;
-  // Warp w takes the 8 consecutive blocks blk0 + 8w .. +7: 8 blocks x 4 heads = 32 dot products,
-  // each the butterfly sum (lane distances 16, 8, 4, 2, 1) of 32 per-lane partials.  Instead of 32
-  // butterflies in which every lane computes every sum, the 32 sums are reduced together: at
-  // distance 16 a lane keeps the 16 sums whose index has the lane's bit 4 and hands the other 16
-  // to its partner, and so on.  Every addition has the same two operands in the same order as in
-  // the butterfly, so the bits are the same; lane j ends up with sum j.
+  // In a round warp w takes the 8 consecutive blocks blk0 + 32 r + 8w .. +7: 8 blocks x 4 heads =
+  // 32 dot products, each the butterfly sum (lane distances 16, 8, 4, 2, 1) of 32 per-lane partials.
+  // Instead of 32 butterflies in which every lane computes every sum, the 32 sums are reduced
+  // together: at distance 16 a lane keeps the 16 sums whose index has the lane's bit 4 and hands
+  // the other 16 to its partner, and so on.  Every addition has the same two operands in the same
+  // order as in the butterfly, so the bits are the same; lane j ends up with sum j.  The key sums
+  // of the next round are requested before this round's reduction.
   constexpr int U = PL_CHUNK / 4;
   static_assert(U * PL_G == 32, "one dot product per lane");
-  {
-    float a[32];   // a[4 * u + g]: this lane's partial of block u, head g
-    const int wb = blk0 + warp * U;
+  auto fetch = [&](float4 (&c)[U], const int r) {
+    const int wb = blk0 + r * PL_CHUNK + warp * U;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int blk = wb + u;
-      const float4 c = blk < nb ? *reinterpret_cast<const float4*>(csum + static_cast<int64_t>(blk) * PL_D + 4 * lane)
-                                : make_float4(0.f, 0.f, 0.f, 0.f);
+      c[u] = blk < nb ? *reinterpret_cast<const float4*>(csum + static_cast<int64_t>(blk) * PL_D + 4 * lane)
+                      : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+  float4 c[U], cn[U];
+  fetch(c, 0);
+#pragma unroll
+  for (int r = 0; r < ROUNDS; ++r) {
+    if (r + 1 < ROUNDS) fetch(cn, r + 1);
+    float a[32];   // a[4 * u + g]: this lane's partial of block u, head g
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
 #pragma unroll
       for (int g = 0; g < PL_G; ++g)
-        a[4 * u + g] = qv[g][0] * c.x + qv[g][1] * c.y + qv[g][2] * c.z + qv[g][3] * c.w;
+        a[4 * u + g] = qv[g][0] * c[u].x + qv[g][1] * c[u].y + qv[g][2] * c[u].z + qv[g][3] * c[u].w;
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -169,98 +252,250 @@ __global__ void __launch_bounds__(PL_THREADS) plan_kernel(const kvskip_plan_para
         a[j] = mine + __shfl_xor_sync(0xffffffffu, theirs, o);
       }
     }
-    const int blk = wb + (lane >> 2), g = lane & 3;
+    const int blk = blk0 + r * PL_CHUNK + warp * U + (lane >> 2), g = lane & 3;
     if (blk < nb) {
       const float inv_n = 1.f / static_cast<float>(blk == nb - 1 ? T - blk * TILE : TILE);
       p.cs_now[row0 + g * p.NBC + blk] = a[0] * inv_n;
     }
+    if (r + 1 < ROUNDS) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) c[u] = cn[u];
+    }
   }
-  // count this chunk; only the last one of the head goes on
+  // count this chunk; only the last one of the head goes on.  While the counter's round trip is
+  // under way every CTA stages the head's attended flags (a byte or two per block, from state that
+  // no CTA of this launch writes) and the scalars of the decision: the last CTA finds them ready.
   __threadfence();
   __syncthreads();
-  if (tid == 0) s_flag = atomicAdd(&done[bh], 1) == chunks - 1;
+  int prev = 0;
+  if (tid == 0) prev = atomicAdd(&done[bh], 1);
+  for (int i = tid; i < nb; i += PL_THREADS) {
+    const uint8_t kp = keep[i], xi = ix[i];
+    pl_att[i] = (kp || pl_always(i, nb, p.local) || (uni && xi)) ? 1 : 0;
+  }
+  const float lse_att = tid < PL_G ? p.lse_att[static_cast<int64_t>(b) * p.Hq + h * PL_G + tid] : 0.f;
+  const float calib = (tid == 0 && p.calib && p.calib_on) ? p.calib[bh] : 0.f;
+  const int age = tid == 0 ? p.age[bh] : 0;
+  if (tid == 0) s_flag = prev == chunks - 1;
   __syncthreads();
   if (!s_flag) return;
   __threadfence();
   if (tid == 0) done[bh] = 0;
 
-  // attended flags of every block into shared memory: independent, coalesced loads
-  extern __shared__ unsigned char pl_att[];   // [nb]
-  for (int i = tid; i < nb; i += PL_THREADS) pl_att[i] = attended(i) ? 1 : 0;
-  __syncthreads();
-
   // 2. estimate of the mass outside the attended set: fold slot t takes blocks t, t+128, ...
-  // (operands of four blocks are loaded before the dependent exp chain of the fold starts)
+  // The operands of eight blocks are requested at once, attended or not (an unused block costs
+  // three loads, a load behind a test of the flag would cost a round trip per block), before the
+  // dependent exp chain of the fold starts.
   float m[PL_G], s[PL_G];
 #pragma unroll
   for (int g = 0; g < PL_G; ++g) {
     m[g] = -INFINITY;
     s[g] = 0.f;
   }
-  for (int base = tid; base < nb; base += 4 * PL_THREADS) {
-    float e[4][PL_G];
-    bool use[4];
+  constexpr int FJ = 8;
+  for (int base = tid; base < nb; base += FJ * PL_THREADS) {
+    float ra[FJ][PL_G], rb[FJ][PL_G], rc[FJ][PL_G];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < FJ; ++j) {
+      const int64_t at = row0 + min(base + j * PL_THREADS, nb - 1);
+#pragma unroll
+      for (int g = 0; g < PL_G; ++g) {
+        ra[j][g] = __ldg(p.lse_ref + at + g * p.NBC);
+        rc[j][g] = __ldg(p.cs_ref + at + g * p.NBC);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < FJ; ++j) {
+      const int64_t at = row0 + min(base + j * PL_THREADS, nb - 1);
+#pragma unroll
+      for (int g = 0; g < PL_G; ++g) rb[j][g] = __ldcg(p.cs_now + at + g * p.NBC);
+    }
+#pragma unroll
+    for (int j = 0; j < FJ; ++j) {
       const int blk = base + j * PL_THREADS;
-      use[j] = blk < nb && !pl_att[blk];
-      if (use[j]) {
+      if (blk < nb && !pl_att[min(blk, nb - 1)]) {
 #pragma unroll
-        for (int g = 0; g < PL_G; ++g)
-          e[j][g] = p.lse_ref[row0 + g * p.NBC + blk] + __ldcg(p.cs_now + row0 + g * p.NBC + blk) -
-                    p.cs_ref[row0 + g * p.NBC + blk];
+        for (int g = 0; g < PL_G; ++g) pl_fold(m[g], s[g], ra[j][g] + rb[j][g] - rc[j][g]);
       }
     }
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (use[j]) {
-#pragma unroll
-        for (int g = 0; g < PL_G; ++g) pl_fold(m[g], s[g], e[j][g]);
-      }
   }
-  constexpr int NW = PL_THREADS / 32;
-#pragma unroll
-  for (int g = 0; g < PL_G; ++g) {
-    const float M = warp_max(m[g]);
-    const float S = warp_sum(s[g] > 0.f ? s[g] * __expf(m[g] - M) : 0.f);
-    if (lane == 0) {
-      wM[warp][g] = M;
-      wS[warp][g] = S;
-    }
-  }
-  __syncthreads();
-  if (tid == 0) {
-    float miss = 0.f;
-    for (int g = 0; g < PL_G; ++g) {
-      float M = -INFINITY, S = 0.f;
-      for (int w = 0; w < NW; ++w)
-        if (wS[w][g] > 0.f) M = fmaxf(M, wM[w][g]);
-      for (int w = 0; w < NW; ++w)
-        if (wS[w][g] > 0.f) S += wS[w][g] * __expf(wM[w][g] - M);
-      if (S > 0.f) {
-        const float est = M + __logf(S);
-        miss = fmaxf(miss, 1.f / (1.f + __expf(p.lse_att[static_cast<int64_t>(b) * p.Hq + h * PL_G + g] - est)));
-      }
-    }
-    if (p.est) p.est[bh] = miss;
-    float dec = miss;
-    if (p.calib && p.calib_on)
-      dec = p.calib_kind ? miss + p.calib[bh] : 1.f / (1.f + __expf(-(pl_logit(miss) + p.calib[bh])));
-    const int a = p.age[bh] + 1;
-    const bool tr = dec > p.delta || a >= p.max_age || (fl & 1);
-    p.age[bh] = tr ? 0 : a;
-    p.trig[bh] = tr ? 1 : 0;
-    s_flag = tr ? 1 : 0;
-  }
-  __syncthreads();
+  pl_decide_list(p, m, s, lse_att, calib, age, fl, nb, bh, bi, pl_att, scan, wM, wS, &s_flag);
+}
 
-  // 3. block list of the attention pass
-  if (s_flag) {
-    for (int i = tid; i < nb; i += PL_THREADS) bi[i] = i;
-    if (tid == 0) p.block_cnt[bh] = nb;
+// `plan` on a thread-block cluster: grid (C, Hkv, B) with the C CTAs of a (batch, kv head) forming
+// one cluster (C = 1, 2, 4 or 8, chosen by the host so that a launch has a few CTAs per SM).  The 32-
+// block rounds of the head are dealt out evenly; a CTA computes the centroid scores of its rounds
+// (the same arithmetic as plan_kernel), stores them to cs_now for `update`, and puts what the fold
+// needs -- e = lse_ref + cs_now - cs_ref per query head and the attended flag of the block --
+// straight into the shared memory of the cluster's first CTA.  Every thread then arrives on an
+// mbarrier of that CTA (release at cluster scope); the first CTA waits for it (bounded), folds from
+// its own shared memory, decides and writes the list.  Against the counter version this takes the
+// global-memory hand-over out of a head's chain: no fence + atomic round trip, no reload of three
+// arrays by one SM.  The operands of e belong to state no CTA of this launch writes, so they are
+// requested together with the key sums.  Shared memory of a CTA: 17 bytes per block of the head.
+// Every CTA of a cluster takes the same branches up to its arrival: the only early exit (a token-
+// index head) depends on the head alone, and with a device-resident length all CTAs see the same nb.
+__global__ void __launch_bounds__(PL_THREADS) plan_cluster_kernel(const kvskip_plan_params p,
+                                                                  const int* __restrict__ t_dev,
+                                                                  const int32_t* __restrict__ pages,
+                                                                  const int max_pages, const int num_pages) {
+  const int rank = static_cast<int>(cluster_ctarank()), C = static_cast<int>(cluster_nctarank());
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t bh = static_cast<int64_t>(b) * p.Hkv + h;
+  float* csum = p.csum + bh * p.NBC * PL_D;
+  const uint8_t* keep = p.keep + bh * p.NBC;
+  int* bi = p.block_idx + bh * p.NBC;
+  __shared__ int scan[PL_THREADS / 32];
+  __shared__ float wM[PL_THREADS / 32][PL_G], wS[PL_THREADS / 32][PL_G];
+  __shared__ int s_flag;
+  __shared__ __align__(8) uint64_t arrived;
+  extern __shared__ __align__(16) unsigned char pl_dyn[];   // first CTA: e [nbs][4] floats, then attended [nbs]
+  const int nbs = (p.T + TILE - 1) / TILE;                  // blocks of the bound: the layout of pl_dyn
+  if (rank == 0 && tid == 0 && C > 1) {
+    mbar_init(&arrived, static_cast<uint32_t>((C - 1) * PL_THREADS));
+    mbar_fence_init();
+  }
+  cluster_arrive();          // (its wait, below, is what makes the initialised barrier visible to the others)
+  pdl_wait_prior();          // the state this kernel reads may come from the previous kernel on the stream
+  pdl_launch_dependents();
+  const int T = t_dev ? max(1, min(*t_dev, p.T)) : p.T;
+  const int nb = (T + TILE - 1) / TILE;
+  const int rounds = (nb + PL_CHUNK - 1) / PL_CHUNK;
+  const int r0 = rank * rounds / C, r1 = (rank + 1) * rounds / C;   // this CTA's rounds
+
+  const int fl = p.flags[h];
+  const bool latched = p.aix && p.aix[bh];
+  if (fl & 2) {   // token-index head: index blocks + sink + newest, never refreshes; one CTA does it
+    if (rank != 0) return;
+    const uint8_t* ix = p.idx + static_cast<int64_t>(b) * p.NBC;
+    pl_compact(nb, bi, p.block_cnt + bh, scan, [&](int i) { return ix[i] || pl_always(i, nb, p.local); });
+    if (tid == 0) p.trig[bh] = 0;
     return;
   }
-  pl_compact(nb, bi, p.block_cnt + bh, scan, [&](int i) { return pl_att[i] != 0; });
+  const bool uni = (fl & 4) || latched;
+  const uint8_t* ix = uni ? p.idx + static_cast<int64_t>(b) * p.NBC : keep;   // (read unconditionally below)
+  // scalars of the decision, ahead of time
+  const float lse_att = (rank == 0 && tid < PL_G) ? p.lse_att[static_cast<int64_t>(b) * p.Hq + h * PL_G + tid] : 0.f;
+  const float calib = (rank == 0 && tid == 0 && p.calib && p.calib_on) ? p.calib[bh] : 0.f;
+  const int age = (rank == 0 && tid == 0) ? p.age[bh] : 0;
+
+  const int tok_blk = (T - 1) / TILE;
+  if (p.add_token && tok_blk >= r0 * PL_CHUNK && tok_blk < r1 * PL_CHUNK) {   // D == 128 == PL_THREADS
+    int64_t seq = b, row = T - 1;
+    if (pages) {
+      seq = pages[static_cast<int64_t>(b) * max_pages + tok_blk];
+      row = (T - 1) % TILE;
+      if (seq < 0 || seq >= num_pages) {   // a table entry outside the pool: nothing is read
+        if (tid == 0) atomicCAS(&g_status, 0u, 0x300u);
+        seq = -1;
+      }
+    }
+    if (seq >= 0) {
+      const __nv_bfloat16* kr = reinterpret_cast<const __nv_bfloat16*>(p.k) + seq * p.k_sb + h * p.k_sh + row * p.k_st;
+      csum[static_cast<int64_t>(tok_blk) * PL_D + tid] += __bfloat162float(kr[tid]);
+    }
+    __syncthreads();
+  }
+
+  float qv[PL_G][4];
+#pragma unroll
+  for (int g = 0; g < PL_G; ++g) {
+    const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(p.q) + b * p.q_sb + (h * PL_G + g) * p.q_sh + 4 * lane;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) qv[g][e] = __bfloat162float(qp[e]) * p.scale;
+  }
+  const int64_t row0 = (static_cast<int64_t>(b) * p.Hq + h * PL_G) * p.NBC;
+  constexpr int U = PL_CHUNK / 4;
+  static_assert(U * PL_G == 32, "one dot product per lane");
+  // what a lane needs of a round: the key sums of the warp's 8 blocks (its 4 dims each) and, for the
+  // (block, head) pair whose score it ends up with, the two references and the block's flags
+  struct Round {
+    float4 c[U];
+    float lref, cref;
+    uint8_t kp, xi;
+  };
+  const int my_u = lane >> 2, my_g = lane & 3;
+  auto fetch = [&](Round& x, const int r) {
+    const int wb = r * PL_CHUNK + warp * U;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int blk = wb + u;
+      x.c[u] = blk < nb ? *reinterpret_cast<const float4*>(csum + static_cast<int64_t>(blk) * PL_D + 4 * lane)
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const int blk = min(wb + my_u, nb - 1);
+    x.lref = p.lse_ref[row0 + my_g * p.NBC + blk];
+    x.cref = p.cs_ref[row0 + my_g * p.NBC + blk];
+    x.kp = keep[blk];
+    x.xi = ix[blk];
+  };
+  const uint32_t e_remote = cluster_map(smem_u32(pl_dyn), 0);
+  const uint32_t att_remote = e_remote + 16u * static_cast<uint32_t>(nbs);
+  bool waited = false;
+  Round cur, nxt;
+  if (r0 < r1) fetch(cur, r0);
+  for (int r = r0; r < r1; ++r) {
+    if (r + 1 < r1) fetch(nxt, r + 1);
+    float a[32];   // a[4 * u + g]: this lane's partial of block u, head g
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+      for (int g = 0; g < PL_G; ++g)
+        a[4 * u + g] = qv[g][0] * cur.c[u].x + qv[g][1] * cur.c[u].y + qv[g][2] * cur.c[u].z + qv[g][3] * cur.c[u].w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {   // the 32 butterflies reduced together, see plan_kernel
+      const bool up = (lane & o) != 0;
+#pragma unroll
+      for (int j = 0; j < o; ++j) {
+        const float mine = up ? a[j + o] : a[j];
+        const float theirs = up ? a[j] : a[j + o];
+        a[j] = mine + __shfl_xor_sync(0xffffffffu, theirs, o);
+      }
+    }
+    if (!waited) {           // the first CTA runs and its barrier is initialised: its shared memory may be written
+      cluster_wait();
+      waited = true;
+    }
+    const int blk = r * PL_CHUNK + warp * U + my_u;
+    if (blk < nb) {
+      const float inv_n = 1.f / static_cast<float>(blk == nb - 1 ? T - blk * TILE : TILE);
+      const float cs = a[0] * inv_n;
+      p.cs_now[row0 + my_g * p.NBC + blk] = cs;
+      cluster_st_f32(e_remote + 4u * static_cast<uint32_t>(blk * PL_G + my_g), cur.lref + cs - cur.cref);
+      if (my_g == 0)
+        cluster_st_u8(att_remote + static_cast<uint32_t>(blk),
+                      (cur.kp || pl_always(blk, nb, p.local) || (uni && cur.xi)) ? 1u : 0u);
+    }
+    cur = nxt;
+  }
+  if (!waited) cluster_wait();
+  if (rank != 0) {
+    cluster_mbar_arrive(cluster_map(smem_u32(&arrived), 0));
+    return;
+  }
+  __syncthreads();           // this CTA's own rounds are in its shared memory
+  if (C > 1 && !cluster_mbar_wait(&arrived, 0, 0x310u)) return;
+
+  // estimate of the mass outside the attended set: fold slot t takes blocks t, t+128, ...
+  const float4* e4 = reinterpret_cast<const float4*>(pl_dyn);
+  const unsigned char* pl_att = pl_dyn + 16 * static_cast<size_t>(nbs);
+  float m[PL_G], s[PL_G];
+#pragma unroll
+  for (int g = 0; g < PL_G; ++g) {
+    m[g] = -INFINITY;
+    s[g] = 0.f;
+  }
+  for (int blk = tid; blk < nb; blk += PL_THREADS) {
+    if (pl_att[blk]) continue;
+    const float4 e = e4[blk];
+    pl_fold(m[0], s[0], e.x);
+    pl_fold(m[1], s[1], e.y);
+    pl_fold(m[2], s[2], e.z);
+    pl_fold(m[3], s[3], e.w);
+  }
+  pl_decide_list(p, m, s, lse_att, calib, age, fl, nb, bh, bi, pl_att, scan, wM, wS, &s_flag);
 }
 
 // The top-p cut of one query head by one warp: 32 bisection steps on the threshold lo in
