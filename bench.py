@@ -369,6 +369,23 @@ def _attention_cases(dev, K, synth, g, add, flush):
         kv_bytes(1, T_HEAD, 0.5 * (1 + kept2)), v_kept=round(kept2, 4),
         bytes="all K + V of the selected blocks (P written and re-read in fp16 not counted)")
     del q, k, v
+    # the same modes at batch 8, where a pass is bandwidth- rather than launch-bound: the V-skip modes
+    # against the dense pass over the same cache (the ratio the modes exist for)
+    q, k, v, scale, keep = synth.body_union_case(4, T_HEAD, B=8)
+    q, k, v = q.to(dev), k.to(dev), v.to(dev)
+    dense8 = time_cuda(lambda: K.decode(q, k, v, scale), 20, flush)
+    add("dense B=8 T=65536 (reference point of the two V-skip rows below)", dense8, kv_bytes(8, T_HEAD, 1.0))
+    lse = K.decode(q, k, v, scale)["lse"]
+    vk = K.vskip_one_pass(q, k, v, scale, tau=1e-4, lse_prev=lse, count=True)["kept_frac"]
+    t1 = time_cuda(lambda: K.vskip_one_pass(q, k, v, scale, tau=1e-4, lse_prev=lse), 20, flush)
+    add("vskip1 (previous-step normaliser, tau 1e-4) B=8 T=65536", t1, kv_bytes(8, T_HEAD, 0.5 * (1 + vk)),
+        v_kept=round(vk, 4), time_vs_dense=round(t1["us"] / dense8["us"], 3), bytes="all K + V of voted blocks")
+    kept2 = float(K.vskip_two_pass(q, k, v, scale, "topp", 0.99)["kept_frac"])
+    t2 = time_cuda(lambda: K.vskip_two_pass(q, k, v, scale, "topp", 0.99, sync=False), 20, flush)
+    add("vskip two-pass (top-p 0.99) B=8 T=65536", t2, kv_bytes(8, T_HEAD, 0.5 * (1 + kept2)), v_kept=round(kept2, 4),
+        time_vs_dense=round(t2["us"] / dense8["us"], 3),
+        bytes="all K + V of the selected blocks (P written and re-read in fp16 not counted)")
+    del q, k, v
 
 
 def _planner_cases(dev, peak, K, synth, RefreshConfig, RefreshLayer, cases, targets=None):

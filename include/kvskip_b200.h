@@ -309,13 +309,20 @@ int kvskip_launch_append(uint16_t* k, uint16_t* v, int64_t sb, int64_t sh, int64
  *                  piece) items from a device-side queue; 0: one CTA per piece.  Same bits either way.
  *   "min_blocks"   shortest piece (in 64-token blocks) a block list is cut into when the launch has
  *                  more CTAs than SMs; default 24.
+ *   "plan_cluster" CTAs per (batch, kv head) of `plan` when it runs on thread-block clusters (the CTAs
+ *                  of a head hand their results to the first one through its shared memory): 1, 2, 4 or
+ *                  8; -1 (default): chosen per launch, about four CTAs per SM; 0: the version that
+ *                  counts a head's finished CTAs in global memory (also used, whatever the option,
+ *                  beyond 12 000 blocks, where a head's table no longer fits in shared memory).
+ *   "plan_rounds"  32-block rounds per CTA of that counter version: 1, 2, 4 or 8; 0 (default): chosen
+ *                  per launch.  Every setting of these two leaves every output of `plan` bit-identical.
  *   "spin_limit"   polls (about 100 ns each) a kernel of the sequence-sharded exchange spends on a
  *                  peer's flag before it gives up, sets the status word (0x500 + peer from
  *                  kvskip_launch_exchange_merge, 0x510 + peer from kvskip_launch_decode_xchg),
  *                  merges what arrived and returns; default 2^21 (about 2 s); 0 restores it.
  *
- * Concurrency.  The kernels that merge their splits in the same launch (attention, V-skip, plan)
- * count finished CTAs in device counters owned by the (device, stream) pair of the launch: launches
+ * Concurrency.  The kernels that merge their splits in the same launch (attention, V-skip, the
+ * counter version of plan) count finished CTAs in device counters owned by the (device, stream) pair of the launch: launches
  * on one stream follow one another and share them safely, launches on different streams use
  * different ones, and a launch captured into a CUDA graph keeps the counters of the stream it was
  * captured on.  Unsupported: replaying such a graph while other launches of this library run on the

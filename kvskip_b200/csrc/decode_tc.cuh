@@ -302,6 +302,86 @@ __device__ __forceinline__ void tc_merge_pieces(const float* ml, const float* ac
   a_out = (a[0] + a[1]) + (a[2] + a[3]);
 }
 
+// tc_merge_pieces for E (query head, output element) pairs at once, with the loads of eight pieces
+// of all E pairs requested before the first is used: the CTA that merges a head is the tail of its
+// launch, and a merge that asks for four values at a time spends a memory round trip on every four
+// pieces of every element.  Every chain sees the same operands in the same order as in
+// tc_merge_pieces, so the bits are the same.
+template <int E>
+__device__ __forceinline__ void tc_merge_pieces_n(const float* const (&ml)[E], const float* const (&acc)[E],
+                                                  const int stride, const int S, float (&m_out)[E], float (&l_out)[E],
+                                                  float (&a_out)[E]) {
+  constexpr int MB = 16, PB = 8;
+  float m[E], mu[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) m[e] = -INFINITY;
+  for (int s0 = 0; s0 < S; s0 += MB) {
+    float v[E][MB];
+#pragma unroll
+    for (int e = 0; e < E; ++e)
+#pragma unroll
+      for (int u = 0; u < MB; ++u) v[e][u] = s0 + u < S ? __ldcg(ml[e] + 2 * (s0 + u)) : -INFINITY;
+#pragma unroll
+    for (int e = 0; e < E; ++e)
+#pragma unroll
+      for (int u = 0; u < MB; ++u) m[e] = fmaxf(m[e], v[e][u]);
+  }
+  float l[E][4], a[E][4];
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    mu[e] = (m[e] == -INFINITY) ? 0.f : m[e];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) l[e][u] = a[e][u] = 0.f;
+  }
+  int s = 0;
+  for (; s + PB <= S; s += PB) {
+    float w[E][PB], pl[E][PB], x[E][PB];
+#pragma unroll
+    for (int e = 0; e < E; ++e)
+#pragma unroll
+      for (int u = 0; u < PB; ++u) {
+        w[e][u] = __ldcg(ml[e] + 2 * (s + u));
+        pl[e][u] = __ldcg(ml[e] + 2 * (s + u) + 1);
+        x[e][u] = __ldcg(acc[e] + static_cast<int64_t>(s + u) * stride);
+      }
+#pragma unroll
+    for (int e = 0; e < E; ++e)
+#pragma unroll
+      for (int u = 0; u < PB; ++u) {
+        const float ww = ex2(w[e][u] - mu[e]);
+        l[e][u & 3] += pl[e][u] * ww;
+        a[e][u & 3] += x[e][u] * ww;
+      }
+  }
+  {   // the last 0..7 pieces: chains 0, 1, 2, 3, 0, ... as above
+    float w[E][PB], pl[E][PB], x[E][PB];
+#pragma unroll
+    for (int e = 0; e < E; ++e)
+#pragma unroll
+      for (int u = 0; u < PB; ++u) {
+        const int su = min(s + u, S - 1);
+        w[e][u] = __ldcg(ml[e] + 2 * su);
+        pl[e][u] = __ldcg(ml[e] + 2 * su + 1);
+        x[e][u] = __ldcg(acc[e] + static_cast<int64_t>(su) * stride);
+      }
+#pragma unroll
+    for (int e = 0; e < E; ++e)
+#pragma unroll
+      for (int u = 0; u < PB; ++u)
+        if (s + u < S) {
+          const float ww = ex2(w[e][u] - mu[e]);
+          l[e][u & 3] += pl[e][u] * ww;
+          a[e][u & 3] += x[e][u] * ww;
+        }
+  }
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    m_out[e] = m[e];
+    l_out[e] = (l[e][0] + l[e][1]) + (l[e][2] + l[e][3]);
+    a_out[e] = (a[e][0] + a[e][1]) + (a[e][2] + a[e][3]);
+  }
+}
+
 // The same merge as a kernel of its own (the fallback when a launch cannot use the device counters):
 // one CTA per (b, query head), one thread per dim; part_acc [rows][S][D], part_ml [rows][S][2].
 template <int D>
@@ -604,12 +684,25 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
       if (s_last) {
         __threadfence();
         const int S2 = S_use;             // partials used; their stride stays p.num_splits
-        for (int o = tid; o < G * D; o += TC_THREADS) {
+        constexpr int E = (G * D + TC_THREADS - 1) / TC_THREADS;   // elements of the head per thread, merged together
+        const float* ml[E];
+        const float* pa[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const int o = min(tid + e * TC_THREADS, G * D - 1);
+          const int64_t hq = static_cast<int64_t>(b) * p.Hq + h * G + o / D;
+          ml[e] = p.part_ml + hq * p.num_splits * 2;
+          pa[e] = p.part_acc + hq * p.num_splits * D + o % D;
+        }
+        float mm[E], ll[E], aa[E];
+        tc_merge_pieces_n<E>(ml, pa, D, S2, mm, ll, aa);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const int o = tid + e * TC_THREADS;
+          if (o >= G * D) continue;
           const int g = o / D, d = o % D;
           const int64_t hq = static_cast<int64_t>(b) * p.Hq + h * G + g;
-          const float* ml = p.part_ml + hq * p.num_splits * 2;
-          float m, l, a;
-          tc_merge_pieces(ml, p.part_acc + hq * p.num_splits * D + d, D, S2, m, l, a);
+          const float m = mm[e], l = ll[e], a = aa[e];
           const float o32 = l > 0.f ? a / l : 0.f;
           const float lse_nat = l > 0.f ? (m + log2f(l)) * LN2 : -INFINITY;
           if (!xchg) {

@@ -195,6 +195,7 @@ std::atomic<int> g_half_cta{1};
 // Block lists on more CTAs than SMs: 1 = one persistent CTA per SM pulling pieces from a queue
 // (decode_tcq.cuh), 0 = one CTA per piece (decode_tc.cuh).  Same bits either way.
 std::atomic<int> g_queue{1};
+std::atomic<int> g_queue_min_heads{32};   // fewest (batch, kv head) pairs of a launch that takes the queue kernel
 std::atomic<int> g_plan_rounds{0};     // 32-block rounds per CTA of `plan` (counter version): 1, 2, 4, 8, or 0 = chosen per launch
 std::atomic<int> g_plan_cluster{-1};   // CTAs per head of `plan` on a cluster: 1, 2, 4, 8; -1 = chosen per launch; 0 = counter version
 std::atomic<int> g_min_blocks{24};     // shortest piece a block list is cut into when there are more CTAs than SMs
@@ -288,7 +289,7 @@ int launch_tc(const kvskip_params& p, const DynArgs& dyn, cudaStream_t stream) {
     // region is the queue head)
     // (from 32 heads on: below that the pieces of a launch are fewer than the SMs and a CTA per piece
     // starts sooner than the queue)
-    if (total > sms && done != nullptr && dyn.xa.R == 0 && p.B * p.Hkv >= 32 &&
+    if (total > sms && done != nullptr && dyn.xa.R == 0 && p.B * p.Hkv >= g_queue_min_heads.load(std::memory_order_relaxed) &&
         p.B * p.Hkv <= kvb::TcqCfg::kMaxHeads && g_queue.load(std::memory_order_relaxed)) {
       auto kernel = kvb::decode_tcq_kernel<MASKED, STATS>;
       if (int rc = ensure_smem(reinterpret_cast<const void*>(kernel), kvb::TcqCfg::kSmemBytes)) return rc;
@@ -580,6 +581,11 @@ int kvskip_set_option(const char* name, int value) {
     g_queue.store(value ? 1 : 0, std::memory_order_relaxed);
     return KVSKIP_OK;
   }
+  if (!std::strcmp(name, "queue_min_heads")) {
+    if (value < 1) return fail(KVSKIP_E_ARG, "queue_min_heads: at least 1");
+    g_queue_min_heads.store(value, std::memory_order_relaxed);
+    return KVSKIP_OK;
+  }
   if (!std::strcmp(name, "min_blocks")) {
     if (value < 1 || value > 4096) return fail(KVSKIP_E_ARG, "min_blocks: 1..4096");
     g_min_blocks.store(value, std::memory_order_relaxed);
@@ -612,6 +618,7 @@ int kvskip_get_option(const char* name) {
   if (name && !std::strcmp(name, "spin_limit")) return g_xchg_spin.load(std::memory_order_relaxed);
   if (name && !std::strcmp(name, "queue")) return g_queue.load(std::memory_order_relaxed);
   if (name && !std::strcmp(name, "min_blocks")) return g_min_blocks.load(std::memory_order_relaxed);
+  if (name && !std::strcmp(name, "queue_min_heads")) return g_queue_min_heads.load(std::memory_order_relaxed);
   if (name && !std::strcmp(name, "plan_rounds")) return g_plan_rounds.load(std::memory_order_relaxed);
   if (name && !std::strcmp(name, "plan_cluster")) return g_plan_cluster.load(std::memory_order_relaxed);
   return fail(KVSKIP_E_ARG, "unknown option");

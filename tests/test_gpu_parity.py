@@ -323,6 +323,42 @@ def test_plan_update_single_step_vs_oracle(T, kind, calib_on, B, path):
     assert torch.allclose(gpu["lse_att"].cpu()[okq], cpu["lse_att"][okq], rtol=1e-5, atol=1e-5)
 
 
+@pytest.mark.parametrize("T,B", [(8192 + 3, 2), (199, 3), (40, 1), (65536 + 1, 1)])
+def test_plan_work_layouts_give_the_same_bits(T, B):
+    """`plan` spreads a head's centroid scores over several CTAs in two ways: a thread-block cluster
+    whose CTAs hand their results to the first one through its shared memory (1, 2, 4 or 8 CTAs per
+    head), and independent CTAs of 32-block rounds counted in global memory (1, 2, 4 or 8 rounds
+    each).  Every layout must leave every output bit-identical: same state in, one call each."""
+    NBC = math.ceil(T / 64) + 64
+    q, k, v, scale, st = _planner_state(77, B, T, NBC, DEV)
+    qc, kc = q.to(DEV), k.to(DEV)
+    ext = K.ext()
+    outs = {}
+    layouts = [("plan_cluster", -1), ("plan_cluster", 1), ("plan_cluster", 2), ("plan_cluster", 4), ("plan_cluster", 8),
+               ("plan_rounds", 0), ("plan_rounds", 1), ("plan_rounds", 2), ("plan_rounds", 4), ("plan_rounds", 8)]
+    try:
+        for name, value in layouts:
+            ext.set_option("plan_cluster", value if name == "plan_cluster" else 0)
+            ext.set_option("plan_rounds", value if name == "plan_rounds" else 0)
+            gpu = {n: t.to(DEV) for n, t in st.items()}
+            ext.plan(qc, kc, gpu["csum"], gpu["lse_ref"], gpu["cs_ref"], gpu["keep"], gpu["lse_att"], gpu["age"],
+                     gpu["flags"], gpu["cs_now"], gpu["trig"], gpu["block_idx"], gpu["block_cnt"], scale, 0.05, 32, 2,
+                     True, gpu["idx"], gpu["calib"], gpu["est"], True, 2, gpu["aix"])
+            cnt = gpu["block_cnt"]
+            valid = torch.arange(NBC, device=DEV)[None, None, :] < cnt[..., None]
+            gpu["block_idx"] = torch.where(valid, gpu["block_idx"], 0)
+            outs[(name, value)] = gpu
+    finally:
+        ext.set_option("plan_cluster", -1)
+        ext.set_option("plan_rounds", 0)
+    assert ext.device_status() == 0
+    first = outs[layouts[0]]
+    assert int(first["block_cnt"].sum()) > 0
+    for key, got in outs.items():
+        for n in ("csum", "cs_now", "trig", "age", "est", "block_cnt", "block_idx"):
+            assert torch.equal(got[n], first[n]), (key, n)
+
+
 VARIANTS = {
     "plain": dict(dense_heads=(6,)),
     "union": dict(dense_heads=(6,), index_heads=(2,), index_union=True),
