@@ -307,6 +307,7 @@ int kvskip_launch_append(uint16_t* k, uint16_t* v, int64_t sb, int64_t sh, int64
  *   "queue"        1 (default): a decode launch with block lists, V loaded, 32 to 1024 (batch, kv head)
  *                  pairs and more pieces than SMs runs as one persistent CTA per SM pulling (head,
  *                  piece) items from a device-side queue; 0: one CTA per piece.  Same bits either way.
+ *   "queue_min_heads"  fewest (batch, kv head) pairs of a launch that takes the queue kernel; default 32.
  *   "min_blocks"   shortest piece (in 64-token blocks) a block list is cut into when the launch has
  *                  more CTAs than SMs; default 24.
  *   "plan_cluster" CTAs per (batch, kv head) of `plan` when it runs on thread-block clusters (the CTAs

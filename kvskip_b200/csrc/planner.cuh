@@ -12,11 +12,12 @@
 //   top-p cut        per query head lane l owns blocks l, l+32, ...; 32 bisection steps on the
 //                    log-weight threshold in [-80, 0], each a lane-serial sum + butterfly.
 // Layout of the work is ours.  Both kernels are chains of dependent memory latencies rather than
-// bandwidth: `plan` spreads the centroid scores over ceil(nb/32) CTAs per head and lets the last
-// one to finish do the fold; the per-block "attended" flags are staged in shared memory with
-// independent coalesced loads, and the fold loads its operands four blocks ahead, so a head costs
-// a handful of memory round trips instead of one per block.  No per-head shared-memory table of
-// scores is needed, so block counts beyond 3072 (contexts beyond 196 608 tokens) work.
+// bandwidth: `plan` spreads a head's centroid scores over the CTAs of a thread-block cluster, which
+// hand scores, fold operands and attended flags to the cluster's first CTA through its shared
+// memory (plan_cluster_kernel; plan_kernel, with a counter in global memory, for heads whose table
+// does not fit there); every load of a phase is requested before the first is used, and the fold
+// is written with selects so that the four query heads' chains overlap.  A head costs a handful of
+// memory round trips, whatever its length.
 #pragma once
 #include "common.cuh"
 
@@ -586,125 +587,6 @@ __device__ __forceinline__ float pl_bisect_smem(const float* x, float* ey, const
   return lo;
 }
 
-// The top-p cut of the two-pass V-skip's block selection (no reference order to keep): the same
-// bisection, but only until at most 32 blocks lie between the bounds (about 6 steps instead of
-// 20-odd, each of which costs a butterfly); those candidates are then sorted across the lanes of
-// the warp, and the cut is the first position at which the mass above the upper bound plus the
-// running sum of the sorted candidates reaches the level.  Returns lo with kept set {y >= lo}, the
-// set the full bisection ends with (up to float rounding of the mass at the threshold).
-// cand: 32 floats of shared memory of this warp.  The blocks of the kept set get mark[block] = 1,
-// straight from the registers that hold y.
-template <int R>
-__device__ __forceinline__ void pl_topp_regs(const float* x, const int nb, const int lane, const float lse,
-                                             const float level, float* cand, uint8_t* mark) {
-  float y[R], e[R];
-#pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const int i = lane + 32 * r;
-    y[r] = i < nb ? x[i] - lse : -INFINITY;
-    e[r] = i < nb ? __expf(x[i] - lse) : 0.f;
-  }
-  float lo = -80.f, hi = 0.f;
-  int n_lo = 0, n_hi = 0;       // blocks with y >= lo, y >= hi
-  float a_hi = 0.f;             // mass{y >= hi}
-#pragma unroll
-  for (int r = 0; r < R; ++r) {
-    n_lo += (y[r] >= lo) ? 1 : 0;
-    n_hi += (y[r] >= hi) ? 1 : 0;
-    a_hi += (y[r] >= hi) ? e[r] : 0.f;
-  }
-  n_lo = __reduce_add_sync(0xffffffffu, n_lo);
-  n_hi = __reduce_add_sync(0xffffffffu, n_hi);
-  a_hi = warp_sum(a_hi);
-  float cut = lo;
-  bool found = a_hi >= level;                       // (one block holds all the mass)
-  if (found) cut = hi;
-  for (int it = 0; it < 32 && !found && n_lo - n_hi > 32; ++it) {
-    const float mid = 0.5f * (lo + hi);
-    float a4[4] = {0.f, 0.f, 0.f, 0.f};
-    int n_mid = 0;
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const bool in = y[r] >= mid;
-      a4[r & 3] += in ? e[r] : 0.f;
-      n_mid += in ? 1 : 0;
-    }
-    const float a = warp_sum((a4[0] + a4[1]) + (a4[2] + a4[3]));
-    n_mid = __reduce_add_sync(0xffffffffu, n_mid);
-    if (a >= level) { lo = mid; n_lo = n_mid; } else { hi = mid; n_hi = n_mid; a_hi = a; }
-  }
-  if (!found) cut = lo;
-  const int total = n_lo - n_hi;                    // candidates: lo <= y < hi
-  if (!found && total > 0 && total <= 32) {         // (more than 32 only if 32 steps did not separate them)
-    int c = 0;
-#pragma unroll
-    for (int r = 0; r < R; ++r) c += (y[r] >= lo && y[r] < hi) ? 1 : 0;
-    int off = c;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int up = __shfl_up_sync(0xffffffffu, off, o);
-      if (lane >= o) off += up;
-    }
-    off -= c;
-    __syncwarp();
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-      if (y[r] >= lo && y[r] < hi) cand[off++] = y[r];
-    __syncwarp();
-    float v = lane < total ? cand[lane] : -INFINITY;
-#pragma unroll
-    for (int k = 2; k <= 32; k <<= 1) {               // bitonic sort, descending over the lanes
-#pragma unroll
-      for (int j = k >> 1; j > 0; j >>= 1) {
-        const float o = __shfl_xor_sync(0xffffffffu, v, j);
-        const bool desc = (lane & k) == 0, lower = (lane & j) == 0;
-        v = (lower == desc) ? fmaxf(v, o) : fminf(v, o);
-      }
-    }
-    float cum = lane < total ? __expf(v) : 0.f;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const float up = __shfl_up_sync(0xffffffffu, cum, o);
-      if (lane >= o) cum += up;
-    }
-    const unsigned reach = __ballot_sync(0xffffffffu, lane < total && a_hi + cum >= level);
-    if (reach != 0) cut = __shfl_sync(0xffffffffu, v, __ffs(reach) - 1);
-  }
-#pragma unroll
-  for (int r = 0; r < R; ++r)
-    if (y[r] >= cut) mark[lane + 32 * r] = 1;
-}
-
-// Second-pass weights of one query head once the kv head's kept set is known: exp(blk_max - lse_kept)
-// on kept blocks, 0 elsewhere, lse_kept the log-sum-exp of x over the kept set.  A lane's R values
-// of x, blk_max and the kept flag are read from shared memory in one go and everything else stays
-// in registers (a loop over shared memory pays a round trip per iteration here).  w: this head's
-// first weight, consecutive blocks PL_G floats apart.
-template <int R>
-__device__ __forceinline__ void pl_weights_regs(const float* x, const float* bm, const uint8_t* kept, const int nb,
-                                                const int lane, float* w) {
-  float xv[R], bv[R];
-  bool kp[R];
-#pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const int i = min(lane + 32 * r, nb - 1);
-    xv[r] = x[i];
-    bv[r] = bm[i];
-    kp[r] = lane + 32 * r < nb && kept[i] != 0;
-  }
-  float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-  for (int r = 0; r < R; ++r) m4[r & 3] = kp[r] ? fmaxf(m4[r & 3], xv[r]) : m4[r & 3];
-  const float M = warp_max(fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
-  float s4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-  for (int r = 0; r < R; ++r) s4[r & 3] += kp[r] ? __expf(xv[r] - M) : 0.f;
-  const float lse_kept = M + __logf(warp_sum((s4[0] + s4[1]) + (s4[2] + s4[3])));
-#pragma unroll
-  for (int r = 0; r < R; ++r)
-    if (lane + 32 * r < nb) w[static_cast<int64_t>(lane + 32 * r) * PL_G] = kp[r] ? __expf(bv[r] - lse_kept) : 0.f;
-}
-
 // With a device-resident length p.T bounds it and gives the row stride of the statistics.
 __global__ void __launch_bounds__(PL_THREADS) update_kernel(const kvskip_update_params p,
                                                             const int* __restrict__ t_dev) {
@@ -892,7 +774,6 @@ __global__ void __launch_bounds__(PL_THREADS) select_kernel(const float* __restr
   float* ey = sel_smem + (PL_G + warp) * nbs;
   uint8_t* skeep = reinterpret_cast<uint8_t*>(sel_smem + 2 * PL_G * nbs);
   __shared__ int scan[PL_THREADS];
-  __shared__ float s_cand[PL_G][32];   // candidates of a warp's top-p cut
   pdl_wait_prior();          // the statistics come from the kernel before this one
   pdl_launch_dependents();
   const int nb = t_dev ? (max(1, min(*t_dev, T_bound)) + TILE - 1) / TILE : nbs;   // blocks of the current length
@@ -910,43 +791,32 @@ __global__ void __launch_bounds__(PL_THREADS) select_kernel(const float* __restr
   for (int i = tid; i < nb; i += PL_THREADS) skeep[i] = pl_always(i, nb, local) ? 1 : 0;
   mx = warp_max(mx);
   __syncthreads();
-  float lse;
-  {   // four interleaved partial sums per lane: no reference order to keep here
-    float se[4] = {0.f, 0.f, 0.f, 0.f};
-    int k4 = 0;
-    for (int i = lane; i < nb; i += 32, ++k4) se[k4 & 3] += __expf(x[i] - mx);
-    lse = mx + __logf(warp_sum((se[0] + se[1]) + (se[2] + se[3])));
-  }
-  if (rule == 0 && in_regs) {
-    if (nb <= 8 * 32) pl_topp_regs<8>(x, nb, lane, lse, value, s_cand[warp], skeep);
-    else if (nb <= 16 * 32) pl_topp_regs<16>(x, nb, lane, lse, value, s_cand[warp], skeep);
-    else if (nb <= 32 * 32) pl_topp_regs<32>(x, nb, lane, lse, value, s_cand[warp], skeep);
-    else pl_topp_regs<64>(x, nb, lane, lse, value, s_cand[warp], skeep);
+  float se = 0.f;
+  for (int i = lane; i < nb; i += 32) se += __expf(x[i] - mx);
+  const float lse = mx + __logf(warp_sum(se));
+  float lo;
+  if (rule == 0) {
+    if (nb <= 8 * 32) lo = pl_bisect_regs<8, false>(x, nb, lane, lse, value);
+    else if (nb <= 16 * 32) lo = pl_bisect_regs<16, false>(x, nb, lane, lse, value);
+    else if (nb <= 32 * 32) lo = pl_bisect_regs<32, false>(x, nb, lane, lse, value);
+    else if (nb <= 64 * 32) lo = pl_bisect_regs<64, false>(x, nb, lane, lse, value);
+    else lo = pl_bisect_smem(x, ey, nb, lane, lse, value);
   } else {
-    const float lo = rule == 0 ? pl_bisect_smem(x, ey, nb, lane, lse, value) : 0.f;
-    for (int i = lane; i < nb; i += 32)
-      if (rule == 0 ? (x[i] - lse >= lo) : (__expf(x[i] - lse) >= value)) skeep[i] = 1;
+    lo = __logf(value);
   }
+  for (int i = lane; i < nb; i += 32)
+    if (rule == 0 ? (x[i] - lse >= lo) : (__expf(x[i] - lse) >= value)) skeep[i] = 1;
   __syncthreads();
   // weights of the second pass, relative to the mass of the kept set
-  float* w = weight + bh * nbs * PL_G + warp;
-  if (in_regs) {
-    if (nb <= 8 * 32) pl_weights_regs<8>(x, ey, skeep, nb, lane, w);
-    else if (nb <= 16 * 32) pl_weights_regs<16>(x, ey, skeep, nb, lane, w);
-    else if (nb <= 32 * 32) pl_weights_regs<32>(x, ey, skeep, nb, lane, w);
-    else pl_weights_regs<64>(x, ey, skeep, nb, lane, w);
-  } else {   // long rows: maximum, then four interleaved partial sums per lane, from shared memory
-    float M = -INFINITY;
-    for (int i = lane; i < nb; i += 32)
-      if (skeep[i]) M = fmaxf(M, x[i]);
-    M = warp_max(M);
-    float sk[4] = {0.f, 0.f, 0.f, 0.f};
-    int k4 = 0;
-    for (int i = lane; i < nb; i += 32, ++k4) sk[k4 & 3] += skeep[i] ? __expf(x[i] - M) : 0.f;
-    const float lse_kept = M + __logf(warp_sum((sk[0] + sk[1]) + (sk[2] + sk[3])));
-    for (int i = lane; i < nb; i += 32)
-      w[static_cast<int64_t>(i) * PL_G] = skeep[i] ? __expf(blk_max[hrow * nbs + i] - lse_kept) : 0.f;
-  }
+  float m2 = -INFINITY, s2 = 0.f;
+  for (int i = lane; i < nb; i += 32)
+    if (skeep[i]) pl_fold(m2, s2, x[i]);
+  const float M = warp_max(m2);
+  const float S = warp_sum(s2 > 0.f ? s2 * __expf(m2 - M) : 0.f);
+  const float lse_kept = M + __logf(S);
+  for (int i = lane; i < nb; i += 32)
+    weight[(bh * nbs + i) * PL_G + warp] =
+        skeep[i] ? __expf((in_regs ? ey[i] : blk_max[hrow * nbs + i]) - lse_kept) : 0.f;
   for (int i = tid; i < nbs; i += PL_THREADS) keep[bh * nbs + i] = i < nb ? skeep[i] : 0;
   for (int i = nb + lane; i < nbs; i += 32) weight[(bh * nbs + i) * PL_G + warp] = 0.f;
   pl_compact(nb, block_idx + bh * nbs, block_cnt + bh, scan, [&](int i) { return skeep[i] != 0; });
