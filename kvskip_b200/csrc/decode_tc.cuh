@@ -264,6 +264,47 @@ struct XchgArgs {
   unsigned int spin;     // polls of a peer's flag before the wait gives up (status word 0x510 + peer)
 };
 
+// Look-ahead of a producer thread over the blocks of its piece.  The number of block i comes from
+// the list (a load) and, with a paged cache, its page from the table (a second load that depends on
+// the first); asked for when the block is due, each costs the producer a memory round trip per
+// block between a stage becoming free and its refill.  Here the list is read eight blocks ahead and
+// the table four, so that in steady state both values are in registers when the stage is free.
+template <bool MASKED>
+struct BlockAhead {
+  static constexpr int LA = 4;
+  int blk[2 * LA];
+  int pg[LA];
+  const int32_t* list;   // entries of this piece (MASKED), first at list[0]
+  const int32_t* table;  // page table row of the sequence, or null
+  int first, n, seq;
+
+  __device__ __forceinline__ int entry(const int j) const {
+    if (j >= n) return 0;
+    return MASKED ? list[j] : first + j;
+  }
+  __device__ __forceinline__ int page(const int b) const { return table ? table[b] : seq; }
+  // first: number of the piece's first block when there is no list; seq: what `page` is without a table
+  __device__ __forceinline__ void init(const int32_t* list_, const int32_t* table_, const int first_, const int n_,
+                                       const int seq_) {
+    list = list_, table = table_, first = first_, n = n_, seq = seq_;
+#pragma unroll
+    for (int j = 0; j < 2 * LA; ++j) blk[j] = entry(j);
+#pragma unroll
+    for (int j = 0; j < LA; ++j) pg[j] = page(blk[j]);
+  }
+  // block i (calls in order i = 0, 1, ...): its number and page; requests those of later blocks
+  __device__ __forceinline__ void next(const int i, int& b_out, int& pg_out) {
+    b_out = blk[0];
+    pg_out = pg[0];
+#pragma unroll
+    for (int j = 0; j + 1 < 2 * LA; ++j) blk[j] = blk[j + 1];
+    blk[2 * LA - 1] = entry(i + 2 * LA);
+#pragma unroll
+    for (int j = 0; j + 1 < LA; ++j) pg[j] = pg[j + 1];
+    pg[LA - 1] = page(blk[LA - 1]);
+  }
+};
+
 // Merge of the S pieces of one (query head, output element) on the tensor-core path: global max,
 // then the rescaled sums in FOUR interleaved chains (pieces s = k mod 4 in ascending order, combined
 // as (c0 + c1) + (c2 + c3)): four independent chains of loads and additions instead of one, which
@@ -529,15 +570,17 @@ decode_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, in
   if (warp == NC) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
+      BlockAhead<MASKED> ahead;
+      ahead.init(MASKED ? list + i0 : nullptr, pages ? pages + static_cast<int64_t>(b) * max_pages : nullptr, i0, n, b);
       for (int i = 0; i < n; ++i) {
         const int s = i % S;
         if (i >= S && !mbar_wait(&empty[s], ((i / S) - 1) & 1, 0x200u + s)) break;
-        const int blk = MASKED ? list[i0 + i] : i0 + i;
         // contiguous cache: rows blk*64.. of sequence b; paged cache: the whole page the table
         // names for block blk (the maps then run over pages instead of sequences; an entry
         // outside the pool is out of bounds for the map and reads as zeros)
+        int blk, bp;
+        ahead.next(i, blk, bp);
         const int t0 = pages ? 0 : blk * TILE;
-        const int bp = pages ? pages[static_cast<int64_t>(b) * max_pages + blk] : b;
         unsigned char* dst = ring + s * Cfg::kStageBytes;
         mbar_expect_tx(&full[s], Cfg::kStageBytes);
 #pragma unroll

@@ -206,12 +206,14 @@ decode_tcq_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, i
         mbar_arrive(&ifull[qi]);
         const int next = atomicAdd(queue, 1);            // in flight while this item's loads are issued
         const int32_t* list = MASKED ? p.block_idx + static_cast<int64_t>(bh) * p.max_blocks : nullptr;
+        BlockAhead<MASKED> ahead;
+        ahead.init(MASKED ? list + i0 : nullptr, pages ? pages + static_cast<int64_t>(b) * max_pages : nullptr, i0, n, b);
         for (int i = 0; i < n; ++i) {
           const int g2 = gi + i, s = g2 % S;
           if (g2 >= S && !mbar_wait(&empty[s], ((g2 / S) - 1) & 1, 0x200u + s)) { ok = false; break; }
-          const int blk = MASKED ? list[i0 + i] : i0 + i;
+          int blk, bp;
+          ahead.next(i, blk, bp);
           const int t0 = pages ? 0 : blk * TILE;
-          const int bp = pages ? pages[static_cast<int64_t>(b) * max_pages + blk] : b;
           unsigned char* dst = ring + s * TcqCfg::kStageBytes;
           mbar_expect_tx(&full[s], TcqCfg::kStageBytes);
           tma_load_4d(dst, &maps.k, &full[s], 0, t0, h, bp);

@@ -62,10 +62,14 @@ pv_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* _
   if (warp == NC) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
+      BlockAhead<true> ahead;   // list entries eight blocks ahead of the stage they are needed for
+      ahead.init(list + i0, nullptr, i0, n, b);
       for (int i = 0; i < n; ++i) {
         const int s = i % S;
         if (i >= S && !mbar_wait(&empty[s], ((i / S) - 1) & 1, 0x420u + s)) break;
-        const int t0 = list[i0 + i] * TILE;
+        int blk_i, unused;
+        ahead.next(i, blk_i, unused);
+        const int t0 = blk_i * TILE;
         unsigned char* dst = ring + s * Cfg::kStageBytes;
         mbar_expect_tx(&full[s], Cfg::kStageBytes);
         tma_load_4d(dst, &maps.v, &full[s], 0, t0, h, b);
@@ -79,26 +83,47 @@ pv_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* _
     const __half* pin = reinterpret_cast<const __half*>(p.p_in) + (hq0 + (head & 3)) * p.t_pad;
     const float* scl = p.blk_scale + (static_cast<int64_t>(b) * p.Hkv + h) * p.nb * G + (head & 3);
 
+    // A warp's blocks are a chain list entry -> (block weight, P of its 64 tokens) -> MMA.  Walked one
+    // block at a time that is two memory round trips per block and warp, which bounded the kernel
+    // (0.4 us per block and CTA whatever the bandwidth).  So the chain is pipelined: the list entry is
+    // read two blocks ahead and the block's weight and P (eight half2 per thread) one block ahead,
+    // while the current block is multiplied.
+    struct Raw {
+      float f;
+      __half2 hh[4][2];
+    };
+    auto fetch = [&](Raw& r, const int blk) {
+      r.f = head < G ? scl[static_cast<int64_t>(blk) * G] : 0.f;
+#pragma unroll
+      for (int kt = 0; kt < 4; ++kt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int tok = kt * 16 + e * 8 + 2 * (lane & 3);          // first of this thread's two tokens
+          r.hh[kt][e] = head < G ? *reinterpret_cast<const __half2*>(pin + blk * TILE + tok) : __half2{};
+        }
+    };
+    const int last = i0 + n - 1;
+    int blk = warp < n ? list[min(i0 + warp, last)] : 0;
+    int blk_next = warp < n ? list[min(i0 + warp + NC, last)] : 0;
+    Raw cur, nxt;
+    if (warp < n) fetch(cur, blk);
     for (int i = warp; i < n; i += NC) {
       const int s = i % S;
-      const int blk = list[i0 + i];
       const int t0 = blk * TILE;
-      // weights of this block as B fragments (high and low bf16 parts), fetched while V is in flight
+      const int blk_after = list[min(i0 + i + 2 * NC, last)];
+      if (i + NC < n) fetch(nxt, blk_next);
+      // weights of this block as B fragments (high and low bf16 parts)
       uint32_t bhi[4][2], blo[4][2];
       {
-        const float f = head < G ? scl[static_cast<int64_t>(blk) * G] : 0.f;
+        const float f = cur.f;
 #pragma unroll
         for (int kt = 0; kt < 4; ++kt)
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int tok = kt * 16 + e * 8 + 2 * (lane & 3);          // first of this thread's two tokens
-            float w0 = 0.f, w1 = 0.f;
-            if (head < G) {
-              const __half2 hh = *reinterpret_cast<const __half2*>(pin + t0 + tok);
-              // P beyond T is not defined (the statistics pass never wrote it): those weights are zero
-              w0 = (t0 + tok < T) ? __half2float(__low2half(hh)) * f : 0.f;
-              w1 = (t0 + tok + 1 < T) ? __half2float(__high2half(hh)) * f : 0.f;
-            }
+            const int tok = kt * 16 + e * 8 + 2 * (lane & 3);
+            // P beyond T is not defined (the statistics pass never wrote it): those weights are zero
+            const float w0 = (head < G && t0 + tok < T) ? __half2float(__low2half(cur.hh[kt][e])) * f : 0.f;
+            const float w1 = (head < G && t0 + tok + 1 < T) ? __half2float(__high2half(cur.hh[kt][e])) * f : 0.f;
             const uint32_t hi = pack_bf16(w0, w1);
             bhi[kt][e] = hi;
             blo[kt][e] = pack_bf16(w0 - bf_lo(hi), w1 - bf_hi(hi));
@@ -131,6 +156,9 @@ pv_tc_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, int* _
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);
+      cur = nxt;
+      blk = blk_next;
+      blk_next = blk_after;
     }
   }
   __syncthreads();   // every block has been consumed: the ring is free for the sum over the warps
