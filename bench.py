@@ -573,7 +573,9 @@ def _planner_cases(dev, peak, K, synth, RefreshConfig, RefreshLayer, cases, targ
                       "note": f"mean per layer-step over steps {skip}..{steps - 1}; top-level figures average over all {L} "
                               f"layers, the dense layer 0 included; planner_layers_only: the {PL} planner layers timed "
                               "without layer 0 in the loop.  One extension call per layer-step (3 launches), issued "
-                              "from Python, no host sync; bytes = K+V of the blocks read; host_us: host time to issue "
+                              "from Python, no host sync; where a step has enough work to pay for it (batch x kv heads "
+                              "x blocks >= 16384: the batch 8 and 16 cases) `update` runs on the layer's own second "
+                              "stream, joined before the layer's next step; bytes = K+V of the blocks read; host_us: host time to issue "
                               "a layer-step; *_graph_replay: the steps replayed from one CUDA graph per step "
                               "(device-resident length), capturing steps left out; *_update_overlapped: `update` on a "
                               "second stream inside the graph (its results are needed only by the same layer's next "

@@ -9,6 +9,8 @@
 // caching allocator, and launches on the current stream of the inputs' device.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <cuda_runtime.h>
 #include <torch/extension.h>
 
 #include <cmath>
@@ -461,6 +463,52 @@ void update(const at::Tensor& blk_max, const at::Tensor& blk_sum, const at::Tens
     raise_on(kvskip_launch_update(&p, cur_stream()));
 }
 
+// `update` beside the main stream.  A layer that wants its `update` off the critical path owns one of
+// these: a second stream and two events.  refresh_step forks after the attention launch and records
+// `done` after update; overlap_join makes the current stream wait for the latest update (before the
+// layer's next step, and before anything else reads the planner state).  The caller keeps the
+// statistics tensors refresh_step returned, and the index tensor it passed, alive until that join:
+// nothing here tells the framework's allocator that the second stream still reads them.
+struct Overlap {
+  int device;
+  c10::cuda::CUDAStream side;   // from the framework's pool: lives as long as the process, so memory that
+                                // was marked as used on it can be released at any time
+  cudaEvent_t fork, done;
+  bool pending;
+};
+
+int64_t overlap_create() {
+  int device = 0;
+  TORCH_CHECK(cudaGetDevice(&device) == cudaSuccess, "overlap_create: no current device");
+  auto* o = new Overlap{device, c10::cuda::getStreamFromPool(false, static_cast<c10::DeviceIndex>(device)), nullptr,
+                        nullptr, false};
+  TORCH_CHECK(cudaEventCreateWithFlags(&o->fork, cudaEventDisableTiming) == cudaSuccess &&
+                  cudaEventCreateWithFlags(&o->done, cudaEventDisableTiming) == cudaSuccess,
+              "overlap_create: cannot create the events");
+  return reinterpret_cast<int64_t>(o);
+}
+
+void overlap_join(int64_t handle) {
+  auto* o = reinterpret_cast<Overlap*>(handle);
+  if (!o || !o->pending) return;
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  TORCH_CHECK(cudaStreamIsCapturing(static_cast<cudaStream_t>(cur_stream()), &st) == cudaSuccess &&
+                  st == cudaStreamCaptureStatusNone,
+              "overlap_join: an update of this layer is in flight on its own stream; join the layer before the capture "
+              "starts (a capturing stream cannot wait for work outside the capture)");
+  TORCH_CHECK(cudaStreamWaitEvent(static_cast<cudaStream_t>(cur_stream()), o->done, 0) == cudaSuccess,
+              "overlap_join: cannot wait for the update stream");
+  o->pending = false;
+}
+
+void overlap_destroy(int64_t handle) {
+  auto* o = reinterpret_cast<Overlap*>(handle);
+  if (!o) return;
+  cudaEventDestroy(o->fork);    // (work already queued behind an event is not affected by its destruction)
+  cudaEventDestroy(o->done);
+  delete o;
+}
+
 // One layer's refresh-policy step in a single call: plan -> masked attention with block
 // statistics over plan's block list -> update, three launches on the current stream and no host
 // synchronisation (what the reference's caller issues as three Python calls,
@@ -474,13 +522,36 @@ std::vector<at::Tensor> refresh_step(const at::Tensor& q, const at::Tensor& k, c
                                      const c10::optional<at::Tensor>& est, bool calib_on, int64_t calib_kind,
                                      double calib_rate, bool calib_free, const c10::optional<at::Tensor>& aix,
                                      double aix_thr, const c10::optional<at::Tensor>& t_dev,
-                                     const c10::optional<at::Tensor>& page_table, int64_t seq_len) {
+                                     const c10::optional<at::Tensor>& page_table, int64_t seq_len, int64_t overlap) {
+  Overlap* o = reinterpret_cast<Overlap*>(overlap);
+  cudaStream_t main = static_cast<cudaStream_t>(cur_stream());
+  if (o) {   // no second stream inside a stream capture: the captured step stays one chain
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(main, &st) != cudaSuccess || st != cudaStreamCaptureStatusNone) o = nullptr;
+  }
+  overlap_join(overlap);          // this layer's previous update wrote what plan reads
   plan(q, k, csum, lse_ref, cs_ref, keep, lse_att, age, flags, cs_now, trig, block_idx, block_cnt, scale, delta, max_age,
        local, true, idx, calib, est, calib_on, calib_kind, aix, t_dev, page_table, seq_len);
   auto r = decode(q, k, v, scale, block_idx, block_cnt, true, true, num_splits, 2, false, false, t_dev, page_table,
                   seq_len);
-  update(r[2], r[3], trig, cs_now, keep, lse_ref, cs_ref, lse_att, page_table.has_value() ? seq_len : k.size(2), level,
-         local, flags, idx, est, calib, calib_rate, calib_free, calib_kind, aix, aix_thr, t_dev);
+  const int64_t T_upd = page_table.has_value() ? seq_len : k.size(2);
+  if (!o) {
+    update(r[2], r[3], trig, cs_now, keep, lse_ref, cs_ref, lse_att, T_upd, level, local, flags, idx, est, calib,
+           calib_rate, calib_free, calib_kind, aix, aix_thr, t_dev);
+    return {r[0], r[1], r[2], r[3]};
+  }
+  // update on the layer's second stream: it needs the statistics of this pass and prepares the same
+  // layer's next step, so whatever follows on the current stream need not wait for it
+  TORCH_CHECK(cudaEventRecord(o->fork, main) == cudaSuccess && cudaStreamWaitEvent(o->side.stream(), o->fork, 0) == cudaSuccess,
+              "refresh_step: cannot fork the update stream");
+  {
+    const c10::cuda::CUDAStream side = o->side;
+    const c10::cuda::CUDAStreamGuard on_side(side);
+    update(r[2], r[3], trig, cs_now, keep, lse_ref, cs_ref, lse_att, T_upd, level, local, flags, idx, est, calib,
+           calib_rate, calib_free, calib_kind, aix, aix_thr, t_dev);
+  }
+  TORCH_CHECK(cudaEventRecord(o->done, o->side.stream()) == cudaSuccess, "refresh_step: cannot record the end of update");
+  o->pending = true;
   return {r[0], r[1], r[2], r[3]};
 }
 
@@ -686,7 +757,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("calib") = py::none(), py::arg("est") = py::none(), py::arg("calib_on") = false,
         py::arg("calib_kind") = 0, py::arg("calib_rate") = 0.0, py::arg("calib_free") = false,
         py::arg("aix") = py::none(), py::arg("aix_thr") = 0.0, py::arg("t_dev") = py::none(),
-        py::arg("page_table") = py::none(), py::arg("seq_len") = 0);
+        py::arg("page_table") = py::none(), py::arg("seq_len") = 0, py::arg("overlap") = 0);
+  m.def("overlap_create", &overlap_create, "a second stream + events for a layer's `update` (handle for refresh_step)");
+  m.def("overlap_join", &overlap_join, "the current stream waits for the layer's latest `update`", py::arg("handle"));
+  m.def("overlap_destroy", &overlap_destroy, py::arg("handle"));
   m.def("merge", &merge, "merge of R partial (max, sum, acc) rows", py::arg("part_acc"), py::arg("part_ml"));
   m.def("pack_partial", &pack_partial, "rank-local (out_f32, lse) -> packed (acc, m, l) rows", py::arg("out_f32"),
         py::arg("lse"));

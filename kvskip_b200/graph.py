@@ -69,6 +69,9 @@ class StepGraph:
             return self.launch()
         sig = self._scalars()
         if self.graph is None or sig != self.signature:
+            for layer in self.layers:            # an `update` still in flight on a layer's own stream
+                if hasattr(layer, "join"):       # is joined here: a capture cannot wait for it
+                    layer.join()
             graph = torch.cuda.CUDAGraph()
             # thread-local capture mode: CUDA calls of other threads (e.g. a communication
             # library's watchdog) do not invalidate the capture

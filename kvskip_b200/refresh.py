@@ -151,15 +151,58 @@ class PlannerState:
 
 @dataclass
 class RefreshLayer:
+    """overlap_update (CUDA backend, eager steps): `update` runs on a second stream owned by the
+    layer.  The attention output does not depend on it -- it prepares this layer's next step -- so
+    the launches that follow on the current stream (the rest of the model, the next layer's plan)
+    need not wait for it.  The layer joins the current stream with that stream before its next
+    step and whenever `state` is read through this object; tensors taken from `state` earlier and
+    kept by the caller are only safe to read after `join()`.  Inside a stream capture the step
+    stays one chain (`kvskip_b200.graph.StepGraph` forks and joins inside the graph itself)."""
     cfg: RefreshConfig
     ops: object = None
-    state: PlannerState | None = None
     t: int = 0
     last: dict = field(default_factory=dict)     # tensors of the latest step (block lists, stats), for inspection
+    overlap_update: bool = True
+    OVERLAP_MIN_WORK = 16384
 
     def __post_init__(self):
         if self.ops is None:
             self.ops = CudaOps()
+        self._state = None
+        self._ov = 0
+
+    @property
+    def state(self):
+        self.join()
+        return self._state
+
+    @state.setter
+    def state(self, st):
+        self._state = st
+
+    def join(self) -> None:
+        """The current stream waits for this layer's latest `update` (no-op without one in flight)."""
+        if self._ov:
+            K.ext().overlap_join(self._ov)
+
+    def _overlap_handle(self, work: int) -> int:
+        # below about 16k (batch x kv head x block) units a step is shorter than the host needs to
+        # issue it, and the fork and join would only add host time
+        if not self.overlap_update or not isinstance(self.ops, CudaOps) or work < self.OVERLAP_MIN_WORK:
+            return 0
+        if not self._ov:
+            self._ov = K.ext().overlap_create()
+        return self._ov
+
+    def __del__(self):
+        ov = getattr(self, "_ov", 0)
+        if ov:
+            try:
+                K.ext().overlap_join(ov)      # before the tensors of the last step are released
+                K.ext().overlap_destroy(ov)
+            except Exception:   # interpreter shutdown: the extension may be gone
+                pass
+            self._ov = 0
 
     # ---- first decode step: dense + statistics, state built with torch ops ------------------
     def _init(self, q, k, v, scale):
@@ -284,8 +327,10 @@ class RefreshLayer:
                 int(self.max_age_now()), int(cfg.local), float(cfg.level), int(ns), idx, s["calib"] if cal else None,
                 s["est"], bool(cal and self.t >= cfg.calib_hold), kind, float(cfg.calib or 0.0),
                 bool(cfg.calib_free), s["aix"] if auto else None, float(cfg.calib_auto_ix or 0.0), t_dev,
-                page_table, T)
-            self.last = {"blk_max": bmax, "blk_sum": bsum, "lse": lse, "first": False}
+                page_table, T,
+                **({"overlap": self._overlap_handle(B * k.shape[1] * nb)} if isinstance(self.ops, CudaOps) else {}))
+            # (with `update` on the layer's own stream these stay referenced until the join of the next step)
+            self.last = {"blk_max": bmax, "blk_sum": bsum, "lse": lse, "first": False, "idx": idx}
             return out
         if t_dev is not None:
             raise ValueError("a device-resident length needs a backend with fused_step")

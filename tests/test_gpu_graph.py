@@ -241,3 +241,31 @@ def test_single_pass_vskip_replayed_from_a_graph():
         assert torch.equal(out, eager[t][0]) and torch.equal(lse, eager[t][1]), t
     assert g.captures == 1 and g.replays >= steps - 2
     assert K.ext().device_status() == 0
+
+
+def test_update_on_the_layers_own_stream_changes_nothing():
+    """RefreshLayer runs `update` on a second stream by default (it prepares the layer's next step;
+    the attention output does not wait for it).  Two layers walk the same 24 steps, one with the
+    overlap and one without, with other work of the model in between on the main stream: outputs
+    and every state tensor are bit-equal after every step, and reading `state` joins the streams."""
+    import math
+    from kvskip_b200.refresh import RefreshConfig, RefreshLayer
+    cfg = RefreshConfig(calib=0.05, calib_warm=(16, 4), calib_kind="peak", calib_auto_ix=0.001)
+    steps, T0, B = 24, 4096 + 11, 2
+    walk = synth.planner_walk_device(61, T0, steps, torch.device(DEV), B=B)
+    ids = synth.token_ids_with_repeats(7, B, T0 + steps).to(DEV)
+    a, b = RefreshLayer(cfg), RefreshLayer(cfg, overlap_update=False)
+    a.OVERLAP_MIN_WORK = 0          # (by default only steps long enough to pay for the fork and join)
+    filler = torch.randn(2048, 2048, device=DEV)
+    for t in range(steps):
+        T = T0 + t + 1
+        idx = synth.index_blocks(ids, T, math.ceil(T / 64))
+        oa = a.step(walk.q[t], walk.k[:, :, :T], walk.v[:, :, :T], walk.scale, idx)
+        filler = torch.tanh(filler @ filler * 1e-3)          # the rest of a model's layer, on the main stream
+        ob = b.step(walk.q[t], walk.k[:, :, :T], walk.v[:, :, :T], walk.scale, idx)
+        assert torch.equal(oa, ob), t
+        for key in ("keep", "lse_ref", "cs_ref", "csum", "lse_att", "age", "calib", "est", "aix", "cs_now", "trig",
+                    "block_cnt"):
+            assert torch.equal(a.state[key], b.state[key]), (t, key)
+    assert a._ov != 0 and b._ov == 0
+    assert K.ext().device_status() == 0
