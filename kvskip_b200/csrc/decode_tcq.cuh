@@ -400,60 +400,91 @@ decode_tcq_kernel(const kvskip_params p, const __grid_constant__ TmaMaps maps, i
       if (!last) continue;
       __threadfence();
       // merge of the head's pieces in the order of tc_merge_pieces (four interleaved chains per output
-      // element: pieces s = u mod 4 ascending, combined (c0 + c1) + (c2 + c3)), written out so that
-      // one warp pulls a query head through in few round trips: the (m, l) pairs and this lane's four
-      // elements of up to 12 pieces are requested before any of them is used.
+      // element: pieces s = u mod 4 ascending, combined (c0 + c1) + (c2 + c3)).  This warp is the tail
+      // of the head (and, for the last head, of the launch), so it is written for few memory round
+      // trips: the maxima of all four query heads in one, then two query heads at a time, a lane
+      // owning four consecutive outputs of each (one 16-byte load per piece) and up to 12 pieces of
+      // both heads requested before any of them is used.
       {
         const int Su = d.S_use, ns = p.num_splits;
         constexpr int BATCH = 12;                         // pieces in flight: a multiple of 4 (chain u = s mod 4)
+        float mh[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) mh[g] = -INFINITY;
+        for (int s0 = 0; s0 < Su; s0 += BATCH) {
+          float t[G][BATCH];
+#pragma unroll
+          for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int u = 0; u < BATCH; ++u)
+              t[g][u] = s0 + u < Su ? __ldcg(p.part_ml + ((hq0 + g) * ns + s0 + u) * 2) : -INFINITY;
+#pragma unroll
+          for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int u = 0; u < BATCH; ++u) mh[g] = fmaxf(mh[g], t[g][u]);
+        }
 #pragma unroll 1
-        for (int g = 0; g < G; ++g) {
-          const int64_t hq = hq0 + g;
-          const float* ml = p.part_ml + hq * ns * 2;
-          const float* pa = p.part_acc + hq * ns * D + lane;
-          float m = -INFINITY;
-          for (int s0 = 0; s0 < Su; s0 += BATCH) {
-            float t[BATCH];
+        for (int g0 = 0; g0 < G; g0 += 2) {
+          float l[2][4], a[2][4][4], mu[2];
 #pragma unroll
-            for (int u = 0; u < BATCH; ++u) t[u] = s0 + u < Su ? __ldcg(ml + 2 * (s0 + u)) : -INFINITY;
+          for (int e = 0; e < 2; ++e) {
+            const float m = g0 == 0 ? mh[e] : mh[2 + e];
+            mu[e] = (m == -INFINITY) ? 0.f : m;
 #pragma unroll
-            for (int u = 0; u < BATCH; ++u) m = fmaxf(m, t[u]);
-          }
-          const float mu = (m == -INFINITY) ? 0.f : m;
-          float l[4] = {0.f, 0.f, 0.f, 0.f}, a[4][4];
+            for (int u = 0; u < 4; ++u) {
+              l[e][u] = 0.f;
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) a[u][j] = 0.f;
-          for (int s0 = 0; s0 < Su; s0 += BATCH) {
-            float w[BATCH], pl[BATCH], x[BATCH][4];
-#pragma unroll
-            for (int u = 0; u < BATCH; ++u) {
-              const int s2 = min(s0 + u, Su - 1);
-              w[u] = __ldcg(ml + 2 * s2);
-              pl[u] = __ldcg(ml + 2 * s2 + 1);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) x[u][j] = __ldcg(pa + static_cast<int64_t>(s2) * D + 32 * j);
+              for (int j = 0; j < 4; ++j) a[e][u][j] = 0.f;
             }
+          }
+          for (int s0 = 0; s0 < Su; s0 += BATCH) {
+            float w[2][BATCH], pl[2][BATCH];
+            float4 x[2][BATCH];
 #pragma unroll
-            for (int u = 0; u < BATCH; ++u) {
-              if (s0 + u < Su) {
-                const float ww = ex2(w[u] - mu);
-                l[u & 3] += pl[u] * ww;
+            for (int e = 0; e < 2; ++e) {
+              const int64_t hq = hq0 + g0 + e;
+              const float* ml = p.part_ml + hq * ns * 2;
+              const float* pa = p.part_acc + hq * ns * D + 4 * lane;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) a[u & 3][j] += x[u][j] * ww;
+              for (int u = 0; u < BATCH; ++u) {
+                const int s2 = min(s0 + u, Su - 1);
+                w[e][u] = __ldcg(ml + 2 * s2);
+                pl[e][u] = __ldcg(ml + 2 * s2 + 1);
+                x[e][u] = __ldcg(reinterpret_cast<const float4*>(pa + static_cast<int64_t>(s2) * D));
               }
             }
-          }
-          const float lt = (l[0] + l[1]) + (l[2] + l[3]);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float at = (a[0][j] + a[1][j]) + (a[2][j] + a[3][j]);
-            const float o32 = lt > 0.f ? at / lt : 0.f;
-            reinterpret_cast<__nv_bfloat16*>(p.out)[hq * D + lane + 32 * j] = __float2bfloat16(o32);
-            if (p.out_f32) p.out_f32[hq * D + lane + 32 * j] = o32;
+            for (int e = 0; e < 2; ++e)
+#pragma unroll
+              for (int u = 0; u < BATCH; ++u) {
+                if (s0 + u < Su) {
+                  const float ww = ex2(w[e][u] - mu[e]);
+                  l[e][u & 3] += pl[e][u] * ww;
+                  a[e][u & 3][0] += x[e][u].x * ww;
+                  a[e][u & 3][1] += x[e][u].y * ww;
+                  a[e][u & 3][2] += x[e][u].z * ww;
+                  a[e][u & 3][3] += x[e][u].w * ww;
+                }
+              }
           }
-          if (lane == 0 && p.lse) p.lse[hq] = lt > 0.f ? (m + log2f(lt)) * LN2 : -INFINITY;
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int64_t hq = hq0 + g0 + e;
+            const float m = g0 == 0 ? mh[e] : mh[2 + e];
+            const float lt = (l[e][0] + l[e][1]) + (l[e][2] + l[e][3]);
+            float o32[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float at = (a[e][0][j] + a[e][1][j]) + (a[e][2][j] + a[e][3][j]);
+              o32[j] = lt > 0.f ? at / lt : 0.f;
+            }
+            __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(p.out) + hq * D + 4 * lane);
+            ob[0] = __floats2bfloat162_rn(o32[0], o32[1]);
+            ob[1] = __floats2bfloat162_rn(o32[2], o32[3]);
+            if (p.out_f32)
+              *reinterpret_cast<float4*>(p.out_f32 + hq * D + 4 * lane) = make_float4(o32[0], o32[1], o32[2], o32[3]);
+            if (lane == 0 && p.lse) p.lse[hq] = lt > 0.f ? (m + log2f(lt)) * LN2 : -INFINITY;
+          }
         }
       }
       if (lane == 0) split_done[d.b * p.Hkv + d.h] = 0;
