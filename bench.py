@@ -574,7 +574,7 @@ def _planner_cases(dev, peak, K, synth, RefreshConfig, RefreshLayer, cases, targ
                               f"layers, the dense layer 0 included; planner_layers_only: the {PL} planner layers timed "
                               "without layer 0 in the loop.  One extension call per layer-step (3 launches), issued "
                               "from Python, no host sync; where a step has enough work to pay for it (batch x kv heads "
-                              "x blocks >= 16384: the batch 8 and 16 cases) `update` runs on the layer's own second "
+                              "x blocks >= 8192: every 64k case) `update` runs on the layer's own second "
                               "stream, joined before the layer's next step; bytes = K+V of the blocks read; host_us: host time to issue "
                               "a layer-step; *_graph_replay: the steps replayed from one CUDA graph per step "
                               "(device-resident length), capturing steps left out; *_update_overlapped: `update` on a "

@@ -85,8 +85,17 @@ def _auto_check(what: str) -> None:
         check_status(what)
 
 
+_SMS: dict = {}
+
+
 def num_sms() -> int:
-    return torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    """SMs of the current device (looked up once per device: the query costs microseconds of host
+    time, and a decode loop asks on every step)."""
+    dev = torch.cuda.current_device()
+    n = _SMS.get(dev)
+    if n is None:
+        n = _SMS[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return n
 
 
 def num_splits_for(bh: int, n_tiles: int, sms: int | None = None, max_splits: int = 64,

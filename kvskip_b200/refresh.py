@@ -163,7 +163,7 @@ class RefreshLayer:
     t: int = 0
     last: dict = field(default_factory=dict)     # tensors of the latest step (block lists, stats), for inspection
     overlap_update: bool = True
-    OVERLAP_MIN_WORK = 16384
+    OVERLAP_MIN_WORK = 8192
 
     def __post_init__(self):
         if self.ops is None:
@@ -186,8 +186,9 @@ class RefreshLayer:
             K.ext().overlap_join(self._ov)
 
     def _overlap_handle(self, work: int) -> int:
-        # below about 16k (batch x kv head x block) units a step is shorter than the host needs to
-        # issue it, and the fork and join would only add host time
+        # below about 8k (batch x kv head x block) units (batch 1 under 64k tokens) a step is shorter
+        # than the host needs to issue it, and the fork and join (about 8 us of host time) only add to that:
+        # batch 1 at 64k 59 -> 51 us per layer-step with the second stream, at 32k 45 -> 51 us
         if not self.overlap_update or not isinstance(self.ops, CudaOps) or work < self.OVERLAP_MIN_WORK:
             return 0
         if not self._ov:
