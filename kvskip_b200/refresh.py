@@ -122,6 +122,9 @@ class PlannerState:
             if fill:                       # a zero fill is already there
                 view.fill_(fill)
             self.views[name] = view
+        v = self.views     # the state tensors in the order the fused step takes them
+        self.step_args = (v["csum"], v["lse_ref"], v["cs_ref"], v["keep"], v["lse_att"], v["age"], v["flags"],
+                          v["cs_now"], v["trig"], v["block_idx"], v["block_cnt"])
 
     # dictionary-style access under the reference's key names ("NBC" and "scale" included)
     def __getitem__(self, key):
@@ -170,6 +173,7 @@ class RefreshLayer:
             self.ops = CudaOps()
         self._state = None
         self._ov = 0
+        self._ns_key, self._ns = None, 1
 
     @property
     def state(self):
@@ -276,9 +280,10 @@ class RefreshLayer:
         if q.dim() == 4:
             q = q.squeeze(2)
         paged = page_table is not None
-        if paged and (seq_len is None or self.state is None or not hasattr(self.ops, "fused_step")):
+        self.join()                        # once; below the state is taken without another join
+        if paged and (seq_len is None or self._state is None or not hasattr(self.ops, "fused_step")):
             raise ValueError("a paged cache needs seq_len, the CUDA backend, and a first step on contiguous views")
-        if self.state is None:
+        if self._state is None:
             if t_dev is not None:
                 raise ValueError("the first step of a layer builds the state on the host: run it with views of "
                                  "the current length and without t_dev")
@@ -286,9 +291,9 @@ class RefreshLayer:
         cfg = self.cfg
         B, T = q.shape[0], (int(seq_len) if paged else k.shape[2])
         nb = math.ceil(T / BLOCK)
-        if nb > self.state["NBC"]:
+        if nb > self._state.nbc:
             self._grow(nb + cfg.margin)
-        s = self.state
+        s = self._state
         idx = None
         if self.uses_index():
             if idx_blocks is None:
@@ -321,15 +326,18 @@ class RefreshLayer:
             self.last = {"blk_max": bmax, "blk_sum": bsum, "lse": lse, "first": False}
             return out
         if hasattr(self.ops, "fused_step"):
-            ns = K.splits_for_unsynced_plan(B * k.shape[1], nb)   # sized for every block: no host sync
-            out, lse, bmax, bsum = self.ops.fused_step(
-                q, k, v, s["csum"], s["lse_ref"], s["cs_ref"], s["keep"], s["lse_att"], s["age"], s["flags"],
-                s["cs_now"], s["trig"], s["block_idx"], s["block_cnt"], float(scale), float(cfg.delta),
-                int(self.max_age_now()), int(cfg.local), float(cfg.level), int(ns), idx, s["calib"] if cal else None,
-                s["est"], bool(cal and self.t >= cfg.calib_hold), kind, float(cfg.calib or 0.0),
-                bool(cfg.calib_free), s["aix"] if auto else None, float(cfg.calib_auto_ix or 0.0), t_dev,
-                page_table, T,
-                **({"overlap": self._overlap_handle(B * k.shape[1] * nb)} if isinstance(self.ops, CudaOps) else {}))
+            bh = B * k.shape[1]
+            if self._ns_key != (bh, nb):                         # sized for every block: no host sync
+                self._ns_key, self._ns = (bh, nb), int(K.splits_for_unsynced_plan(bh, nb))
+            a = s.step_args
+            args = (q, k, v, *a, float(scale), float(cfg.delta), int(self.max_age_now()), int(cfg.local),
+                    float(cfg.level), self._ns, idx, s.views["calib"] if cal else None, s.views["est"],
+                    bool(cal and self.t >= cfg.calib_hold), kind, float(cfg.calib or 0.0), bool(cfg.calib_free),
+                    s.views["aix"] if auto else None, float(cfg.calib_auto_ix or 0.0), t_dev, page_table, T)
+            if isinstance(self.ops, CudaOps):                    # straight to the extension, one call
+                out, lse, bmax, bsum = K.ext().refresh_step(*args, self._overlap_handle(bh * nb))
+            else:
+                out, lse, bmax, bsum = self.ops.fused_step(*args)
             # (with `update` on the layer's own stream these stay referenced until the join of the next step)
             self.last = {"blk_max": bmax, "blk_sum": bsum, "lse": lse, "first": False, "idx": idx}
             return out
