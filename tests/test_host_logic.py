@@ -129,3 +129,21 @@ def test_paged_cache_bookkeeping_on_cpu():
     small = PagedKV(2, B, H, D, 256, "cpu")
     with pytest.raises(RuntimeError, match="exhausted"):
         small.reserve(64)
+
+
+def test_pv_splits_is_one_wave_of_pieces_of_at_least_16_blocks():
+    """Split rule of the two-pass V-skip's second pass: as many pieces per (batch, kv head) as keep
+    the grid within the SM count, none shorter than 16 blocks, at least one."""
+    from kvskip_b200 import kvskip as K
+    assert K.pv_splits(8, 1024, sms=148) == 18
+    assert K.pv_splits(32, 1024, sms=148) == 4
+    assert K.pv_splits(64, 1024, sms=148) == 2
+    assert K.pv_splits(128, 512, sms=148) == 1
+    assert K.pv_splits(1000, 512, sms=148) == 1
+    assert K.pv_splits(8, 20, sms=148) == 2
+    assert K.pv_splits(8, 1, sms=148) == 1
+    for bh in (1, 7, 8, 33, 148, 149):
+        for cnt in (1, 15, 16, 17, 500, 4096):
+            s_ = K.pv_splits(bh, cnt, sms=148)
+            assert s_ >= 1 and (s_ == 1 or (bh * s_ <= 148 and (s_ - 1) * 16 < cnt))
+
