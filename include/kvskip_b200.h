@@ -337,7 +337,9 @@ const char* kvskip_last_error(void);
 
 /* Reads (and clears) the current device's kernel status word after synchronising `stream`:
  * 0 if every bounded wait inside the kernels completed, otherwise the code of the first that
- * gave up.  Host-blocking; meant for tests and post-mortems, not for the hot path.  When the word is
+ * gave up (0x2xx / 0x4xx: a stage of a kernel's load ring; 0x300 / 0x301: a page table entry outside
+ * the pool; 0x310: plan's hand-over inside a cluster; 0x500 + peer, 0x510 + peer: the exchange between
+ * GPUs).  Host-blocking; meant for tests and post-mortems, not for the hot path.  When the word is
  * non-zero the call also waits for the whole device and clears the split counters a kernel that
  * gave up may have left behind: no launch of this library may be in flight on another host thread. */
 int kvskip_device_status(void* stream, unsigned int* status);

@@ -483,6 +483,9 @@ __global__ void __launch_bounds__(PL_THREADS) plan_cluster_kernel(const kvskip_p
     return;
   }
   __syncthreads();           // this CTA's own rounds are in its shared memory
+  // (The CTAs of a cluster are scheduled together and every one of them arrives unconditionally, so
+  // this wait can only run out if a peer is stuck; the bound turns that into status word 0x310 and
+  // an unwritten list instead of a hang.)
   if (C > 1 && !cluster_mbar_wait(&arrived, 0, 0x310u)) return;
 
   // estimate of the mass outside the attended set: fold slot t takes blocks t, t+128, ...
